@@ -1,0 +1,377 @@
+// extern "C" surface of librglru_b200.so: argument validation, tensor-map
+// construction, and dispatch to the kernel launchers.  Declarations and the
+// reference lines each entry point replaces are in include/rglru_b200.h.
+
+#include <mutex>
+
+#include "../../include/rglru_b200.h"
+#include "rglru_device.cuh"
+#include "rglru_internal.h"
+
+namespace rglru {
+
+__device__ int g_device_status = 0;
+
+static thread_local cudaError_t t_last_cuda = cudaSuccess;
+
+static int fail_cuda(cudaError_t e) {
+  t_last_cuda = e;
+  return RGLRU_ERR_LAUNCH;
+}
+
+constexpr int MAX_DEVICES = 64;
+static std::mutex g_mutex;
+static int* g_status_ptr[MAX_DEVICES] = {nullptr};
+static int g_arch_ok[MAX_DEVICES] = {0};  // 0 unknown, 1 sm_100, -1 other
+
+// Device address of the status word and architecture check, once per device.
+static int device_setup(int** status) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (dev < 0 || dev >= MAX_DEVICES) return RGLRU_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_arch_ok[dev] == 0) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail_cuda(e);
+    g_arch_ok[dev] = (major == 10) ? 1 : -1;
+    if (g_arch_ok[dev] == 1) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_device_status);
+      if (e != cudaSuccess) { g_arch_ok[dev] = 0; return fail_cuda(e); }
+      g_status_ptr[dev] = static_cast<int*>(p);
+    }
+  }
+  if (g_arch_ok[dev] != 1) return RGLRU_ERR_UNSUPPORTED;
+  *status = g_status_ptr[dev];
+  return RGLRU_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 3-D map over a dense [B, T, D] tensor with a [1, rows, CH] box; out-of-range parts
+// of a box read as zero and are dropped on store.
+static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const size_t es = bf16 ? 2 : 4;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * es, static_cast<cuuint64_t>(D) * es * T};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(CH), static_cast<cuuint32_t>(rows), 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static bool aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) % n) == 0; }
+
+// TMA needs 16-byte aligned bases and row pitches, and strides below 2^40 bytes.
+static bool tma_shape_ok(int T, int D, size_t es) {
+  const unsigned long long pitch = static_cast<unsigned long long>(D) * es;
+  return (pitch % 16 == 0) && (pitch * static_cast<unsigned long long>(T) < (1ull << 40));
+}
+
+static int check_dims(int B, int T, int D) {
+  if (B <= 0 || T <= 0 || D <= 0) return RGLRU_ERR_BAD_SHAPE;
+  if (B > 65535) return RGLRU_ERR_BAD_SHAPE;  // batch rows map to gridDim.y
+  return RGLRU_OK;
+}
+
+}  // namespace rglru
+
+using namespace rglru;
+
+extern "C" {
+
+const char* rglru_status_string(int status) {
+  switch (status) {
+    case RGLRU_OK: return "ok";
+    case RGLRU_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case RGLRU_ERR_BAD_DTYPE: return "unknown io_dtype";
+    case RGLRU_ERR_BAD_SHAPE: return "bad shape: every dimension must be positive and B <= 65535";
+    case RGLRU_ERR_MISALIGNED: return "pointer not aligned to its element size";
+    case RGLRU_ERR_WORKSPACE: return "workspace missing or too small";
+    case RGLRU_ERR_LAUNCH: return "CUDA launch failed";
+    case RGLRU_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
+    case RGLRU_ERR_UNSUPPORTED: return "unsupported device: CUDA kernels are built for sm_100a only";
+    default: return "unknown status";
+  }
+}
+
+const char* rglru_last_cuda_error(void) { return cudaGetErrorString(t_last_cuda); }
+
+int rglru_abi_version(void) { return 1; }
+
+int rglru_device_status(int* detail) {
+  int* status = nullptr;
+  int rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e);
+  int host = 0;
+  e = cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (detail) *detail = host;
+  if (host != 0) {
+    const int zero = 0;
+    cudaMemcpy(status, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    return RGLRU_ERR_DEVICE_TIMEOUT;
+  }
+  return RGLRU_OK;
+}
+
+int rglru_chunk_steps(int io_dtype) {
+  (void)io_dtype;
+  return SAVE_EVERY;
+}
+
+size_t rglru_workspace_bytes(int B, int T, int D, int io_dtype) {
+  (void)io_dtype;
+  if (B <= 0 || T <= 0 || D <= 0) return 0;
+  const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+  return (static_cast<size_t>(B) * nsave * D + static_cast<size_t>(B) * D) * sizeof(float);
+}
+
+int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+              const uint8_t* tok, void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c,
+              int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x || !u_r || !u_i || !lambda || !y) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(x, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(y, es) || !aligned(lambda, 4) ||
+      !aligned(h0, 4) || !aligned(h_last, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (ws && ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  ScanFwdArgs a;
+  a.x = x; a.ur = u_r; a.ui = u_i; a.y = y;
+  a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
+  a.states = static_cast<float*>(ws);
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  FwdMaps maps;
+  bool tma = tma_shape_ok(T, D, es) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) && aligned(y, 16);
+  if (tma) {
+    const int rows = scan_fwd_box_rows(bf16);
+    tma = make_map(&maps.x, x, bf16, B, T, D, rows) && make_map(&maps.ur, u_r, bf16, B, T, D, rows) &&
+          make_map(&maps.ui, u_i, bf16, B, T, D, rows) && make_map(&maps.y, y, bf16, B, T, D, rows);
+  }
+  const cudaError_t e = launch_scan_fwd(bf16, tma, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u_r, const void* u_i,
+              const float* lambda, const float* h0, const uint8_t* tok, void* ws, size_t ws_bytes, void* dx,
+              void* du_r, void* du_i, float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype,
+              void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!dy || !x || !u_r || !u_i || !lambda || !dx || !du_r || !du_i || !dlambda) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(dy, es) || !aligned(x, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(dx, es) ||
+      !aligned(du_r, es) || !aligned(du_i, es) || !aligned(lambda, 4) || !aligned(h0, 4) || !aligned(dh_last, 4) ||
+      !aligned(dlambda, 4) || !aligned(dh0, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (!ws || ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+  ScanBwdArgs a;
+  a.dy = dy; a.x = x; a.ur = u_r; a.ui = u_i; a.dx = dx; a.dur = du_r; a.dui = du_i;
+  a.lambda = lambda; a.h0 = h0; a.dh_last = dh_last; a.tok = tok;
+  a.states = static_cast<const float*>(ws);
+  a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
+  a.dlambda = dlambda; a.dh0 = dh0;
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  BwdMaps maps;
+  bool tma = tma_shape_ok(T, D, es) && aligned(dy, 16) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) &&
+             aligned(dx, 16) && aligned(du_r, 16) && aligned(du_i, 16);
+  if (tma) {
+    const int rows = scan_bwd_box_rows(bf16);
+    tma = make_map(&maps.dy, dy, bf16, B, T, D, rows) && make_map(&maps.x, x, bf16, B, T, D, rows) &&
+          make_map(&maps.ur, u_r, bf16, B, T, D, rows) && make_map(&maps.ui, u_i, bf16, B, T, D, rows) &&
+          make_map(&maps.dx, dx, bf16, B, T, D, rows) && make_map(&maps.dur, du_r, bf16, B, T, D, rows) &&
+          make_map(&maps.dui, du_i, bf16, B, T, D, rows);
+  }
+  const cudaError_t e = launch_scan_bwd(bf16, tma, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_linear_scan_fwd(const float* decay, const float* drive, const float* h0, float* out, int B, int T, int D,
+                          void* stream) {
+  if (!decay || !drive || !out) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  if (!aligned(decay, 4) || !aligned(drive, 4) || !aligned(out, 4) || !aligned(h0, 4)) return RGLRU_ERR_MISALIGNED;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  RawScanArgs a = {};
+  a.decay = decay; a.drive = drive; a.h0 = h0; a.out = out;
+  a.B = B; a.T = T; a.D = D; a.status = status;
+  RawFwdMaps maps;
+  bool tma = tma_shape_ok(T, D, 4) && aligned(decay, 16) && aligned(drive, 16) && aligned(out, 16);
+  if (tma) {
+    const int rows = raw_box_rows();
+    tma = make_map(&maps.drive, drive, false, B, T, D, rows) && make_map(&maps.decay, decay, false, B, T, D, rows) &&
+          make_map(&maps.out, out, false, B, T, D, rows);
+  }
+  const cudaError_t e = launch_raw_fwd(tma, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_linear_scan_bwd(const float* d_out, const float* decay, const float* h0, const float* out, float* d_decay,
+                          float* d_drive, float* d_h0, int B, int T, int D, void* stream) {
+  if (!d_out || !decay || !out || !d_decay || !d_drive) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  if (!aligned(d_out, 4) || !aligned(decay, 4) || !aligned(out, 4) || !aligned(d_decay, 4) || !aligned(d_drive, 4) ||
+      !aligned(h0, 4) || !aligned(d_h0, 4))
+    return RGLRU_ERR_MISALIGNED;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  RawScanArgs a = {};
+  a.dout = d_out; a.decay = decay; a.h0 = h0; a.out_in = out; a.ddecay = d_decay; a.ddrive = d_drive; a.dh0 = d_h0;
+  a.B = B; a.T = T; a.D = D; a.status = status;
+  RawBwdMaps maps;
+  bool tma = tma_shape_ok(T, D, 4) && aligned(d_out, 16) && aligned(decay, 16) && aligned(out, 16) &&
+             aligned(d_decay, 16) && aligned(d_drive, 16);
+  if (tma) {
+    const int rows = raw_box_rows();
+    tma = make_map(&maps.dout, d_out, false, B, T, D, rows) && make_map(&maps.decay, decay, false, B, T, D, rows) &&
+          make_map(&maps.out, out, false, B, T, D, rows) && make_map(&maps.ddecay, d_decay, false, B, T, D, rows) &&
+          make_map(&maps.ddrive, d_drive, false, B, T, D, rows);
+  }
+  const cudaError_t e = launch_raw_bwd(tma, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_conv_fwd(const void* x_in, const float* conv_w, const float* conv_b, const void* conv_state,
+                   const uint8_t* tok, void* x_conv, void* new_state, int B, int T, int D, int io_dtype,
+                   void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x_in || !conv_w || !x_conv) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(x_in, es) || !aligned(x_conv, es) || !aligned(conv_state, es) || !aligned(new_state, es) ||
+      !aligned(conv_w, 4) || !aligned(conv_b, 4))
+    return RGLRU_ERR_MISALIGNED;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  ConvArgs a;
+  a.x_in = x_in; a.w = conv_w; a.bias = conv_b; a.state = conv_state; a.tok = tok; a.out = x_conv;
+  a.new_state = new_state; a.B = B; a.T = T; a.D = D;
+  a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(x_in, 16) && aligned(x_conv, 16) &&
+                aligned(conv_state, 16);
+  const cudaError_t e = launch_conv_fwd(bf16, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+size_t rglru_conv_bwd_workspace_bytes(int B, int T, int D) {
+  if (B <= 0 || T <= 0 || D <= 0) return 0;
+  return static_cast<size_t>(conv_bwd_partial_rows(B, T)) * 5 * D * sizeof(float);
+}
+
+int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, const void* conv_state,
+                   const uint8_t* tok, void* dx_in, float* d_w, float* d_b, void* d_state, void* ws, size_t ws_bytes,
+                   int B, int T, int D, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!d_conv || !x_in || !conv_w || !dx_in || !d_w) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(d_conv, es) || !aligned(x_in, es) || !aligned(dx_in, es) || !aligned(conv_state, es) ||
+      !aligned(d_state, es) || !aligned(conv_w, 4) || !aligned(d_w, 4) || !aligned(d_b, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (!ws || ws_bytes < rglru_conv_bwd_workspace_bytes(B, T, D)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  ConvBwdArgs a;
+  a.d_conv = d_conv; a.x_in = x_in; a.w = conv_w; a.state = conv_state; a.tok = tok; a.dx_in = dx_in;
+  a.d_w = d_w; a.d_b = d_b; a.d_state = d_state; a.part = static_cast<float*>(ws);
+  a.B = B; a.T = T; a.D = D;
+  a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(d_conv, 16) && aligned(x_in, 16) &&
+                aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16);
+  const cudaError_t e = launch_conv_bwd(bf16, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_decode_conv(const void* x_in, const float* conv_w, const float* conv_b, void* conv_state,
+                      const uint8_t* tok, void* x_conv, int B, int D, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x_in || !conv_w || !conv_state || !x_conv) return RGLRU_ERR_NULL_POINTER;
+  if (B <= 0 || D <= 0) return RGLRU_ERR_BAD_SHAPE;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(x_in, es) || !aligned(x_conv, es) || !aligned(conv_state, es) || !aligned(conv_w, 4) ||
+      !aligned(conv_b, 4))
+    return RGLRU_ERR_MISALIGNED;
+  int* status = nullptr;
+  int rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  ConvArgs a;
+  a.x_in = x_in; a.w = conv_w; a.bias = conv_b; a.state = nullptr; a.tok = tok; a.out = x_conv;
+  a.new_state = conv_state; a.B = B; a.T = 1; a.D = D;
+  a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(x_in, 16) && aligned(x_conv, 16) &&
+                aligned(conv_state, 16);
+  const cudaError_t e = launch_decode_conv(bf16, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_decode_step(const void* x, const void* u_r, const void* u_i, const float* lambda, float* h,
+                      const uint8_t* tok, void* y, int B, int D, float c, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x || !u_r || !u_i || !lambda || !h || !y) return RGLRU_ERR_NULL_POINTER;
+  if (B <= 0 || D <= 0) return RGLRU_ERR_BAD_SHAPE;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(x, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(y, es) || !aligned(lambda, 4) ||
+      !aligned(h, 4))
+    return RGLRU_ERR_MISALIGNED;
+  int* status = nullptr;
+  int rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  DecodeArgs a;
+  a.x = x; a.ur = u_r; a.ui = u_i; a.lambda = lambda; a.h = h; a.tok = tok; a.y = y;
+  a.B = B; a.D = D; a.c = c;
+  a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) &&
+                aligned(y, 16) && aligned(h, 16);
+  const cudaError_t e = launch_decode_step(bf16, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,481 @@
+// Causal depthwise convolution (kernel width 4) in front of the RG-LRU, its
+// backward, and the two single-token decode kernels.  All are streaming
+// kernels bound by HBM bandwidth: every activation is read once and written
+// once with 16-byte accesses, each thread sliding a 4-row register window over
+// a run of time-steps so the three-row halo is re-read once per run.
+//
+// Reference behaviour: griffin/griffin.py:474-487 (dense path), :488-510
+// (right-padded path), :459-528 at T = 1 (decode).
+
+#include "rglru_device.cuh"
+#include "rglru_internal.h"
+
+namespace rglru {
+
+constexpr int CONV_TAPS = 4;
+
+template <typename IO, int VEC>
+struct Vec {
+  // VEC channels of IO as one aligned access (VEC == 1: scalar fallback for odd widths).
+  static __device__ __forceinline__ void load(const IO* p, float (&v)[VEC]) {
+    if (VEC == 1) {
+      v[0] = Pack<IO>::to_float(p[0]);
+    } else if (sizeof(IO) == 4) {
+      const float4 r = *reinterpret_cast<const float4*>(p);
+      v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    } else {
+      const uint4 r = *reinterpret_cast<const uint4*>(p);
+      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[(2 * k) % VEC] = __uint_as_float(w[k] << 16);
+        v[(2 * k + 1) % VEC] = __uint_as_float(w[k] & 0xffff0000u);
+      }
+    }
+  }
+  static __device__ __forceinline__ void store(IO* p, const float (&v)[VEC]) {
+    if (VEC == 1) {
+      p[0] = Pack<IO>::from_float(v[0]);
+    } else if (sizeof(IO) == 4) {
+      *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+    } else {
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[(2 * k) % VEC], v[(2 * k + 1) % VEC]);
+        w[k] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+};
+
+template <typename IO>
+constexpr int vec_width() { return 16 / sizeof(IO); }
+
+// ---------------------------------------------------------------- forward
+// Thread = (batch row, run of RUN time-steps, VEC channels).
+template <typename IO, int VEC, int RUN>
+__global__ void __launch_bounds__(256) conv_fwd_kernel(const IO* __restrict__ xin, const float* __restrict__ w,
+                                                       const float* __restrict__ bias, const IO* __restrict__ state,
+                                                       const uint8_t* __restrict__ tok, IO* __restrict__ out, int B,
+                                                       int T, int D) {
+  const int nvec = D / VEC;
+  const int nrun = (T + RUN - 1) / RUN;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * nrun * nvec) return;
+  const int dv = static_cast<int>(gid % nvec);
+  const int run = static_cast<int>((gid / nvec) % nrun);
+  const int b = static_cast<int>(gid / nvec / nrun);
+  const int d = dv * VEC;
+  const int t_begin = run * RUN;
+  const int t_end = min(T, t_begin + RUN);
+
+  float wt[CONV_TAPS][VEC], bs[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    bs[v] = bias ? bias[d + v] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < CONV_TAPS; ++k) wt[k][v] = w[(d + v) * CONV_TAPS + k];
+  }
+  // hist[l-1] holds the input l steps before the current one.
+  float hist[CONV_TAPS - 1][VEC];
+#pragma unroll
+  for (int l = 1; l < CONV_TAPS; ++l) {
+    const int t = t_begin - l;
+    if (t >= 0) {
+      Vec<IO, VEC>::load(xin + (static_cast<size_t>(b) * T + t) * D + d, hist[l - 1]);
+    } else if (state) {
+      Vec<IO, VEC>::load(state + (static_cast<size_t>(b) * (CONV_TAPS - 1) + (CONV_TAPS - 1 + t)) * D + d, hist[l - 1]);
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) hist[l - 1][v] = 0.0f;
+    }
+  }
+  for (int t = t_begin; t < t_end; ++t) {
+    const size_t at = (static_cast<size_t>(b) * T + t) * D + d;
+    float cur[VEC], acc[VEC];
+    Vec<IO, VEC>::load(xin + at, cur);
+    const uint32_t f = tok ? tok[static_cast<size_t>(b) * T + t] : 0u;
+    const int reach = 3 - static_cast<int>(f & TOK_CUT_MASK);  // taps with lag <= reach stay inside the document
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float a = fmaf(wt[3][v], cur[v], bs[v]);
+      if (reach >= 1) a = fmaf(wt[2][v], hist[0][v], a);
+      if (reach >= 2) a = fmaf(wt[1][v], hist[1][v], a);
+      if (reach >= 3) a = fmaf(wt[0][v], hist[2][v], a);
+      acc[v] = (f & TOK_INACTIVE) ? 0.0f : a;
+    }
+    Vec<IO, VEC>::store(out + at, acc);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      hist[2][v] = hist[1][v];
+      hist[1][v] = hist[0][v];
+      hist[0][v] = cur[v];
+    }
+  }
+}
+
+// Next conv state: the last three inputs of the active prefix of each row (older
+// entries come from the previous state); entries older than the last token flagged
+// ZERO_HISTORY are zero.  One block per (channel slab, row).
+template <typename IO>
+__global__ void conv_state_kernel(const IO* __restrict__ xin, const IO* __restrict__ state,
+                                  const uint8_t* __restrict__ tok, IO* __restrict__ new_state, int T, int D) {
+  __shared__ int s_len, s_zero;
+  const int b = blockIdx.y;
+  if (threadIdx.x == 0) { s_len = tok ? 0 : T; s_zero = -4; }
+  __syncthreads();
+  if (tok) {
+    int len = 0, zero_at = -4;
+    for (int t = threadIdx.x; t < T; t += blockDim.x) {
+      const uint32_t f = tok[static_cast<size_t>(b) * T + t];
+      if (!(f & TOK_INACTIVE)) {
+        len = max(len, t + 1);
+        if (f & TOK_ZERO_HISTORY) zero_at = max(zero_at, t);
+      }
+    }
+    atomicMax(&s_len, len);
+    atomicMax(&s_zero, zero_at);
+    __syncthreads();
+  }
+  const int len = s_len, zero_at = s_zero;
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+#pragma unroll
+  for (int slot = 0; slot < CONV_TAPS - 1; ++slot) {
+    const int t = len - (CONV_TAPS - 1) + slot;
+    float v = 0.0f;
+    if (t >= zero_at) {
+      if (t >= 0) v = Pack<IO>::to_float(xin[(static_cast<size_t>(b) * T + t) * D + d]);
+      else if (state) v = Pack<IO>::to_float(state[(static_cast<size_t>(b) * (CONV_TAPS - 1) + (CONV_TAPS - 1 + t)) * D + d]);
+    }
+    new_state[(static_cast<size_t>(b) * (CONV_TAPS - 1) + slot) * D + d] = Pack<IO>::from_float(v);
+  }
+}
+
+// ---------------------------------------------------------------- backward
+// dx_in[t] = sum_lag w[3-lag] * dconv[t+lag] * [tap (t+lag, lag) inside its document]
+// d_w[3-lag] += dconv[t] * xin[t-lag] (same mask), d_b += dconv[t].
+// Block = 8 runs x 32 channel vectors; the 8 runs are folded in shared memory so one
+// partial row [5, D] is written per (row, 8*RUN time-steps).
+template <typename IO, int VEC, int RUN>
+__global__ void __launch_bounds__(256) conv_bwd_kernel(const IO* __restrict__ dconv, const IO* __restrict__ xin,
+                                                       const float* __restrict__ w, const IO* __restrict__ state,
+                                                       const uint8_t* __restrict__ tok, IO* __restrict__ dxin,
+                                                       IO* __restrict__ dstate, float* __restrict__ part, int B, int T,
+                                                       int D) {
+  constexpr int RUNS_PER_BLOCK = 8, VECS_PER_BLOCK = 32;
+  __shared__ float red[RUNS_PER_BLOCK][5][VECS_PER_BLOCK * VEC + 1];
+  const int nvec = D / VEC;
+  const int vslot = threadIdx.x % VECS_PER_BLOCK;
+  const int rslot = threadIdx.x / VECS_PER_BLOCK;
+  const int dv = blockIdx.x * VECS_PER_BLOCK + vslot;
+  const int run = blockIdx.y * RUNS_PER_BLOCK + rslot;
+  const int b = blockIdx.z;
+  const bool live = dv < nvec;
+  const int d = dv * VEC;
+  const int t_begin = run * RUN;
+  const int t_end = min(T, t_begin + RUN);
+
+  float gw[5][VEC];
+#pragma unroll
+  for (int k = 0; k < 5; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) gw[k][v] = 0.0f;
+
+  if (live && t_begin < T) {
+    float wt[CONV_TAPS][VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+#pragma unroll
+      for (int k = 0; k < CONV_TAPS; ++k) wt[k][v] = w[(d + v) * CONV_TAPS + k];
+
+    auto load_in = [&](int t, float (&v)[VEC]) {
+      if (t >= 0) Vec<IO, VEC>::load(xin + (static_cast<size_t>(b) * T + t) * D + d, v);
+      else if (state) Vec<IO, VEC>::load(state + (static_cast<size_t>(b) * (CONV_TAPS - 1) + (CONV_TAPS - 1 + t)) * D + d, v);
+      else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = 0.0f;
+      }
+    };
+    // Masked upstream gradient of the token at time t (zero outside [0, T) and on padding)
+    // together with how far back its taps reach.
+    auto load_grad = [&](int t, float (&g)[VEC], int& reach) {
+      reach = -1;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) g[k] = 0.0f;
+      if (t < 0 || t >= T) return;
+      const uint32_t f = tok ? tok[static_cast<size_t>(b) * T + t] : 0u;
+      if (f & TOK_INACTIVE) return;
+      reach = 3 - static_cast<int>(f & TOK_CUT_MASK);
+      Vec<IO, VEC>::load(dconv + (static_cast<size_t>(b) * T + t) * D + d, g);
+    };
+
+    // Sliding windows: xin at t-1..t-3 (for d_w) and dconv at t+1..t+3 (for dx_in).
+    float hist[3][VEC];
+#pragma unroll
+    for (int l = 1; l <= 3; ++l) load_in(t_begin - l, hist[l - 1]);
+    float g0[VEC], g1[VEC], g2[VEC], g3[VEC];
+    int r0, r1, r2, r3;
+    load_grad(t_begin, g0, r0);
+    load_grad(t_begin + 1, g1, r1);
+    load_grad(t_begin + 2, g2, r2);
+
+    // History rows before t = 0 receive gradient only from the first run of a row.
+    if (dstate && t_begin == 0) {
+      float e1[VEC], e2[VEC];
+      int q1, q2;
+      load_grad(1, e1, q1);
+      load_grad(2, e2, q2);
+#pragma unroll
+      for (int slot = 0; slot < 3; ++slot) {  // slot holds time slot-3
+        float acc[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          float a = 0.0f;
+          // token at time u reads this row with lag u - (slot-3)
+          if (3 - slot <= r0) a = fmaf(wt[slot][v], g0[v], a);
+          if (slot >= 1 && 4 - slot <= q1) a = fmaf(wt[slot >= 1 ? slot - 1 : 0][v], e1[v], a);
+          if (slot >= 2 && 5 - slot <= q2) a = fmaf(wt[slot >= 2 ? slot - 2 : 0][v], e2[v], a);
+          acc[v] = a;
+        }
+        Vec<IO, VEC>::store(dstate + (static_cast<size_t>(b) * 3 + slot) * D + d, acc);
+      }
+    }
+
+    for (int t = t_begin; t < t_end; ++t) {
+      float cur[VEC], dx[VEC];
+      load_in(t, cur);
+      load_grad(t + 3, g3, r3);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        float a = 0.0f;
+        if (r0 >= 0) a = wt[3][v] * g0[v];
+        if (r1 >= 1) a = fmaf(wt[2][v], g1[v], a);
+        if (r2 >= 2) a = fmaf(wt[1][v], g2[v], a);
+        if (r3 >= 3) a = fmaf(wt[0][v], g3[v], a);
+        dx[v] = a;
+        gw[4][v] += g0[v];
+        gw[3][v] = fmaf(g0[v], cur[v], gw[3][v]);
+        if (r0 >= 1) gw[2][v] = fmaf(g0[v], hist[0][v], gw[2][v]);
+        if (r0 >= 2) gw[1][v] = fmaf(g0[v], hist[1][v], gw[1][v]);
+        if (r0 >= 3) gw[0][v] = fmaf(g0[v], hist[2][v], gw[0][v]);
+      }
+      Vec<IO, VEC>::store(dxin + (static_cast<size_t>(b) * T + t) * D + d, dx);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        hist[2][v] = hist[1][v]; hist[1][v] = hist[0][v]; hist[0][v] = cur[v];
+        g0[v] = g1[v]; g1[v] = g2[v]; g2[v] = g3[v];
+      }
+      r0 = r1; r1 = r2; r2 = r3;
+    }
+  }
+
+#pragma unroll
+  for (int k = 0; k < 5; ++k)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) red[rslot][k][vslot * VEC + v] = gw[k][v];
+  __syncthreads();
+  // Fold the 8 runs in index order; thread -> (k, channel) pairs of this block.
+  const int nblk_t = gridDim.y;
+  float* row = part + (static_cast<size_t>(b) * nblk_t + blockIdx.y) * 5 * D;
+  for (int idx = threadIdx.x; idx < 5 * VECS_PER_BLOCK * VEC; idx += blockDim.x) {
+    const int k = idx / (VECS_PER_BLOCK * VEC);
+    const int cc = idx % (VECS_PER_BLOCK * VEC);
+    const int dd = blockIdx.x * VECS_PER_BLOCK * VEC + cc;
+    if (dd >= D) continue;
+    float acc = 0.0f;
+#pragma unroll
+    for (int r = 0; r < RUNS_PER_BLOCK; ++r) acc += red[r][k][cc];
+    row[static_cast<size_t>(k) * D + dd] = acc;
+  }
+}
+
+// d_w[d, k] = sum over partial rows; d_b[d] likewise.  Rows are added in index order.
+__global__ void conv_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, float* __restrict__ db,
+                                       int rows, int D) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= 5 * D) return;
+  const int k = idx / D, d = idx % D;
+  float acc = 0.0f;
+  for (int r = 0; r < rows; ++r) acc += part[(static_cast<size_t>(r) * 5 + k) * D + d];
+  if (k < 4) dw[d * CONV_TAPS + k] = acc;
+  else if (db) db[d] = acc;
+}
+
+// ---------------------------------------------------------------- decode
+template <typename IO, int VEC>
+__global__ void __launch_bounds__(256) decode_conv_kernel(const IO* __restrict__ xin, const float* __restrict__ w,
+                                                          const float* __restrict__ bias, IO* __restrict__ state,
+                                                          const uint8_t* __restrict__ tok, IO* __restrict__ out, int B,
+                                                          int D) {
+  const int nvec = D / VEC;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * nvec) return;
+  const int b = static_cast<int>(gid / nvec);
+  const int d = static_cast<int>(gid % nvec) * VEC;
+  const uint32_t f = tok ? tok[b] : 0u;
+  float cur[VEC], s0[VEC], s1[VEC], s2[VEC], acc[VEC];
+  IO* st = state + static_cast<size_t>(b) * 3 * D + d;
+  Vec<IO, VEC>::load(xin + static_cast<size_t>(b) * D + d, cur);
+  Vec<IO, VEC>::load(st, s0);
+  Vec<IO, VEC>::load(st + D, s1);
+  Vec<IO, VEC>::load(st + 2 * static_cast<size_t>(D), s2);
+  const int reach = 3 - static_cast<int>(f & TOK_CUT_MASK);
+  const bool inactive = (f & TOK_INACTIVE) != 0;
+  const bool wipe = (f & TOK_ZERO_HISTORY) != 0;
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    float a = fmaf(w[(d + v) * CONV_TAPS + 3], cur[v], bias ? bias[d + v] : 0.0f);
+    if (reach >= 1) a = fmaf(w[(d + v) * CONV_TAPS + 2], s2[v], a);
+    if (reach >= 2) a = fmaf(w[(d + v) * CONV_TAPS + 1], s1[v], a);
+    if (reach >= 3) a = fmaf(w[(d + v) * CONV_TAPS + 0], s0[v], a);
+    acc[v] = inactive ? 0.0f : a;
+    if (wipe) { s1[v] = 0.0f; s2[v] = 0.0f; }
+  }
+  Vec<IO, VEC>::store(out + static_cast<size_t>(b) * D + d, acc);
+  if (!inactive) {
+    Vec<IO, VEC>::store(st, s1);
+    Vec<IO, VEC>::store(st + D, s2);
+    Vec<IO, VEC>::store(st + 2 * static_cast<size_t>(D), cur);
+  }
+}
+
+template <typename IO, int VEC>
+__global__ void __launch_bounds__(256) decode_step_kernel(const IO* __restrict__ x, const IO* __restrict__ ur,
+                                                          const IO* __restrict__ ui, const float* __restrict__ lambda,
+                                                          float* __restrict__ h, const uint8_t* __restrict__ tok,
+                                                          IO* __restrict__ y, int B, int D, float c) {
+  const int nvec = D / VEC;
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * nvec) return;
+  const int b = static_cast<int>(gid / nvec);
+  const int d = static_cast<int>(gid % nvec) * VEC;
+  const size_t at = static_cast<size_t>(b) * D + d;
+  const uint32_t f = tok ? tok[b] : 0u;
+  float xv[VEC], rv[VEC], iv[VEC], hv[VEC], yv[VEC];
+  Vec<IO, VEC>::load(x + at, xv);
+  Vec<IO, VEC>::load(ur + at, rv);
+  Vec<IO, VEC>::load(ui + at, iv);
+#pragma unroll
+  for (int v = 0; v < VEC; v += 4) {
+    if (VEC == 1) { hv[0] = h[at]; }
+    else {
+      const float4 t4 = *reinterpret_cast<const float4*>(h + at + v);
+      hv[v] = t4.x; hv[(v + 1) % VEC] = t4.y; hv[(v + 2) % VEC] = t4.z; hv[(v + 3) % VEC] = t4.w;
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    const float lam = lambda[d + v];
+    const float ls = lam >= 0.0f ? -log1pf(__expf(-lam)) : lam - log1pf(__expf(lam));
+    float r, i;
+    sigmoid_pair(rv[v], iv[v], r, i);
+    const float em = expm1_nonpos<false>(r * (c * ls));
+    float a = 1.0f + em;
+    float bdrive = sqrt_approx(fmaxf(-em * (2.0f + em), 0.0f)) * i * xv[v];
+    if (f & TOK_RESET) { a = 0.0f; bdrive = i * xv[v]; }
+    if (f & TOK_INACTIVE) { a = 1.0f; bdrive = 0.0f; }
+    hv[v] = fmaf(a, hv[v], bdrive);
+    yv[v] = hv[v];
+  }
+  Vec<IO, VEC>::store(y + at, yv);
+#pragma unroll
+  for (int v = 0; v < VEC; v += 4) {
+    if (VEC == 1) { h[at] = hv[0]; }
+    else *reinterpret_cast<float4*>(h + at + v) = make_float4(hv[v], hv[(v + 1) % VEC], hv[(v + 2) % VEC], hv[(v + 3) % VEC]);
+  }
+}
+
+// ---------------------------------------------------------------- launchers
+constexpr int CONV_RUN = 32;
+
+template <typename IO>
+static cudaError_t conv_fwd_t(const ConvArgs& a, cudaStream_t s) {
+  constexpr int V = vec_width<IO>();
+  const bool vec_ok = a.vector_ok;
+  const int nvec = vec_ok ? a.D / V : a.D;
+  const int nrun = (a.T + CONV_RUN - 1) / CONV_RUN;
+  const long long total = static_cast<long long>(a.B) * nrun * nvec;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  const IO* xin = static_cast<const IO*>(a.x_in);
+  const IO* st = static_cast<const IO*>(a.state);
+  IO* out = static_cast<IO*>(a.out);
+  if (vec_ok) conv_fwd_kernel<IO, V, CONV_RUN><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.T, a.D);
+  else conv_fwd_kernel<IO, 1, CONV_RUN><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.T, a.D);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || !a.new_state) return e;
+  dim3 grid((a.D + 255) / 256, a.B);
+  conv_state_kernel<IO><<<grid, 256, 0, s>>>(xin, st, a.tok, static_cast<IO*>(a.new_state), a.T, a.D);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_conv_fwd(bool bf16, const ConvArgs& a, cudaStream_t s) {
+  return bf16 ? conv_fwd_t<__nv_bfloat16>(a, s) : conv_fwd_t<float>(a, s);
+}
+
+int conv_bwd_partial_rows(int B, int T) { return B * ((T + 8 * CONV_RUN - 1) / (8 * CONV_RUN)); }
+
+template <typename IO>
+static cudaError_t conv_bwd_t(const ConvBwdArgs& a, cudaStream_t s) {
+  constexpr int V = vec_width<IO>();
+  const bool vec_ok = a.vector_ok;
+  const int nvec = vec_ok ? a.D / V : a.D;
+  const int tblocks = (a.T + 8 * CONV_RUN - 1) / (8 * CONV_RUN);
+  dim3 grid((nvec + 31) / 32, tblocks, a.B);
+  const IO* dc = static_cast<const IO*>(a.d_conv);
+  const IO* xin = static_cast<const IO*>(a.x_in);
+  const IO* st = static_cast<const IO*>(a.state);
+  IO* dx = static_cast<IO*>(a.dx_in);
+  IO* ds = static_cast<IO*>(a.d_state);
+  if (vec_ok) conv_bwd_kernel<IO, V, CONV_RUN><<<grid, 256, 0, s>>>(dc, xin, a.w, st, a.tok, dx, ds, a.part, a.B, a.T, a.D);
+  else conv_bwd_kernel<IO, 1, CONV_RUN><<<grid, 256, 0, s>>>(dc, xin, a.w, st, a.tok, dx, ds, a.part, a.B, a.T, a.D);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  conv_bwd_reduce_kernel<<<(5 * a.D + 255) / 256, 256, 0, s>>>(a.part, a.d_w, a.d_b, a.B * tblocks, a.D);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_conv_bwd(bool bf16, const ConvBwdArgs& a, cudaStream_t s) {
+  return bf16 ? conv_bwd_t<__nv_bfloat16>(a, s) : conv_bwd_t<float>(a, s);
+}
+
+template <typename IO>
+static cudaError_t decode_conv_t(const ConvArgs& a, cudaStream_t s) {
+  constexpr int V = vec_width<IO>();
+  const int nvec = a.vector_ok ? a.D / V : a.D;
+  const long long total = static_cast<long long>(a.B) * nvec;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  const IO* xin = static_cast<const IO*>(a.x_in);
+  IO* st = static_cast<IO*>(a.new_state);
+  IO* out = static_cast<IO*>(a.out);
+  if (a.vector_ok) decode_conv_kernel<IO, V><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.D);
+  else decode_conv_kernel<IO, 1><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.D);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_decode_conv(bool bf16, const ConvArgs& a, cudaStream_t s) {
+  return bf16 ? decode_conv_t<__nv_bfloat16>(a, s) : decode_conv_t<float>(a, s);
+}
+
+template <typename IO>
+static cudaError_t decode_step_t(const DecodeArgs& a, cudaStream_t s) {
+  constexpr int V = vec_width<IO>();
+  const int nvec = a.vector_ok ? a.D / V : a.D;
+  const long long total = static_cast<long long>(a.B) * nvec;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  const IO* x = static_cast<const IO*>(a.x);
+  const IO* ur = static_cast<const IO*>(a.ur);
+  const IO* ui = static_cast<const IO*>(a.ui);
+  IO* y = static_cast<IO*>(a.y);
+  if (a.vector_ok) decode_step_kernel<IO, V><<<blocks, 256, 0, s>>>(x, ur, ui, a.lambda, a.h, a.tok, y, a.B, a.D, a.c);
+  else decode_step_kernel<IO, 1><<<blocks, 256, 0, s>>>(x, ur, ui, a.lambda, a.h, a.tok, y, a.B, a.D, a.c);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_decode_step(bool bf16, const DecodeArgs& a, cudaStream_t s) {
+  return bf16 ? decode_step_t<__nv_bfloat16>(a, s) : decode_step_t<float>(a, s);
+}
+
+}  // namespace rglru

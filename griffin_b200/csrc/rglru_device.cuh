@@ -1,0 +1,193 @@
+// Device-side building blocks shared by the RG-LRU kernels: PTX wrappers for
+// mbarrier / TMA (cp.async.bulk.tensor), fast-math primitives, the gate
+// arithmetic, and packed I/O conversion.  sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rglru {
+
+// ---------------------------------------------------------------- geometry
+// One CTA owns CH adjacent channels of one batch row for the whole sequence.
+// Its 256 threads form a grid of LANES time-lanes x NCV channel-vectors; a
+// thread handles CV adjacent channels over TS consecutive time-steps of each
+// chunk, so one chunk covers LANES*TS time-steps.
+constexpr int CH = 64;
+constexpr int CV = 4;
+constexpr int NCV = CH / CV;      // 16
+constexpr int LANES = 16;
+constexpr int NT = LANES * NCV;   // 256
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float SLOPE_CAP = 1000.0f;  // bound on d sqrt / d gamma^2
+// Channels whose c*logsigmoid(Lambda) is above this use a polynomial expm1.
+constexpr float POLY_RANGE = -0.25f;
+
+// Codes written to the device status word.
+constexpr int DEV_TIMEOUT_LOAD = 1;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      " selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about two seconds of SM clock and reports false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int spin = 0; spin < 256; ++spin)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - start > 4000000000LL) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const void* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const void* map, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_map(const void* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// ---------------------------------------------------------------- fast math
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rsqrt_approx(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Both gate sigmoids with one reciprocal: 1/((1+er)(1+ei)) scaled by the other
+// factor.  The exponent clamp keeps the product finite (sigmoid saturates at
+// 2^-60, far below fp32 resolution of anything it multiplies).
+__device__ __forceinline__ void sigmoid_pair(float ur, float ui, float& r, float& i) {
+  const float er = ex2_approx(fminf(-LOG2E * ur, 60.0f));
+  const float ei = ex2_approx(fminf(-LOG2E * ui, 60.0f));
+  const float dr = 1.0f + er;
+  const float di = 1.0f + ei;
+  const float inv = rcp_approx(dr * di);
+  r = inv * di;
+  i = inv * dr;
+}
+
+// expm1(z) for z <= 0 with full relative accuracy.
+//   POLY: z is known to lie in [POLY_RANGE, 0]; degree-6 Taylor, truncation < 5e-8 relative.
+//   otherwise: the polynomial where it is valid, 2^(z log2 e) - 1 elsewhere.
+template <bool POLY>
+__device__ __forceinline__ float expm1_nonpos(float z) {
+  float t = fmaf(z, 1.0f / 720.0f, 1.0f / 120.0f);
+  t = fmaf(t, z, 1.0f / 24.0f);
+  t = fmaf(t, z, 1.0f / 6.0f);
+  t = fmaf(t, z, 0.5f);
+  const float poly = fmaf(z * z, t, z);
+  if (POLY) return poly;
+  const float wide = ex2_approx(z * LOG2E) - 1.0f;
+  return z > POLY_RANGE ? poly : wide;
+}
+
+// ---------------------------------------------------------------- packed I/O
+template <typename IO>
+struct Pack;
+
+template <>
+struct Pack<float> {
+  static constexpr int BYTES = 16;
+  using Raw = float4;
+  static __device__ __forceinline__ Raw load(const void* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float (&v)[4]) {
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
+  static __device__ __forceinline__ void store(void* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+  static __device__ __forceinline__ float to_float(float x) { return x; }
+  static __device__ __forceinline__ float from_float(float x) { return x; }
+};
+
+template <>
+struct Pack<__nv_bfloat16> {
+  static constexpr int BYTES = 8;
+  using Raw = uint2;
+  static __device__ __forceinline__ Raw load(const void* p) { return *reinterpret_cast<const uint2*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float (&v)[4]) {
+    v[0] = __uint_as_float(r.x << 16);
+    v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16);
+    v[3] = __uint_as_float(r.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(void* p, const float (&v)[4]) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+};
+
+// Token flag bits (mirrors include/rglru_b200.h).
+constexpr uint32_t TOK_CUT_MASK = 0x03u;
+constexpr uint32_t TOK_RESET = 0x04u;
+constexpr uint32_t TOK_INACTIVE = 0x08u;
+constexpr uint32_t TOK_ZERO_HISTORY = 0x10u;
+
+}  // namespace rglru

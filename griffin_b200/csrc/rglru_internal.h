@@ -1,0 +1,134 @@
+// Host-side declarations shared between the C ABI layer and the kernel files.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace rglru {
+
+// Time-steps between saved recurrent states == chunk length of the backward kernel.
+constexpr int SAVE_EVERY = 64;
+
+struct ScanFwdArgs {
+  const void* x;
+  const void* ur;
+  const void* ui;
+  void* y;
+  const float* lambda;
+  const float* h0;
+  const uint8_t* tok;
+  float* h_last;
+  float* states;  // [B, ceil(T/SAVE_EVERY), D] or nullptr
+  int B, T, D;
+  float c;
+  int* status;
+};
+
+struct ScanBwdArgs {
+  const void* dy;
+  const void* x;
+  const void* ur;
+  const void* ui;
+  void* dx;
+  void* dur;
+  void* dui;
+  const float* lambda;
+  const float* h0;
+  const float* dh_last;
+  const uint8_t* tok;
+  const float* states;  // written by the forward kernel
+  float* dlam_part;     // [B, D] per-row partial sums of dl * r
+  float* dlambda;       // [D]
+  float* dh0;           // [B, D] or nullptr
+  int B, T, D;
+  float c;
+  int* status;
+};
+
+struct FwdMaps {
+  CUtensorMap x, ur, ui, y;
+};
+struct BwdMaps {
+  CUtensorMap dy, x, ur, ui, dx, dur, dui;
+};
+
+struct RawFwdMaps {
+  CUtensorMap drive, decay, out;
+};
+struct RawBwdMaps {
+  CUtensorMap dout, decay, out, ddecay, ddrive;
+};
+struct RawScanArgs {
+  const float* dout;   // backward only
+  const float* decay;
+  const float* drive;  // forward only
+  const float* h0;
+  const float* out_in;  // backward: saved forward output
+  float* out;           // forward output
+  float* ddecay;
+  float* ddrive;
+  float* dh0;
+  int B, T, D;
+  int* status;
+};
+
+struct ConvArgs {
+  const void* x_in;
+  const float* w;
+  const float* bias;
+  const void* state;  // history before t = 0 (forward) or nullptr
+  const uint8_t* tok;
+  void* out;
+  void* new_state;  // decode: the in/out state
+  int B, T, D;
+  bool vector_ok;   // D and all pointers allow 16-byte accesses
+};
+struct ConvBwdArgs {
+  const void* d_conv;
+  const void* x_in;
+  const float* w;
+  const void* state;
+  const uint8_t* tok;
+  void* dx_in;
+  float* d_w;
+  float* d_b;
+  void* d_state;
+  float* part;
+  int B, T, D;
+  bool vector_ok;
+};
+struct DecodeArgs {
+  const void* x;
+  const void* ur;
+  const void* ui;
+  const float* lambda;
+  float* h;
+  const uint8_t* tok;
+  void* y;
+  int B, D;
+  float c;
+  bool vector_ok;
+};
+
+cudaError_t launch_raw_fwd(bool use_tma, const RawFwdMaps& maps, const RawScanArgs& args, cudaStream_t s);
+cudaError_t launch_raw_bwd(bool use_tma, const RawBwdMaps& maps, const RawScanArgs& args, cudaStream_t s);
+int raw_box_rows();
+cudaError_t launch_conv_fwd(bool bf16, const ConvArgs& a, cudaStream_t s);
+cudaError_t launch_conv_bwd(bool bf16, const ConvBwdArgs& a, cudaStream_t s);
+int conv_bwd_partial_rows(int B, int T);
+cudaError_t launch_decode_conv(bool bf16, const ConvArgs& a, cudaStream_t s);
+cudaError_t launch_decode_step(bool bf16, const DecodeArgs& a, cudaStream_t s);
+
+// use_tma == false selects the bounds-checked plain-load staging path that accepts any D.
+cudaError_t launch_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
+cudaError_t launch_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
+
+// Box extents (time rows) the tensor maps must be encoded with.
+int scan_fwd_box_rows(bool bf16);
+int scan_bwd_box_rows(bool bf16);
+
+int* device_status_word();  // device address of the status word of the current device
+
+}  // namespace rglru

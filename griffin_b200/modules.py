@@ -1,0 +1,265 @@
+"""Host-side mirror of the reference's RG-LRU modules, backed only by the CUDA kernels.
+
+``RG_LRU``, ``RecurrentBlock``, ``BlockDiagonalLinear`` and ``RecurrentBlockCache``
+keep the constructor arguments, forward signatures, parameter names/shapes and
+error behaviour of the reference (griffin/griffin.py:26-33, 129-154, 157-306,
+361-529) so reference checkpoints load unchanged.  The one difference is the
+scan backend: ``scan_mode="cuda"`` (also what ``"auto"`` resolves to here) runs
+the hand-written sm_100a kernels; the reference's "sequential", "associative" and
+"fused" (Triton) backends are not part of this package and are rejected, and
+there is no CPU fallback -- a CPU tensor raises ``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Literal, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+
+from . import _lib, ops
+
+ScanMode = Literal["auto", "cuda"]
+_REFERENCE_ONLY_MODES = ("sequential", "associative", "fused")
+
+
+def _check_scan_mode(scan_mode: str) -> str:
+    if scan_mode in ("auto", "cuda"):
+        return "cuda"
+    if scan_mode in _REFERENCE_ONLY_MODES:
+        raise ValueError(
+            f"scan_mode={scan_mode!r} is a backend of the reference implementation; this package provides only "
+            "scan_mode='cuda' (the sm_100a kernels)")
+    raise ValueError(f"Unknown RG-LRU scan mode: {scan_mode}")
+
+
+@dataclass
+class RecurrentBlockCache:
+    """State needed to continue a recurrent block on a later chunk (griffin/griffin.py:26-33)."""
+
+    rnn_state: Tensor          # [B, D] fp32
+    conv_state: Tensor         # [B, 3, D] activation dtype
+    segment_position: Tensor   # [B] int64, position of the last real token
+
+
+def _largest_block_count(width: int, requested: int) -> int:
+    if width <= 0 or requested <= 0:
+        raise ValueError("width and requested_blocks must be positive")
+    count = min(width, requested)
+    while width % count:
+        count -= 1
+    return count
+
+
+class BlockDiagonalLinear(nn.Module):
+    """Gate projection with independent diagonal blocks (griffin/griffin.py:129-154).
+
+    Stays an ordinary batched GEMM; only its output feeds the CUDA kernels.
+    ``weight`` is [blocks, out, in], ``bias`` [blocks, out].
+    """
+
+    def __init__(self, width: int, num_blocks: int = 16):
+        super().__init__()
+        self.width = width
+        self.num_blocks = _largest_block_count(width, num_blocks)
+        self.block_width = width // self.num_blocks
+        self.weight = nn.Parameter(torch.empty(self.num_blocks, self.block_width, self.block_width))
+        self.bias = nn.Parameter(torch.empty(self.num_blocks, self.block_width))
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.normal_(self.weight, mean=0.0, std=math.sqrt(1.0 / self.block_width))
+        nn.init.zeros_(self.bias)
+
+    def forward(self, x: Tensor) -> Tensor:
+        lead = x.shape[:-1]
+        rows = x.reshape(-1, self.num_blocks, self.block_width).transpose(0, 1)   # [G, N, in]
+        out = torch.baddbmm(self.bias[:, None, :], rows, self.weight.transpose(1, 2))  # [G, N, out]
+        return out.transpose(0, 1).reshape(*lead, self.width)
+
+
+def token_flags(batch: int, steps: int, device, *, reset: Optional[Tensor] = None, active: Optional[Tensor] = None,
+                segment_pos: Optional[Tensor] = None, padded: Optional[Tensor] = None) -> Optional[Tensor]:
+    """Pack the per-token masks into the flag byte the kernels read ([B, T] uint8), or None if all are absent."""
+    if reset is None and active is None and segment_pos is None:
+        return None
+    flags = torch.zeros(batch, steps, device=device, dtype=torch.uint8)
+    if segment_pos is not None:
+        cut = (3 - segment_pos.clamp(min=0, max=3)).to(torch.uint8)
+        flags = flags | cut
+    if reset is not None:
+        flags = flags | (reset.to(torch.uint8) * _lib.TOK_RESET)
+    if active is not None:
+        flags = flags | ((~active).to(torch.uint8) * _lib.TOK_INACTIVE)
+    if padded is not None and segment_pos is not None and active is not None:
+        wipe = (segment_pos == 0) & active & padded
+        flags = flags | (wipe.to(torch.uint8) * _lib.TOK_ZERO_HISTORY)
+    return flags
+
+
+class RG_LRU(nn.Module):
+    """Real-gated linear recurrent unit on the CUDA kernels (reference: griffin/griffin.py:157-306)."""
+
+    def __init__(self, rnn_width: int, c: float = 8.0, gate_blocks: int = 16, scan_mode: str = "cuda"):
+        super().__init__()
+        self.rnn_width = rnn_width
+        self.c = c
+        self.scan_mode = _check_scan_mode(scan_mode)
+        self.recurrence_gate = BlockDiagonalLinear(rnn_width, gate_blocks)
+        self.input_gate = BlockDiagonalLinear(rnn_width, gate_blocks)
+        self.Lambda = nn.Parameter(torch.empty(rnn_width))
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        """sigmoid(Lambda)^c uniform in [0.9, 0.999] (griffin/griffin.py:179-188)."""
+        self.recurrence_gate.reset_parameters()
+        self.input_gate.reset_parameters()
+        with torch.no_grad():
+            target = torch.empty_like(self.Lambda).uniform_(0.9, 0.999)
+            self.Lambda.copy_(torch.logit(target.pow(1.0 / self.c)))
+
+    def forward(self, xt: Tensor, ht_minus_1: Optional[Tensor] = None, *, reset_mask: Optional[Tensor] = None,
+                active_mask: Optional[Tensor] = None, return_state: bool = False, _flags: Optional[Tensor] = None):
+        if xt.dim() != 3:
+            raise ValueError(f"RG_LRU expects [batch, sequence, width], got {tuple(xt.shape)}")
+        batch, steps, width = xt.shape
+        if width != self.rnn_width:
+            raise ValueError(f"Expected width {self.rnn_width}, got {width}")
+        if reset_mask is not None:
+            if reset_mask.shape != (batch, steps):
+                raise ValueError(f"reset_mask must have shape ({batch}, {steps}), got {tuple(reset_mask.shape)}")
+            reset_mask = reset_mask.to(device=xt.device, dtype=torch.bool)
+        if active_mask is not None:
+            if active_mask.shape != (batch, steps):
+                raise ValueError(f"active_mask must have shape ({batch}, {steps}), got {tuple(active_mask.shape)}")
+            active_mask = active_mask.to(device=xt.device, dtype=torch.bool)
+        if ht_minus_1 is not None:
+            if ht_minus_1.shape != (batch, width):
+                raise ValueError(f"ht_minus_1 must have shape ({batch}, {width}), got {tuple(ht_minus_1.shape)}")
+            ht_minus_1 = ht_minus_1.to(device=xt.device, dtype=torch.float32)
+        if not xt.is_cuda:
+            raise RuntimeError("scan_mode='cuda' requires CUDA tensors; there is no CPU fallback")
+        if xt.dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError(f"scan_mode='cuda' supports float32 and bfloat16 activations, got {xt.dtype}")
+
+        u_r = self.recurrence_gate(xt).to(xt.dtype)
+        u_i = self.input_gate(xt).to(xt.dtype)
+        flags = _flags if _flags is not None else token_flags(batch, steps, xt.device, reset=reset_mask, active=active_mask)
+        yt, h_last = ops.rglru(xt, u_r, u_i, self.Lambda, ht_minus_1, flags, self.c)
+        if return_state:
+            return yt, h_last
+        return yt
+
+
+def _positions(x: Tensor, segment_pos: Optional[Tensor], previous: Optional[Tensor], active: Optional[Tensor]) -> Tensor:
+    """Per-token position inside its document (behaviour of griffin/griffin.py:309-338)."""
+    batch, steps = x.shape[:2]
+    if steps == 0:
+        raise ValueError("Empty token sequences are not supported")
+    if segment_pos is not None:
+        if segment_pos.shape != (batch, steps):
+            raise ValueError(f"segment_pos must have shape ({batch}, {steps}), got {tuple(segment_pos.shape)}")
+        return segment_pos.to(device=x.device, dtype=torch.long)
+    if previous is None:
+        start = torch.full((batch, 1), -1, device=x.device, dtype=torch.long)
+    else:
+        if previous.shape != (batch,):
+            raise ValueError("Cached segment positions have an incompatible shape")
+        start = previous.to(device=x.device, dtype=torch.long)[:, None]
+    if active is None:
+        return start + torch.arange(1, steps + 1, device=x.device, dtype=torch.long)[None, :]
+    return start + active.to(torch.long).cumsum(dim=1)
+
+
+def _last_real_position(segment_pos: Tensor, active: Optional[Tensor], previous: Optional[Tensor]) -> Tensor:
+    """Position of each row's last non-padding token, without a host loop (griffin/griffin.py:341-358)."""
+    batch, steps = segment_pos.shape
+    if active is None:
+        return segment_pos[:, -1].clone()
+    index = torch.arange(1, steps + 1, device=segment_pos.device)[None, :] * active.to(torch.long)
+    last = index.max(dim=1).values                       # 0 when the row is all padding
+    picked = segment_pos.gather(1, (last - 1).clamp(min=0)[:, None])[:, 0]
+    if previous is None:
+        fallback = torch.full((batch,), -1, device=segment_pos.device, dtype=torch.long)
+    else:
+        fallback = previous.to(device=segment_pos.device, dtype=torch.long)
+    return torch.where(last > 0, picked, fallback)
+
+
+class RecurrentBlock(nn.Module):
+    """Causal conv + RG-LRU temporal-mixing block with cached decoding (griffin/griffin.py:361-529).
+
+    The two input projections, the GeLU branch and the output projection are ordinary
+    torch GEMMs; the conv, the RG-LRU and the single-token decode run on the CUDA kernels.
+    Padding (``active_mask``) must be right padding, which is what the model passes.
+    """
+
+    def __init__(self, input_dim: int, rnn_width: int, conv_kernel_size: int = 4, gate_blocks: int = 16,
+                 final_w_init_variance_scale: float = 1.0, scan_mode: str = "cuda"):
+        super().__init__()
+        if conv_kernel_size <= 0:
+            raise ValueError("conv_kernel_size must be positive")
+        if conv_kernel_size != 4:
+            raise ValueError("scan_mode='cuda' implements the temporal convolution for conv_kernel_size=4 only")
+        self.rnn_width = rnn_width
+        self.conv_kernel_size = conv_kernel_size
+        self.linear_x = nn.Linear(input_dim, rnn_width)
+        self.linear_y = nn.Linear(input_dim, rnn_width)
+        self.temporal_conv = nn.Conv1d(rnn_width, rnn_width, kernel_size=conv_kernel_size, padding=0, groups=rnn_width)
+        self.rg_lru = RG_LRU(rnn_width, gate_blocks=gate_blocks, scan_mode=scan_mode)
+        self.linear_out = nn.Linear(rnn_width, input_dim)
+        self.final_w_init_variance_scale = final_w_init_variance_scale
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        """Initialisation of griffin/griffin.py:393-407."""
+        nn.init.normal_(self.linear_x.weight, std=math.sqrt(1.0 / self.linear_x.in_features))
+        nn.init.normal_(self.linear_y.weight, std=math.sqrt(1.0 / self.linear_y.in_features))
+        nn.init.normal_(self.linear_out.weight, std=math.sqrt(self.final_w_init_variance_scale / self.linear_out.in_features))
+        nn.init.normal_(self.temporal_conv.weight, std=math.sqrt(0.01 / self.conv_kernel_size))
+        for bias in (self.linear_x.bias, self.linear_y.bias, self.linear_out.bias, self.temporal_conv.bias):
+            nn.init.zeros_(bias)
+
+    def forward(self, x: Tensor, cache: Optional[RecurrentBlockCache] = None, segment_pos: Optional[Tensor] = None, *,
+                active_mask: Optional[Tensor] = None, return_cache: bool = False):
+        if x.dim() != 3:
+            raise ValueError(f"RecurrentBlock expects [batch, sequence, width], got {tuple(x.shape)}")
+        batch, steps = x.shape[:2]
+        if active_mask is not None:
+            if active_mask.shape != (batch, steps):
+                raise ValueError("active_mask must match the input [batch, sequence] dimensions")
+            active_mask = active_mask.to(device=x.device, dtype=torch.bool)
+        previous = None if cache is None else cache.segment_position
+        plain = segment_pos is None and cache is None and active_mask is None
+        pos = _positions(x, segment_pos, previous, active_mask)
+
+        y_branch = F.gelu(self.linear_y(x), approximate="tanh")
+        x_in = self.linear_x(x)
+        conv_state = None if cache is None else cache.conv_state
+        if conv_state is not None and conv_state.shape != (batch, self.conv_kernel_size - 1, self.rnn_width):
+            raise ValueError("Recurrent convolution cache has an incompatible shape")
+
+        if plain:
+            # contiguous positions 0..T-1: only the first three tokens lose taps, token 0 is a reset
+            flags = torch.zeros(batch, steps, device=x.device, dtype=torch.uint8)
+            head = min(3, steps)
+            flags[:, :head] = torch.tensor([3, 2, 1][:head], device=x.device, dtype=torch.uint8)
+            flags[:, 0] |= _lib.TOK_RESET
+        else:
+            padded = None if active_mask is None else ~active_mask.all()
+            flags = token_flags(batch, steps, x.device, reset=pos == 0, active=active_mask, segment_pos=pos, padded=padded)
+
+        conv_w = self.temporal_conv.weight[:, 0, :]
+        x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags)
+        rnn_state = None if cache is None else cache.rnn_state
+        y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags)
+        out = self.linear_out(y * y_branch)
+        if active_mask is not None:
+            out = torch.where(active_mask[..., None], out, torch.zeros_like(out))
+        if return_cache:
+            return out, RecurrentBlockCache(new_rnn, new_conv, _last_real_position(pos, active_mask, previous))
+        return out

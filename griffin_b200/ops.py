@@ -1,0 +1,322 @@
+"""Differentiable torch operators over the C ABI.
+
+Each operator is registered with ``torch.library`` (namespace ``griffin_b200``)
+with an explicit backward, so autograd, DDP and ``torch.compile`` see ordinary
+ops.  Tensors are passed to the library as raw device pointers on the current
+CUDA stream; nothing here computes on the CPU.
+
+* ``rglru``        -- gate epilogue + scan (griffin/griffin.py:237-286 of the reference)
+* ``linear_scan``  -- raw affine scan, the counterpart of ``fused_rglru_scan``
+                      (griffin/triton_scan.py:274-276)
+* ``causal_conv``  -- width-4 depthwise causal conv (griffin/griffin.py:474-510)
+* ``decode_conv`` / ``decode_step`` -- single-token updates (no autograd)
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+def _io_dtype(t: Tensor, what: str) -> int:
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"CUDA RG-LRU {what} expects float32 or bfloat16 activations, got {t.dtype}")
+    return _DTYPES[t.dtype]
+
+
+def _require_cuda(*tensors: Optional[Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("CUDA RG-LRU kernels require CUDA tensors (scan_mode='cuda' has no CPU path)")
+
+
+def _ptr(t: Optional[Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+# ----------------------------------------------------------------------------- rglru
+@torch.library.custom_op("griffin_b200::rglru_fwd", mutates_args=())
+def _rglru_fwd(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
+               c: float, save: bool) -> tuple[Tensor, Tensor, Tensor]:
+    lib = _lib.load()
+    _require_cuda(x, u_r, u_i, lam, h0, tok)
+    dt = _io_dtype(x, "forward")
+    B, T, D = x.shape
+    y = torch.empty_like(x)
+    h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
+    nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
+    ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        rc = lib.rglru_fwd(_ptr(x), _ptr(u_r), _ptr(u_i), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(y), _ptr(h_last),
+                           _ptr(ws) if save else None, nbytes, B, T, D, c, dt, _stream(x))
+    _lib.check(rc, "rglru_fwd")
+    return y, h_last, ws
+
+
+@_rglru_fwd.register_fake
+def _(x, u_r, u_i, lam, h0, tok, c, save):
+    B, T, D = x.shape
+    return (torch.empty_like(x), x.new_empty((B, D), dtype=torch.float32), x.new_empty((0,), dtype=torch.uint8))
+
+
+@torch.library.custom_op("griffin_b200::rglru_bwd", mutates_args=())
+def _rglru_bwd(dy: Tensor, dh_last: Optional[Tensor], x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor,
+               h0: Optional[Tensor], tok: Optional[Tensor], ws: Tensor, c: float, want_dh0: bool
+               ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    lib = _lib.load()
+    dt = _io_dtype(x, "backward")
+    B, T, D = x.shape
+    dx = torch.empty_like(x)
+    du_r = torch.empty_like(x)
+    du_i = torch.empty_like(x)
+    dlam = torch.empty(D, device=x.device, dtype=torch.float32)
+    dh0 = torch.empty((B, D) if want_dh0 else (0,), device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        rc = lib.rglru_bwd(_ptr(dy), _ptr(dh_last), _ptr(x), _ptr(u_r), _ptr(u_i), _ptr(lam), _ptr(h0), _ptr(tok),
+                           _ptr(ws), ws.numel(), _ptr(dx), _ptr(du_r), _ptr(du_i), _ptr(dlam),
+                           _ptr(dh0) if want_dh0 else None, B, T, D, c, dt, _stream(x))
+    _lib.check(rc, "rglru_bwd")
+    return dx, du_r, du_i, dlam, dh0
+
+
+@_rglru_bwd.register_fake
+def _(dy, dh_last, x, u_r, u_i, lam, h0, tok, ws, c, want_dh0):
+    B, T, D = x.shape
+    return (torch.empty_like(x), torch.empty_like(x), torch.empty_like(x), x.new_empty((D,), dtype=torch.float32),
+            x.new_empty((B, D) if want_dh0 else (0,), dtype=torch.float32))
+
+
+def _rglru_setup(ctx, inputs, output):
+    x, u_r, u_i, lam, h0, tok, c, save = inputs
+    _, _, ws = output
+    ctx.save_for_backward(x, u_r, u_i, lam, h0, tok, ws)
+    ctx.c = c
+    ctx.saved = save
+    ctx.want_dh0 = h0 is not None and ctx.needs_input_grad[4]
+
+
+def _rglru_backward(ctx, dy, dh_last, _dws):
+    if not ctx.saved:
+        raise RuntimeError("rglru was run with save=False (inference); its backward is unavailable")
+    x, u_r, u_i, lam, h0, tok, ws = ctx.saved_tensors
+    if dy is None:
+        dy = torch.zeros_like(x)
+    dy = dy.contiguous()
+    if dh_last is not None:
+        dh_last = dh_last.to(torch.float32).contiguous()
+    dx, du_r, du_i, dlam, dh0 = _rglru_bwd(dy, dh_last, x, u_r, u_i, lam, h0, tok, ws, ctx.c, ctx.want_dh0)
+    return dx, du_r, du_i, dlam, (dh0 if ctx.want_dh0 else None), None, None, None
+
+
+_rglru_fwd.register_autograd(_rglru_backward, setup_context=_rglru_setup)
+
+
+def rglru(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor] = None,
+          tok: Optional[Tensor] = None, c: float = 8.0) -> tuple[Tensor, Tensor]:
+    """y, h_last = RG-LRU(x | gate pre-activations u_r, u_i).  ``lam`` and ``h0`` are fp32."""
+    if x.dim() != 3 or u_r.shape != x.shape or u_i.shape != x.shape:
+        raise ValueError("x, u_r and u_i must share shape [batch, sequence, width]")
+    if u_r.dtype != x.dtype or u_i.dtype != x.dtype:
+        raise TypeError("x, u_r and u_i must share one dtype")
+    if lam.shape != (x.shape[2],):
+        raise ValueError("Lambda must have shape [width]")
+    save = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (x, u_r, u_i, lam, h0))
+    y, h_last, _ = _rglru_fwd(x.contiguous(), u_r.contiguous(), u_i.contiguous(),
+                              lam.to(torch.float32).contiguous(),
+                              None if h0 is None else h0.to(torch.float32).contiguous(),
+                              None if tok is None else tok.contiguous(), float(c), save)
+    return y, h_last
+
+
+# ----------------------------------------------------------------------------- raw affine scan
+@torch.library.custom_op("griffin_b200::linear_scan_fwd", mutates_args=())
+def _scan_fwd(decay: Tensor, drive: Tensor, h0: Tensor) -> Tensor:
+    lib = _lib.load()
+    B, T, D = decay.shape
+    out = torch.empty_like(drive)
+    with torch.cuda.device(decay.device):
+        rc = lib.rglru_linear_scan_fwd(_ptr(decay), _ptr(drive), _ptr(h0), _ptr(out), B, T, D, _stream(decay))
+    _lib.check(rc, "rglru_linear_scan_fwd")
+    return out
+
+
+@_scan_fwd.register_fake
+def _(decay, drive, h0):
+    return torch.empty_like(drive)
+
+
+@torch.library.custom_op("griffin_b200::linear_scan_bwd", mutates_args=())
+def _scan_bwd(d_out: Tensor, decay: Tensor, h0: Tensor, out: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+    lib = _lib.load()
+    B, T, D = decay.shape
+    d_decay = torch.empty_like(decay)
+    d_drive = torch.empty_like(decay)
+    d_h0 = torch.empty_like(h0)
+    with torch.cuda.device(decay.device):
+        rc = lib.rglru_linear_scan_bwd(_ptr(d_out), _ptr(decay), _ptr(h0), _ptr(out), _ptr(d_decay), _ptr(d_drive),
+                                       _ptr(d_h0), B, T, D, _stream(decay))
+    _lib.check(rc, "rglru_linear_scan_bwd")
+    return d_decay, d_drive, d_h0
+
+
+@_scan_bwd.register_fake
+def _(d_out, decay, h0, out):
+    return torch.empty_like(decay), torch.empty_like(decay), torch.empty_like(h0)
+
+
+def _scan_setup(ctx, inputs, output):
+    decay, _, h0 = inputs
+    ctx.save_for_backward(decay, h0, output)
+
+
+def _scan_backward(ctx, d_out):
+    decay, h0, out = ctx.saved_tensors
+    return _scan_bwd(d_out.contiguous(), decay, h0, out)
+
+
+_scan_fwd.register_autograd(_scan_backward, setup_context=_scan_setup)
+
+
+def linear_scan(decay: Tensor, current_input: Tensor, initial_state: Tensor) -> Tensor:
+    """h_t = decay_t * h_{t-1} + current_input_t; same contract as the reference's
+    ``fused_rglru_scan`` (griffin/triton_scan.py:211-224, 274-276)."""
+    if not decay.is_cuda or not current_input.is_cuda or not initial_state.is_cuda:
+        raise RuntimeError("CUDA linear scan requires CUDA tensors")
+    if decay.shape != current_input.shape or decay.dim() != 3:
+        raise ValueError("decay and current_input must share shape [batch, sequence, width]")
+    if initial_state.shape != (decay.size(0), decay.size(2)):
+        raise ValueError("initial_state must have shape [batch, width]")
+    if decay.dtype != torch.float32 or current_input.dtype != torch.float32:
+        raise TypeError("CUDA linear scan expects fp32 decay and normalized input")
+    if initial_state.dtype != torch.float32:
+        raise TypeError("CUDA linear scan expects fp32 recurrent state")
+    return _scan_fwd(decay.contiguous(), current_input.contiguous(), initial_state.contiguous())
+
+
+# ----------------------------------------------------------------------------- causal conv
+@torch.library.custom_op("griffin_b200::conv_fwd", mutates_args=())
+def _conv_fwd(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tensor], tok: Optional[Tensor]
+              ) -> tuple[Tensor, Tensor]:
+    lib = _lib.load()
+    _require_cuda(x_in, w, b, state, tok)
+    dt = _io_dtype(x_in, "conv")
+    B, T, D = x_in.shape
+    out = torch.empty_like(x_in)
+    new_state = torch.empty(B, 3, D, device=x_in.device, dtype=x_in.dtype)
+    with torch.cuda.device(x_in.device):
+        rc = lib.rglru_conv_fwd(_ptr(x_in), _ptr(w), _ptr(b), _ptr(state), _ptr(tok), _ptr(out), _ptr(new_state),
+                                B, T, D, dt, _stream(x_in))
+    _lib.check(rc, "rglru_conv_fwd")
+    return out, new_state
+
+
+@_conv_fwd.register_fake
+def _(x_in, w, b, state, tok):
+    B, T, D = x_in.shape
+    return torch.empty_like(x_in), x_in.new_empty((B, 3, D))
+
+
+@torch.library.custom_op("griffin_b200::conv_bwd", mutates_args=())
+def _conv_bwd(d_conv: Tensor, x_in: Tensor, w: Tensor, state: Optional[Tensor], tok: Optional[Tensor],
+              want_state: bool) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    lib = _lib.load()
+    dt = _io_dtype(x_in, "conv backward")
+    B, T, D = x_in.shape
+    dx = torch.empty_like(x_in)
+    d_w = torch.empty(D, 4, device=x_in.device, dtype=torch.float32)
+    d_b = torch.empty(D, device=x_in.device, dtype=torch.float32)
+    d_state = torch.empty((B, 3, D) if want_state else (0,), device=x_in.device, dtype=x_in.dtype)
+    nbytes = lib.rglru_conv_bwd_workspace_bytes(B, T, D)
+    ws = torch.empty(nbytes, device=x_in.device, dtype=torch.uint8)
+    with torch.cuda.device(x_in.device):
+        rc = lib.rglru_conv_bwd(_ptr(d_conv), _ptr(x_in), _ptr(w), _ptr(state), _ptr(tok), _ptr(dx), _ptr(d_w),
+                                _ptr(d_b), _ptr(d_state) if want_state else None, _ptr(ws), nbytes, B, T, D, dt,
+                                _stream(x_in))
+    _lib.check(rc, "rglru_conv_bwd")
+    return dx, d_w, d_b, d_state
+
+
+@_conv_bwd.register_fake
+def _(d_conv, x_in, w, state, tok, want_state):
+    B, T, D = x_in.shape
+    return (torch.empty_like(x_in), x_in.new_empty((D, 4), dtype=torch.float32),
+            x_in.new_empty((D,), dtype=torch.float32), x_in.new_empty((B, 3, D) if want_state else (0,)))
+
+
+def _conv_setup(ctx, inputs, output):
+    x_in, w, b, state, tok = inputs
+    ctx.save_for_backward(x_in, w, state, tok)
+    ctx.has_bias = b is not None
+    ctx.want_state = state is not None and ctx.needs_input_grad[3]
+
+
+def _conv_backward(ctx, d_out, _d_new_state):
+    x_in, w, state, tok = ctx.saved_tensors
+    dx, d_w, d_b, d_state = _conv_bwd(d_out.contiguous(), x_in, w, state, tok, ctx.want_state)
+    return dx, d_w, (d_b if ctx.has_bias else None), (d_state if ctx.want_state else None), None
+
+
+_conv_fwd.register_autograd(_conv_backward, setup_context=_conv_setup)
+
+
+def causal_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state: Optional[Tensor] = None,
+                tok: Optional[Tensor] = None) -> tuple[Tensor, Tensor]:
+    """Width-4 depthwise causal convolution; ``weight`` is [D, 4] with column 3 on the current token.
+
+    Returns the convolved sequence and the next conv state [B, 3, D].  The gradient with
+    respect to the returned state is not propagated (the reference never differentiates it).
+    """
+    if x_in.dim() != 3:
+        raise ValueError("conv input must be [batch, sequence, width]")
+    if weight.shape != (x_in.shape[2], 4):
+        raise ValueError("CUDA causal conv supports kernel width 4 with weight [width, 4]")
+    w = weight.to(torch.float32).contiguous()
+    b = None if bias is None else bias.to(torch.float32).contiguous()
+    st = None if conv_state is None else conv_state.to(x_in.dtype).contiguous()
+    return _conv_fwd(x_in.contiguous(), w, b, st, None if tok is None else tok.contiguous())
+
+
+# ----------------------------------------------------------------------------- decode (in-place state, no autograd)
+def decode_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state: Tensor,
+                tok: Optional[Tensor] = None) -> Tensor:
+    """One token of the causal conv; ``conv_state`` [B,3,D] is updated in place."""
+    lib = _lib.load()
+    _require_cuda(x_in, weight, bias, conv_state, tok)
+    dt = _io_dtype(x_in, "decode conv")
+    B, D = x_in.shape
+    if conv_state.shape != (B, 3, D) or conv_state.dtype != x_in.dtype or not conv_state.is_contiguous():
+        raise ValueError("conv_state must be a contiguous [batch, 3, width] tensor of the activation dtype")
+    out = torch.empty_like(x_in)
+    with torch.cuda.device(x_in.device):
+        rc = lib.rglru_decode_conv(_ptr(x_in.contiguous()), _ptr(weight), _ptr(bias), _ptr(conv_state), _ptr(tok),
+                                   _ptr(out), B, D, dt, _stream(x_in))
+    _lib.check(rc, "rglru_decode_conv")
+    return out
+
+
+def decode_step(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h: Tensor, tok: Optional[Tensor] = None,
+                c: float = 8.0) -> Tensor:
+    """One token of the RG-LRU; the fp32 state ``h`` [B,D] is updated in place, returns y."""
+    lib = _lib.load()
+    _require_cuda(x, u_r, u_i, lam, h, tok)
+    dt = _io_dtype(x, "decode step")
+    B, D = x.shape
+    if h.shape != (B, D) or h.dtype != torch.float32 or not h.is_contiguous():
+        raise ValueError("h must be a contiguous fp32 [batch, width] tensor")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = lib.rglru_decode_step(_ptr(x.contiguous()), _ptr(u_r.contiguous()), _ptr(u_i.contiguous()), _ptr(lam),
+                                   _ptr(h), _ptr(tok), _ptr(y), B, D, float(c), dt, _stream(x))
+    _lib.check(rc, "rglru_decode_step")
+    return y

@@ -1,0 +1,163 @@
+/*
+ * rglru_b200.h -- C ABI of the B200 (sm_100a) RG-LRU kernels.
+ *
+ * Every entry point replaces one piece of the Griffin reference's RG-LRU path
+ * (paths below are relative to the reference project root).  All pointers are
+ * DEVICE pointers owned by the caller, tensors are dense row-major with the
+ * channel axis fastest ([B, T, D] unless stated otherwise).  Functions never
+ * throw and never synchronise; they enqueue work on `stream` (a cudaStream_t
+ * passed as void*, NULL = legacy default stream) of the current device and
+ * return an rglru_status.  Except where stated they allocate no device memory.
+ *
+ * io_dtype selects the element type of the [B,T,D] activations and their
+ * gradients; the recurrent state, Lambda and every reduction are fp32.
+ */
+#ifndef RGLRU_B200_H
+#define RGLRU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum rglru_dtype { RGLRU_F32 = 0, RGLRU_BF16 = 1 };
+
+enum rglru_status {
+  RGLRU_OK = 0,
+  RGLRU_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+  RGLRU_ERR_BAD_DTYPE = 2,      /* io_dtype is not a member of rglru_dtype */
+  RGLRU_ERR_BAD_SHAPE = 3,      /* a dimension is <= 0 or exceeds the supported range */
+  RGLRU_ERR_MISALIGNED = 4,     /* a pointer is not aligned to its element size */
+  RGLRU_ERR_WORKSPACE = 5,      /* workspace is missing or smaller than rglru_workspace_bytes() */
+  RGLRU_ERR_LAUNCH = 6,         /* the CUDA runtime rejected a launch (see rglru_last_cuda_error) */
+  RGLRU_ERR_DEVICE_TIMEOUT = 7, /* a bounded in-kernel wait expired (reported by rglru_device_status) */
+  RGLRU_ERR_UNSUPPORTED = 8     /* the device is not sm_100 or the driver lacks a required entry point */
+};
+
+/* Per-token flag byte shared by all kernels (one byte per (b, t), row-major [B, T]).
+ * It packs what the reference passes as three tensors: `reset_mask`, `active_mask`
+ * (griffin/griffin.py:195-196) and, for the convolution, the tap mask
+ * `segment_pos >= lag` (griffin/griffin.py:485).  A zero byte is an ordinary token
+ * (active, no reset, all four taps inside its document) and a NULL mask pointer
+ * means "all zero". */
+#define RGLRU_TOK_CUT_MASK 0x03u     /* 3 - min(segment_pos, 3): how many of the oldest taps fall outside the document */
+#define RGLRU_TOK_RESET 0x04u        /* recurrence restarts here: a = 0, gamma = 1 */
+#define RGLRU_TOK_INACTIVE 0x08u     /* right padding: a = 1, b = 0, conv emits 0 and keeps its history */
+#define RGLRU_TOK_ZERO_HISTORY 0x10u /* conv history older than this token is returned as zeros in the next
+                                        conv state (the variable-length path, griffin/griffin.py:495-496) */
+
+const char* rglru_status_string(int status);
+/* Text of the last CUDA runtime error seen by this library on the calling thread. */
+const char* rglru_last_cuda_error(void);
+int rglru_abi_version(void);
+
+/* Reads (and clears) the device-side status word that kernels set when a bounded
+ * wait expires.  Synchronises the current device.  Returns RGLRU_OK or
+ * RGLRU_ERR_DEVICE_TIMEOUT; *detail receives a kernel-specific code. */
+int rglru_device_status(int* detail);
+
+/* Time-steps between two saved recurrent states (the backward kernel rebuilds the
+ * states inside one such chunk from its entry state). */
+int rglru_chunk_steps(int io_dtype);
+
+/* Bytes of caller-provided workspace shared by rglru_fwd and rglru_bwd of one call
+ * pair: chunk-entry states [B, ceil(T/chunk), D] fp32 followed by per-row dLambda
+ * partial sums [B, D] fp32.  Contents written by rglru_fwd must be left untouched
+ * until the matching rglru_bwd has run. */
+size_t rglru_workspace_bytes(int B, int T, int D, int io_dtype);
+
+/* Forward: gate epilogue + linear scan.
+ * Replaces RG_LRU.forward from the gate activations on: griffin/griffin.py:237-258
+ * (sigmoid gates, a = exp(c r logsigmoid(Lambda)), gamma = sqrt(-expm1(2 log a)),
+ * reset / active masking, b = gamma i x) and the scan griffin/griffin.py:273-286
+ * (also griffin/triton_scan.py:31-60 fed by the eager epilogue).
+ *   x, u_r, u_i : [B,T,D] io_dtype; u_r / u_i are the outputs of the recurrence and
+ *                 input BlockDiagonalLinear gates (griffin/griffin.py:237-238) BEFORE the sigmoid
+ *   lambda      : [D] fp32        h0 : [B,D] fp32 or NULL (zeros)
+ *   tok         : [B,T] flag bytes or NULL
+ *   y           : [B,T,D] io_dtype out      h_last : [B,D] fp32 out or NULL
+ *   ws          : workspace or NULL; NULL skips saving chunk states (inference only)
+ */
+int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+              const uint8_t* tok, void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T,
+              int D, float c, int io_dtype, void* stream);
+
+/* Backward of rglru_fwd.  The reference obtains these gradients from autograd over
+ * griffin/griffin.py:237-286 with the capped sqrt slope of griffin/griffin.py:59-65
+ * and, for the scan itself, griffin/triton_scan.py:63-122.
+ *   dy       : [B,T,D] io_dtype     dh_last : [B,D] fp32 or NULL (zeros)
+ *   x,u_r,u_i,lambda,h0,tok : the forward inputs;  ws : the workspace rglru_fwd filled
+ *   dx       : [B,T,D] io_dtype out -- the DIRECT path only (through b = gamma i x); the
+ *              part through the gate projections is the caller's GEMM backward of du_r/du_i
+ *   du_r,du_i: [B,T,D] io_dtype out     dlambda : [D] fp32 out     dh0 : [B,D] fp32 out or NULL
+ */
+int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u_r, const void* u_i,
+              const float* lambda, const float* h0, const uint8_t* tok, void* ws, size_t ws_bytes,
+              void* dx, void* du_r, void* du_i, float* dlambda, float* dh0, int B, int T, int D,
+              float c, int io_dtype, void* stream);
+
+/* Raw affine scan h_t = a_t h_{t-1} + b_t on fp32 tensors: the operator
+ * fused_rglru_scan(decay, current_input, initial_state) of griffin/triton_scan.py:274-276
+ * (forward kernel :31-60).  decay, drive, out: [B,T,D] fp32; h0: [B,D] fp32 or NULL. */
+int rglru_linear_scan_fwd(const float* decay, const float* drive, const float* h0, float* out, int B,
+                          int T, int D, void* stream);
+
+/* Backward of the raw scan (griffin/triton_scan.py:63-122, 248-271): given the saved
+ * decay, h0 and forward output, writes d_decay = g_t h_{t-1}, d_drive = g_t and
+ * d_h0 = a_0 g_0 with g_t = d_out_t + a_{t+1} g_{t+1}.  d_h0 may be NULL. */
+int rglru_linear_scan_bwd(const float* d_out, const float* decay, const float* h0, const float* out,
+                          float* d_decay, float* d_drive, float* d_h0, int B, int T, int D,
+                          void* stream);
+
+/* Causal depthwise convolution, kernel width 4, with document-boundary tap masking:
+ * griffin/griffin.py:474-487 (dense path) and, when tok carries RGLRU_TOK_INACTIVE
+ * bytes, the right-padded path griffin/griffin.py:488-510.
+ *   x_in       : [B,T,D] io_dtype (output of linear_x)
+ *   conv_w     : [D,4] fp32, column 3 multiplies the current token (temporal_conv.weight[:,0,:])
+ *   conv_b     : [D] fp32 or NULL
+ *   conv_state : [B,3,D] io_dtype history before t = 0, or NULL (zeros)
+ *   tok        : [B,T] flag bytes or NULL
+ *   x_conv     : [B,T,D] io_dtype out
+ *   new_state  : [B,3,D] io_dtype out or NULL
+ */
+int rglru_conv_fwd(const void* x_in, const float* conv_w, const float* conv_b, const void* conv_state,
+                   const uint8_t* tok, void* x_conv, void* new_state, int B, int T, int D,
+                   int io_dtype, void* stream);
+
+/* Backward of rglru_conv_fwd for the dense (no padding) case: the reference gets it from
+ * autograd over griffin/griffin.py:478-486.
+ *   d_conv : [B,T,D] io_dtype gradient of x_conv;   x_in, conv_w, conv_state, tok as in forward
+ *   dx_in  : [B,T,D] io_dtype out
+ *   d_w    : [D,4] fp32 out   d_b : [D] fp32 out or NULL   d_state : [B,3,D] io_dtype out or NULL
+ *   ws     : >= rglru_conv_bwd_workspace_bytes(B,T,D) bytes of scratch
+ */
+size_t rglru_conv_bwd_workspace_bytes(int B, int T, int D);
+int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, const void* conv_state,
+                   const uint8_t* tok, void* dx_in, float* d_w, float* d_b, void* d_state, void* ws,
+                   size_t ws_bytes, int B, int T, int D, int io_dtype, void* stream);
+
+/* Single-token decode update: the T = 1 case of RecurrentBlock.forward with a cache,
+ * griffin/griffin.py:459-528, split at the gate projections (which stay ordinary GEMMs):
+ *
+ * rglru_decode_conv: x_conv = bias + sum_k w[:,k] * [conv_state; x_in][k] with tap masking,
+ * then conv_state <- last 3 rows (griffin/griffin.py:478-487); inactive rows leave the
+ * state unchanged and emit zeros (griffin/griffin.py:505-508).
+ *   x_in : [B,D] io_dtype   conv_state : [B,3,D] io_dtype in/out   tok : [B] or NULL
+ *   x_conv : [B,D] io_dtype out
+ */
+int rglru_decode_conv(const void* x_in, const float* conv_w, const float* conv_b, void* conv_state,
+                      const uint8_t* tok, void* x_conv, int B, int D, int io_dtype, void* stream);
+
+/* rglru_decode_step: h <- a h + b for one token and y = h (griffin/griffin.py:237-258 at T = 1,
+ * the sequential branch :280-286 that decode always takes).
+ *   x, u_r, u_i : [B,D] io_dtype   h : [B,D] fp32 in/out   tok : [B] or NULL   y : [B,D] io_dtype out
+ */
+int rglru_decode_step(const void* x, const void* u_r, const void* u_i, const float* lambda, float* h,
+                      const uint8_t* tok, void* y, int B, int D, float c, int io_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RGLRU_B200_H */

@@ -1,0 +1,251 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the reference's stored
+outputs (tests/golden) and against the CPU oracle on the same seeded inputs.
+
+Tolerances (from the task statement): fp32 I/O 1e-5 norm-wise relative, bf16 I/O 2e-2,
+on outputs and on every gradient; small golden cases additionally use the reference's
+own element-wise tolerances (2e-5 / 3e-5, tests/test_rglru.py:127-204 of the reference).
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import load_golden, params_of
+from oracle import rglru_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FP32_REL = 1e-5
+BF16_REL = 2e-2
+DEV = "cuda"
+
+
+def _ops():
+    from griffin_b200 import ops
+    return ops
+
+
+def _flags(case, B, T):
+    from griffin_b200.modules import token_flags
+    reset = case.get("reset")
+    active = case.get("active")
+    return token_flags(B, T, DEV, reset=None if reset is None else reset.to(DEV),
+                       active=None if active is None else active.to(DEV))
+
+
+def _cuda_core(case, dtype=torch.float32, prefix=""):
+    """Run rglru fwd+bwd on the stored gate pre-activations; returns outputs and grads on CPU."""
+    ops = _ops()
+    x = case["x"].to(DEV, dtype).requires_grad_(True)
+    u_r = case[prefix + "u_r"].to(DEV, dtype).requires_grad_(True)
+    u_i = case[prefix + "u_i"].to(DEV, dtype).requires_grad_(True)
+    lam = case["p.Lambda"].to(DEV, torch.float32).requires_grad_(True)
+    h0 = case["h0"].to(DEV).requires_grad_(True) if "h0" in case else None
+    B, T, _ = x.shape
+    y, h_last = ops.rglru(x, u_r, u_i, lam, h0, _flags(case, B, T))
+    loss = (y.float() * case["dy"].to(DEV).float()).sum()
+    if "dh_last" in case:
+        loss = loss + (h_last * case["dh_last"].to(DEV)).sum()
+    loss.backward()
+    out = {"y": y, "h_last": h_last, "dx": x.grad, "du_r": u_r.grad, "du_i": u_i.grad, "dLambda": lam.grad}
+    if h0 is not None:
+        out["dh0"] = h0.grad
+    return {k: v.detach().float().cpu() for k, v in out.items()}
+
+
+@pytest.mark.parametrize("name", ["rglru_masks_f32", "rglru_state_f32", "rglru_plain_f32"])
+def test_core_matches_reference_golden_fp32(name):
+    case = load_golden(name)
+    got = _cuda_core(case)
+    # reference tolerances for its fused-vs-sequential test
+    torch.testing.assert_close(got["y"], case["y"], atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(got["h_last"], case["h_last"], atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(got["du_r"], case["du_r"], atol=3e-5, rtol=3e-5)
+    torch.testing.assert_close(got["du_i"], case["du_i"], atol=3e-5, rtol=3e-5)
+    torch.testing.assert_close(got["dLambda"], case["g.Lambda"], atol=3e-5, rtol=3e-5)
+    if "dh0" in case:
+        torch.testing.assert_close(got["dh0"], case["dh0"], atol=3e-5, rtol=3e-5)
+    for key, ref in (("y", "y"), ("du_r", "du_r"), ("du_i", "du_i"), ("dLambda", "g.Lambda")):
+        assert orc.rel_l2(got[key], case[ref]) <= FP32_REL, key
+
+
+def _load_module(case, width, blocks, dtype=torch.float32):
+    from griffin_b200 import RG_LRU
+    m = RG_LRU(width, gate_blocks=blocks, scan_mode="cuda")
+    m.load_state_dict(params_of(case))
+    return m.to(DEV, dtype)
+
+
+@pytest.mark.parametrize("name,width,blocks", [("rglru_masks_f32", 32, 4), ("rglru_state_f32", 24, 4),
+                                                ("rglru_plain_f32", 40, 4)])
+def test_module_matches_reference_golden_fp32(name, width, blocks):
+    """Whole RG_LRU module (gate GEMMs in torch + CUDA kernels): outputs, dx and all parameter grads."""
+    case = load_golden(name)
+    m = _load_module(case, width, blocks)
+    x = case["x"].to(DEV).requires_grad_(True)
+    h0 = case["h0"].to(DEV).requires_grad_(True) if "h0" in case else None
+    reset = case["reset"].to(DEV) if "reset" in case else None
+    active = case["active"].to(DEV) if "active" in case else None
+    y, h_last = m(x, h0, reset_mask=reset, active_mask=active, return_state=True)
+    loss = (y * case["dy"].to(DEV)).sum()
+    if "dh_last" in case:
+        loss = loss + (h_last * case["dh_last"].to(DEV)).sum()
+    loss.backward()
+    torch.testing.assert_close(y.cpu(), case["y"], atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(x.grad.cpu(), case["dx"], atol=3e-5, rtol=3e-5)
+    for key, p in m.named_parameters():
+        torch.testing.assert_close(p.grad.cpu(), case["g." + key], atol=5e-5, rtol=5e-5)
+        assert orc.rel_l2(p.grad, case["g." + key]) <= FP32_REL, key
+
+
+def test_config0_full_shape_fp32():
+    """BASELINE config 0 (B=2, T=256, D=256, 4 gate heads, fp32) against the reference's stored results."""
+    from griffin_b200 import RG_LRU
+    case = load_golden("rglru_config0_f32")
+    inp = orc.make_rglru_case(2, 256, 256, 4, seed=0)
+    m = RG_LRU(256, gate_blocks=4, scan_mode="cuda")
+    m.load_state_dict({k: inp[k] for k in ("Lambda", "recurrence_gate.weight", "recurrence_gate.bias",
+                                            "input_gate.weight", "input_gate.bias")})
+    m = m.to(DEV)
+    x = inp["x"].to(DEV).requires_grad_(True)
+    y, h_last = m(x, return_state=True)
+    (y * inp["dy"].to(DEV)).sum().backward()
+    ts = int(case["subsample"][0])
+    assert orc.rel_l2(y[:, ts // 2 :: ts], case["y"]) <= FP32_REL
+    assert orc.rel_l2(x.grad[:, ts // 2 :: ts], case["dx"]) <= FP32_REL
+    assert orc.rel_l2(h_last, case["h_last"]) <= FP32_REL
+    assert abs(y.double().norm().item() / case["y_norm"].item() - 1) <= FP32_REL
+    assert abs(x.grad.double().norm().item() / case["dx_norm"].item() - 1) <= FP32_REL
+    for key, p in m.named_parameters():
+        assert orc.rel_l2(p.grad, case["g." + key]) <= FP32_REL, key
+
+
+def test_bf16_io_against_both_references():
+    """bf16 I/O, fp32 state: within 2e-2 of the literal bf16 reference and of the fp32 reference on rounded data."""
+    case = load_golden("rglru_bf16_pair")
+    for tag in ("f32", "bf16"):
+        got = _cuda_core(case, torch.bfloat16, prefix=tag + ".")
+        assert orc.rel_l2(got["y"], case[tag + ".y"]) <= BF16_REL
+        assert orc.rel_l2(got["h_last"], case[tag + ".h_last"]) <= BF16_REL
+        assert orc.rel_l2(got["du_r"], case[tag + ".du_r"]) <= BF16_REL
+        assert orc.rel_l2(got["du_i"], case[tag + ".du_i"]) <= BF16_REL
+        assert orc.rel_l2(got["dLambda"], case[tag + ".g.Lambda"]) <= BF16_REL
+    # whole module incl. gate GEMMs and parameter grads, against the fp32 reference on rounded data
+    m = _load_module(case, 64, 2, torch.bfloat16)
+    x = case["x"].to(DEV, torch.bfloat16).requires_grad_(True)
+    y = m(x)
+    (y.float() * case["dy"].to(DEV)).sum().backward()
+    assert orc.rel_l2(y, case["f32.y"]) <= BF16_REL
+    assert orc.rel_l2(x.grad, case["f32.dx"]) <= BF16_REL
+    for key, p in m.named_parameters():
+        assert orc.rel_l2(p.grad, case["f32.g." + key]) <= BF16_REL, key
+
+
+def test_bf16_near_unit_decay_stays_finite():
+    """Lambda = 20 and a gate bias of -100 (reference tests/test_rglru.py:61-75): a -> 1, gamma^2 -> 0."""
+    case = load_golden("rglru_extreme_bf16")
+    got = _cuda_core(case, torch.bfloat16)
+    for key, v in got.items():
+        assert torch.isfinite(v).all(), key
+    assert orc.rel_l2(got["y"], case["y"]) <= BF16_REL
+    assert orc.rel_l2(got["du_i"], case["du_i"]) <= BF16_REL
+
+
+SHAPES = [(1, 1, 1), (2, 5, 6), (1, 63, 64), (2, 64, 64), (2, 65, 128), (3, 67, 65), (2, 130, 257),
+          (2, 200, 72), (1, 257, 320), (4, 33, 8)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("masked", [False, True])
+def test_core_against_oracle_odd_shapes(shape, dtype, masked):
+    """Ragged sizes (T not a multiple of the chunk, D not a multiple of the tile or of the vector width),
+    with and without masks, non-zero h0 and a gradient on the final state, against the O(T) oracle in fp64."""
+    B, T, D = shape
+    gen = torch.Generator().manual_seed(B * 1000 + T * 10 + D)
+    x = torch.randn(B, T, D, generator=gen).to(dtype)
+    u_r = torch.randn(B, T, D, generator=gen).to(dtype)
+    u_i = torch.randn(B, T, D, generator=gen).to(dtype)
+    dy = torch.randn(B, T, D, generator=gen).to(dtype)
+    lam = orc.init_lambda(D, 8.0, gen)
+    if D > 2:
+        lam[0] = -3.0   # a channel outside the polynomial range of expm1
+        lam[1] = 20.0   # near-unit decay
+    h0 = torch.randn(B, D, generator=gen)
+    dh = torch.randn(B, D, generator=gen)
+    reset = active = None
+    if masked:
+        reset = torch.rand(B, T, generator=gen) < 0.1
+        active = torch.ones(B, T, dtype=torch.bool)
+        active[-1, T - T // 3:] = False
+    case = {"x": x, "u_r": u_r, "u_i": u_i, "dy": dy, "p.Lambda": lam, "h0": h0, "dh_last": dh}
+    if masked:
+        case["reset"], case["active"] = reset, active
+    got = _cuda_core(case, dtype)
+    want = orc.rglru_backward_linear(x.double(), u_r.double(), u_i.double(), lam.double(), dy.double(), h0=h0,
+                                     dh_last=dh, reset=reset, active=active)
+    tol = FP32_REL if dtype == torch.float32 else BF16_REL
+    for key in ("y", "h_last", "dx", "du_r", "du_i", "dLambda", "dh0"):
+        err = orc.rel_l2(got[key], want[key])
+        assert err <= tol, (key, err)
+
+
+def test_inference_without_workspace_and_determinism():
+    ops = _ops()
+    gen = torch.Generator().manual_seed(7)
+    x, u_r, u_i = (torch.randn(2, 300, 192, generator=gen).to(DEV) for _ in range(3))
+    lam = orc.init_lambda(192, 8.0, gen).to(DEV)
+    with torch.no_grad():
+        y1, h1 = ops.rglru(x, u_r, u_i, lam)
+        y2, h2 = ops.rglru(x, u_r, u_i, lam)
+    assert torch.equal(y1, y2) and torch.equal(h1, h2)
+    torch.testing.assert_close(y1[:, -1], h1, atol=0, rtol=0)
+    # chunked == whole: carry the state across two calls
+    with torch.no_grad():
+        ya, ha = ops.rglru(x[:, :131].contiguous(), u_r[:, :131].contiguous(), u_i[:, :131].contiguous(), lam)
+        yb, hb = ops.rglru(x[:, 131:].contiguous(), u_r[:, 131:].contiguous(), u_i[:, 131:].contiguous(), lam, ha)
+    assert orc.rel_l2(torch.cat([ya, yb], 1), y1) <= FP32_REL
+    assert orc.rel_l2(hb, h1) <= FP32_REL
+    from griffin_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+def test_raw_scan_matches_reference_selftest_and_random():
+    """The operator-level drop-in for fused_rglru_scan, on the reference's own self-test inputs
+    (griffin/triton_scan.py:142-177, tolerances 2e-5 / 3e-5) and its random GPU test shape (2, 37, 65)."""
+    ops = _ops()
+    vec = orc.selftest_vectors()
+    gold = load_golden("scan_selftest")
+    leaves = [vec[k].to(DEV).requires_grad_(True) for k in ("decay", "drive", "h0")]
+    out = ops.linear_scan(*leaves)
+    grads = torch.autograd.grad(out, leaves, vec["upstream"].to(DEV))
+    torch.testing.assert_close(out.cpu(), gold["out"], atol=2e-5, rtol=2e-5)
+    for g, key in zip(grads, ("d_decay", "d_drive", "d_h0")):
+        torch.testing.assert_close(g.cpu(), gold[key], atol=3e-5, rtol=3e-5)
+    rnd = load_golden("scan_random")
+    leaves = [rnd[k].to(DEV).requires_grad_(True) for k in ("decay", "drive", "h0")]
+    out = ops.linear_scan(*leaves)
+    grads = torch.autograd.grad(out, leaves, rnd["upstream"].to(DEV))
+    torch.testing.assert_close(out.cpu(), rnd["out"], atol=2e-5, rtol=2e-5)
+    for g, key in zip(grads, ("d_decay", "d_drive", "d_h0")):
+        torch.testing.assert_close(g.cpu(), rnd[key], atol=3e-5, rtol=3e-5)
+
+
+@pytest.mark.parametrize("shape", [(2, 300, 128), (1, 70, 64), (3, 9, 20)])
+def test_raw_scan_tma_and_plain_paths(shape):
+    ops = _ops()
+    B, T, D = shape
+    gen = torch.Generator().manual_seed(T)
+    decay = torch.sigmoid(torch.randn(B, T, D, generator=gen)).requires_grad_(True)
+    drive = torch.randn(B, T, D, generator=gen).requires_grad_(True)
+    h0 = torch.randn(B, D, generator=gen).requires_grad_(True)
+    up = torch.randn(B, T, D, generator=gen)
+    ref = orc.linear_scan(decay.double(), drive.double(), h0.double())
+    ref_g = torch.autograd.grad(ref, (decay, drive, h0), up.double())
+    leaves = [t.detach().to(DEV).requires_grad_(True) for t in (decay, drive, h0)]
+    out = ops.linear_scan(*leaves)
+    grads = torch.autograd.grad(out, leaves, up.to(DEV))
+    assert orc.rel_l2(out, ref) <= FP32_REL
+    for g, r in zip(grads, ref_g):
+        assert orc.rel_l2(g, r) <= FP32_REL
