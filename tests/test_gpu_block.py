@@ -1,0 +1,190 @@
+"""GPU parity of the conv, the cached recurrent block and single-token decode against the
+reference's stored results (tests/golden, written by the unmodified reference) and the CPU oracle."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import load_golden, params_of
+from oracle import rglru_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FP32_REL = 1e-5
+BF16_REL = 2e-2
+
+
+def _block(case, input_dim, width, blocks=16, dtype=torch.float32):
+    from griffin_b200 import RecurrentBlock
+    blk = RecurrentBlock(input_dim, width, gate_blocks=blocks, scan_mode="cuda")
+    blk.load_state_dict(params_of(case))
+    return blk.to(DEV, dtype).eval()
+
+
+def _cache_to(cache):
+    return cache
+
+
+def test_chunked_prefill_matches_full_and_reference():
+    """tests/test_recurrentblock.py:33-50 of the reference: chunks 3/4/2 carry conv history and RNN state."""
+    case = load_golden("block_chunked")
+    blk = _block(case, 8, 12)
+    x = case["x"].to(DEV)
+    with torch.no_grad():
+        full = blk(x)
+        a, c1 = blk(x[:, :3], return_cache=True)
+        b, c2 = blk(x[:, 3:7], c1, return_cache=True)
+        c, c3 = blk(x[:, 7:], c2, return_cache=True)
+    torch.testing.assert_close(full.cpu(), case["full"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(torch.cat([a, b, c], 1).cpu(), case["chunks"], atol=2e-6, rtol=2e-5)
+    for tag, cache in (("c1", c1), ("c2", c2), ("c3", c3)):
+        torch.testing.assert_close(cache.rnn_state.cpu(), case[f"{tag}.rnn"], atol=2e-6, rtol=2e-5)
+        torch.testing.assert_close(cache.conv_state.cpu(), case[f"{tag}.conv"], atol=1e-6, rtol=1e-6)
+        assert torch.equal(cache.segment_position.cpu(), case[f"{tag}.pos"])
+        assert cache.rnn_state.dtype == torch.float32
+
+
+def test_document_reset_inside_sequence():
+    case = load_golden("block_reset")
+    blk = _block(case, 8, 16, 4)
+    with torch.no_grad():
+        out, cache = blk(case["x"].to(DEV), segment_pos=case["segment_pos"].to(DEV), return_cache=True)
+    torch.testing.assert_close(out.cpu(), case["full"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(cache.rnn_state.cpu(), case["rnn"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(cache.conv_state.cpu(), case["conv"], atol=1e-6, rtol=1e-6)
+    assert torch.equal(cache.segment_position.cpu(), case["pos"])
+    # cached continuation across the reset equals the full run
+    seg = case["segment_pos"].to(DEV)
+    x = case["x"].to(DEV)
+    with torch.no_grad():
+        first, c1 = blk(x[:, :6], segment_pos=seg[:, :6], return_cache=True)
+        second, _ = blk(x[:, 6:], c1, seg[:, 6:], return_cache=True)
+    torch.testing.assert_close(torch.cat([first, second], 1).cpu(), case["full"], atol=2e-6, rtol=2e-5)
+
+
+def test_right_padded_prefill_then_decode():
+    case = load_golden("block_padded")
+    blk = _block(case, 8, 16, 4)
+    with torch.no_grad():
+        pre, c1 = blk(case["x"].to(DEV), active_mask=case["active"].to(DEV), return_cache=True)
+        dec, c2 = blk(case["next"].to(DEV), c1, return_cache=True)
+    torch.testing.assert_close(pre.cpu(), case["prefill"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(dec.cpu(), case["decode"], atol=2e-6, rtol=2e-5)
+    for tag, cache in (("c1", c1), ("c2", c2)):
+        torch.testing.assert_close(cache.rnn_state.cpu(), case[f"{tag}.rnn"], atol=2e-6, rtol=2e-5)
+        torch.testing.assert_close(cache.conv_state.cpu(), case[f"{tag}.conv"], atol=1e-6, rtol=1e-6)
+        assert torch.equal(cache.segment_position.cpu(), case[f"{tag}.pos"])
+
+
+def test_token_by_token_decode_matches_full():
+    """tests/test_griffin_model.py:87-118 family at the block level, plus the dedicated decode kernels."""
+    from griffin_b200 import ops
+    case = load_golden("block_decode")
+    blk = _block(case, 8, 16, 4)
+    x = case["x"].to(DEV)
+    cache = None
+    outs = []
+    with torch.no_grad():
+        for t in range(x.shape[1]):
+            o, cache = blk(x[:, t : t + 1], cache, return_cache=True)
+            outs.append(o)
+            torch.testing.assert_close(cache.rnn_state.cpu(), case["rnn"][t], atol=2e-6, rtol=2e-5)
+            torch.testing.assert_close(cache.conv_state.cpu(), case["conv"][t], atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(torch.cat(outs, 1).cpu(), case["steps"], atol=2e-6, rtol=2e-5)
+
+    # the in-place single-token kernels give the same trajectory
+    B, T, _ = x.shape
+    D = 16
+    h = torch.zeros(B, D, device=DEV)
+    conv_state = torch.zeros(B, 3, D, device=DEV)
+    w = blk.temporal_conv.weight[:, 0, :].float().contiguous()
+    bias = blk.temporal_conv.bias.float().contiguous()
+    lam = blk.rg_lru.Lambda.float().contiguous()
+    outs = []
+    with torch.no_grad():
+        for t in range(T):
+            flag = torch.full((B,), (3 - min(t, 3)) | (4 if t == 0 else 0), device=DEV, dtype=torch.uint8)
+            gate = torch.nn.functional.gelu(blk.linear_y(x[:, t]), approximate="tanh")
+            xc = ops.decode_conv(blk.linear_x(x[:, t]), w, bias, conv_state, flag)
+            y = ops.decode_step(xc, blk.rg_lru.recurrence_gate(xc), blk.rg_lru.input_gate(xc), lam, h, flag)
+            outs.append(blk.linear_out(y * gate))
+            torch.testing.assert_close(h.cpu(), case["rnn"][t], atol=2e-6, rtol=2e-5)
+            torch.testing.assert_close(conv_state.cpu(), case["conv"][t], atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(torch.stack(outs, 1).cpu(), case["steps"], atol=2e-6, rtol=2e-5)
+
+
+def test_block_forward_backward_all_gradients():
+    """Whole block with conv weights ~ N(0, 1/4): output, dx and every parameter gradient."""
+    case = load_golden("block_grads")
+    blk = _block(case, 16, 32, 4).train()
+    x = case["x"].to(DEV).requires_grad_(True)
+    out = blk(x)
+    (out * case["dout"].to(DEV)).sum().backward()
+    assert orc.rel_l2(out, case["out"]) <= FP32_REL
+    assert orc.rel_l2(x.grad, case["dx"]) <= FP32_REL
+    for key, p in blk.named_parameters():
+        assert orc.rel_l2(p.grad, case["g." + key]) <= FP32_REL, key
+
+
+@pytest.mark.parametrize("shape", [(2, 70, 64), (3, 37, 20), (1, 300, 136), (2, 5, 7)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_conv_forward_backward_against_oracle(shape, dtype):
+    """Conv alone with a carried state, document boundaries, and gradients incl. the state's."""
+    from griffin_b200 import ops
+    from griffin_b200.modules import token_flags
+    B, T, D = shape
+    gen = torch.Generator().manual_seed(T + D)
+    x_in = torch.randn(B, T, D, generator=gen).to(dtype)
+    w = torch.randn(D, 4, generator=gen) * 0.5
+    b = torch.randn(D, generator=gen) * 0.1
+    state = torch.randn(B, 3, D, generator=gen).to(dtype)
+    dout = torch.randn(B, T, D, generator=gen).to(dtype)
+    seg = torch.arange(T)[None, :].repeat(B, 1) + 2     # continues a document: two earlier tokens exist
+    if T > 8:
+        seg[:, T // 2 :] = torch.arange(T - T // 2)      # a new document starts mid-sequence
+    xr = x_in.double().requires_grad_(True)
+    wr = w.double().requires_grad_(True)
+    br = b.double().requires_grad_(True)
+    sr = state.double().requires_grad_(True)
+    ref, ref_state = orc.causal_conv_dense(xr, wr, br, sr, seg)
+    (ref * dout.double()).sum().backward()
+
+    xg = x_in.to(DEV).requires_grad_(True)
+    wg = w.to(DEV).requires_grad_(True)
+    bg = b.to(DEV).requires_grad_(True)
+    sg = state.to(DEV).requires_grad_(True)
+    flags = token_flags(B, T, DEV, segment_pos=seg.to(DEV))
+    out, new_state = ops.causal_conv(xg, wg, bg, sg, flags)
+    (out.float() * dout.to(DEV).float()).sum().backward()
+    tol = FP32_REL if dtype == torch.float32 else BF16_REL
+    assert orc.rel_l2(out, ref) <= tol
+    assert orc.rel_l2(new_state, ref_state) <= tol
+    assert orc.rel_l2(xg.grad, xr.grad) <= tol
+    assert orc.rel_l2(wg.grad, wr.grad) <= tol
+    assert orc.rel_l2(bg.grad, br.grad) <= tol
+    assert orc.rel_l2(sg.grad, sr.grad) <= tol
+
+
+def test_block_bf16_against_fp32_oracle():
+    """Config-2 style block in bf16 (reduced size) against the oracle on bf16-rounded weights."""
+    from griffin_b200 import RecurrentBlock
+    torch.manual_seed(11)
+    blk = RecurrentBlock(48, 128, gate_blocks=4, scan_mode="cuda")
+    with torch.no_grad():
+        blk.temporal_conv.weight.normal_(0.0, 0.5)
+    blk = blk.to(torch.bfloat16)
+    params = {k: v.detach().float().clone().requires_grad_(True) for k, v in blk.state_dict().items()}
+    x = torch.randn(2, 150, 48).to(torch.bfloat16)
+    dout = torch.randn(2, 150, 48).to(torch.bfloat16)
+    xr = x.float().requires_grad_(True)
+    ref, _ = orc.recurrent_block(xr, params)
+    (ref * dout.float()).sum().backward()
+    blk = blk.to(DEV)
+    xg = x.to(DEV).requires_grad_(True)
+    out = blk(xg)
+    (out.float() * dout.to(DEV).float()).sum().backward()
+    assert orc.rel_l2(out, ref) <= BF16_REL
+    assert orc.rel_l2(xg.grad, xr.grad) <= BF16_REL
+    for key, p in blk.named_parameters():
+        assert orc.rel_l2(p.grad, params[key].grad) <= 3e-2, key
