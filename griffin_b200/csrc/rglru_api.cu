@@ -63,15 +63,15 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 3-D map over a dense [B, T, D] tensor with a [1, rows, CH] box; out-of-range parts
+// 3-D map over a dense [B, T, D] tensor with a [1, rows, cols] box; out-of-range parts
 // of a box read as zero and are dropped on store.
-static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows) {
+static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const size_t es = bf16 ? 2 : 4;
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * es, static_cast<cuuint64_t>(D) * es * T};
-  const cuuint32_t box[3] = {static_cast<cuuint32_t>(CH), static_cast<cuuint32_t>(rows), 1u};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(cols), static_cast<cuuint32_t>(rows), 1u};
   const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -174,12 +174,13 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
 
   FwdMaps maps;
   bool tma = tma_shape_ok(T, D, es) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) && aligned(y, 16);
+  const int variant = scan_fwd_variant(B, T, D);
   if (tma) {
-    const int rows = scan_fwd_box_rows(bf16);
-    tma = make_map(&maps.x, x, bf16, B, T, D, rows) && make_map(&maps.ur, u_r, bf16, B, T, D, rows) &&
-          make_map(&maps.ui, u_i, bf16, B, T, D, rows) && make_map(&maps.y, y, bf16, B, T, D, rows);
+    const int rows = scan_fwd_box_rows(variant), cols = scan_fwd_box_cols(variant);
+    tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) && make_map(&maps.y, y, bf16, B, T, D, rows, cols);
   }
-  const cudaError_t e = launch_scan_fwd(bf16, tma, maps, a, static_cast<cudaStream_t>(stream));
+  const cudaError_t e = launch_scan_fwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
 
@@ -214,14 +215,15 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
   BwdMaps maps;
   bool tma = tma_shape_ok(T, D, es) && aligned(dy, 16) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) &&
              aligned(dx, 16) && aligned(du_r, 16) && aligned(du_i, 16);
+  const int variant = scan_bwd_variant(B, T, D);
   if (tma) {
-    const int rows = scan_bwd_box_rows(bf16);
-    tma = make_map(&maps.dy, dy, bf16, B, T, D, rows) && make_map(&maps.x, x, bf16, B, T, D, rows) &&
-          make_map(&maps.ur, u_r, bf16, B, T, D, rows) && make_map(&maps.ui, u_i, bf16, B, T, D, rows) &&
-          make_map(&maps.dx, dx, bf16, B, T, D, rows) && make_map(&maps.dur, du_r, bf16, B, T, D, rows) &&
-          make_map(&maps.dui, du_i, bf16, B, T, D, rows);
+    const int rows = scan_bwd_box_rows(variant), cols = scan_bwd_box_cols(variant);
+    tma = make_map(&maps.dy, dy, bf16, B, T, D, rows, cols) && make_map(&maps.x, x, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) && make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dx, dx, bf16, B, T, D, rows, cols) && make_map(&maps.dur, du_r, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dui, du_i, bf16, B, T, D, rows, cols);
   }
-  const cudaError_t e = launch_scan_bwd(bf16, tma, maps, a, static_cast<cudaStream_t>(stream));
+  const cudaError_t e = launch_scan_bwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
 
@@ -240,9 +242,9 @@ int rglru_linear_scan_fwd(const float* decay, const float* drive, const float* h
   RawFwdMaps maps;
   bool tma = tma_shape_ok(T, D, 4) && aligned(decay, 16) && aligned(drive, 16) && aligned(out, 16);
   if (tma) {
-    const int rows = raw_box_rows();
-    tma = make_map(&maps.drive, drive, false, B, T, D, rows) && make_map(&maps.decay, decay, false, B, T, D, rows) &&
-          make_map(&maps.out, out, false, B, T, D, rows);
+    const int rows = raw_box_rows(), cols = raw_box_cols();
+    tma = make_map(&maps.drive, drive, false, B, T, D, rows, cols) && make_map(&maps.decay, decay, false, B, T, D, rows, cols) &&
+          make_map(&maps.out, out, false, B, T, D, rows, cols);
   }
   const cudaError_t e = launch_raw_fwd(tma, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
@@ -266,10 +268,10 @@ int rglru_linear_scan_bwd(const float* d_out, const float* decay, const float* h
   bool tma = tma_shape_ok(T, D, 4) && aligned(d_out, 16) && aligned(decay, 16) && aligned(out, 16) &&
              aligned(d_decay, 16) && aligned(d_drive, 16);
   if (tma) {
-    const int rows = raw_box_rows();
-    tma = make_map(&maps.dout, d_out, false, B, T, D, rows) && make_map(&maps.decay, decay, false, B, T, D, rows) &&
-          make_map(&maps.out, out, false, B, T, D, rows) && make_map(&maps.ddecay, d_decay, false, B, T, D, rows) &&
-          make_map(&maps.ddrive, d_drive, false, B, T, D, rows);
+    const int rows = raw_box_rows(), cols = raw_box_cols();
+    tma = make_map(&maps.dout, d_out, false, B, T, D, rows, cols) && make_map(&maps.decay, decay, false, B, T, D, rows, cols) &&
+          make_map(&maps.out, out, false, B, T, D, rows, cols) && make_map(&maps.ddecay, d_decay, false, B, T, D, rows, cols) &&
+          make_map(&maps.ddrive, d_drive, false, B, T, D, rows, cols);
   }
   const cudaError_t e = launch_raw_bwd(tma, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);

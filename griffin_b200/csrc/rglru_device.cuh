@@ -11,14 +11,13 @@ namespace rglru {
 
 // ---------------------------------------------------------------- geometry
 // One CTA owns CH adjacent channels of one batch row for the whole sequence.
-// Its 256 threads form a grid of LANES time-lanes x NCV channel-vectors; a
+// Its threads form a grid of LANES time-lanes x NCV channel-vectors; a
 // thread handles CV adjacent channels over TS consecutive time-steps of each
 // chunk, so one chunk covers LANES*TS time-steps.
-constexpr int CH = 64;
+// CH (32 or 64) and LANES are template parameters of the scan kernels.
 constexpr int CV = 4;
-constexpr int NCV = CH / CV;      // 16
-constexpr int LANES = 16;
-constexpr int NT = LANES * NCV;   // 256
+// LANES (16 or 32 time-lanes per chunk) is a template parameter of the scan kernels;
+// the CTA has LANES * NCV threads.
 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float SLOPE_CAP = 1000.0f;  // bound on d sqrt / d gamma^2
@@ -26,7 +25,8 @@ constexpr float SLOPE_CAP = 1000.0f;  // bound on d sqrt / d gamma^2
 constexpr float POLY_RANGE = -0.25f;
 
 // Codes written to the device status word.
-constexpr int DEV_TIMEOUT_LOAD = 1;
+constexpr int DEV_TIMEOUT_LOAD = 1;   // a tile load never completed
+constexpr int DEV_TIMEOUT_STORE = 2;  // the producer never saw a chunk's results
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -65,6 +65,33 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
       if (mbar_try_wait(bar, parity)) return true;
     if (clock64() - start > 4000000000LL) return false;
   }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Wait used inside the pipelined kernels.  Once any thread of the CTA has seen a wait
+// expire, `dead` is set and every later wait returns at once, so all threads keep
+// executing the same barriers and the kernel runs to its end (producing garbage) with
+// the device status word set, instead of hanging or leaving barriers unmatched.
+__device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity, volatile int* dead, int* status,
+                                                  int code) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int spin = 0; spin < 128; ++spin)
+      if (mbar_try_wait(bar, parity)) return;
+    if (*dead) return;
+    if (clock64() - start > 4000000000LL) {
+      *dead = 1;
+      atomicExch(status, code);
+      return;
+    }
+  }
+}
+// Named barrier 1: the compute warps of a CTA (the TMA producer warp does not take part).
+__device__ __forceinline__ void bar_compute(int nthreads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const void* map, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
@@ -114,6 +141,65 @@ __device__ __forceinline__ float rsqrt_approx(float x) {
   return y;
 }
 
+// ---------------------------------------------------------------- packed fp32 (two lanes per instruction)
+// sm_100 executes add/mul/fma on a pair of fp32 values in one issue slot; the scan
+// kernels are issue-bound, so all channel arithmetic is written on float2 pairs.
+__device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// r = sigmoid(ur), i = sigmoid(ui) for two channels.
+//   HALF_IO = false: exp2 + one shared reciprocal, about 1e-7 relative (three MUFU operations per element).
+//   HALF_IO = true : 0.5 + 0.5 tanh(u / 2) on the hardware tanh (two MUFU operations per element); its
+//                    absolute error of 2.5e-4 is a sixteenth of the bf16 quantum of the tensors it feeds.
+template <bool HALF_IO>
+__device__ __forceinline__ void sigmoid_pair2(float2 ur, float2 ui, float2& r, float2& i) {
+  if (HALF_IO) {
+    const float2 hr = mul2(ur, f2(0.5f));
+    const float2 hi = mul2(ui, f2(0.5f));
+    r = fma2(make_float2(tanh_approx(hr.x), tanh_approx(hr.y)), f2(0.5f), f2(0.5f));
+    i = fma2(make_float2(tanh_approx(hi.x), tanh_approx(hi.y)), f2(0.5f), f2(0.5f));
+    return;
+  }
+  float2 tr = mul2(ur, f2(-LOG2E));
+  float2 ti = mul2(ui, f2(-LOG2E));
+  const float2 er = make_float2(ex2_approx(fminf(tr.x, 60.0f)), ex2_approx(fminf(tr.y, 60.0f)));
+  const float2 ei = make_float2(ex2_approx(fminf(ti.x, 60.0f)), ex2_approx(fminf(ti.y, 60.0f)));
+  const float2 dr = add2(er, f2(1.0f));
+  const float2 di = add2(ei, f2(1.0f));
+  const float2 d = mul2(dr, di);
+  const float2 inv = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+  r = mul2(inv, di);
+  i = mul2(inv, dr);
+}
+
+// E(y) = 1 - exp(-y) for y >= 0 (y = -c r logsigmoid(Lambda)), so that the decay is
+// a = 1 - E and gamma^2 = 1 - a^2 = E (2 - E) without cancellation.
+//   POLY: y is known to lie in [0, -POLY_RANGE]; alternating degree-6 Taylor, truncation < 5e-8 relative.
+//   otherwise: the polynomial where valid, 1 - 2^(-y log2 e) elsewhere (chosen per element).
+template <bool POLY>
+__device__ __forceinline__ float2 one_minus_exp_neg2(float2 y) {
+  float2 t = fma2(y, f2(-1.0f / 720.0f), f2(1.0f / 120.0f));
+  t = fma2(t, y, f2(-1.0f / 24.0f));
+  t = fma2(t, y, f2(1.0f / 6.0f));
+  t = fma2(t, y, f2(-0.5f));
+  float2 e = fma2(mul2(y, y), t, y);
+  if (!POLY) {
+    const float wx = 1.0f - ex2_approx(-LOG2E * y.x);
+    const float wy = 1.0f - ex2_approx(-LOG2E * y.y);
+    e.x = y.x < -POLY_RANGE ? e.x : wx;
+    e.y = y.y < -POLY_RANGE ? e.y : wy;
+  }
+  return e;
+}
+
 // Both gate sigmoids with one reciprocal: 1/((1+er)(1+ei)) scaled by the other
 // factor.  The exponent clamp keeps the product finite (sigmoid saturates at
 // 2^-60, far below fp32 resolution of anything it multiplies).
@@ -157,6 +243,13 @@ struct Pack<float> {
   static __device__ __forceinline__ void store(void* p, const float (&v)[4]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
+  static __device__ __forceinline__ void unpack2(const Raw& r, float2 (&v)[2]) {
+    v[0] = make_float2(r.x, r.y);
+    v[1] = make_float2(r.z, r.w);
+  }
+  static __device__ __forceinline__ void store2(void* p, const float2 (&v)[2]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+  }
   static __device__ __forceinline__ float to_float(float x) { return x; }
   static __device__ __forceinline__ float from_float(float x) { return x; }
 };
@@ -175,6 +268,18 @@ struct Pack<__nv_bfloat16> {
   static __device__ __forceinline__ void store(void* p, const float (&v)[4]) {
     __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
     __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+  static __device__ __forceinline__ void unpack2(const Raw& r, float2 (&v)[2]) {
+    v[0] = make_float2(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u));
+    v[1] = make_float2(__uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
+  }
+  static __device__ __forceinline__ void store2(void* p, const float2 (&v)[2]) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0].x, v[0].y);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v[1].x, v[1].y);
     uint2 raw;
     raw.x = *reinterpret_cast<uint32_t*>(&lo);
     raw.y = *reinterpret_cast<uint32_t*>(&hi);

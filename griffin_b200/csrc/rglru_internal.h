@@ -122,12 +122,18 @@ cudaError_t launch_decode_conv(bool bf16, const ConvArgs& a, cudaStream_t s);
 cudaError_t launch_decode_step(bool bf16, const DecodeArgs& a, cudaStream_t s);
 
 // use_tma == false selects the bounds-checked plain-load staging path that accepts any D.
-cudaError_t launch_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
-cudaError_t launch_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
-
-// Box extents (time rows) the tensor maps must be encoded with.
-int scan_fwd_box_rows(bool bf16);
-int scan_bwd_box_rows(bool bf16);
+// `variant` picks the CTA shape (see scan_fwd_variant); the tensor maps must be encoded with its box rows.
+cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps& maps, const ScanFwdArgs& args,
+                            cudaStream_t s);
+cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& args,
+                            cudaStream_t s);
+int scan_fwd_variant(int B, int T, int D);
+int scan_bwd_variant(int B, int T, int D);
+int scan_fwd_box_rows(int variant);
+int scan_fwd_box_cols(int variant);
+int scan_bwd_box_rows(int variant);
+int scan_bwd_box_cols(int variant);
+int raw_box_cols();
 
 int* device_status_word();  // device address of the status word of the current device
 

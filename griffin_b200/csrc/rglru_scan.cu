@@ -2,38 +2,47 @@
 //
 // Work decomposition.  A CTA owns CH = 64 adjacent channels of one batch row and
 // walks the whole sequence in chunks of LANES*TS time-steps.  Inside a chunk the
-// time axis is split over LANES = 16 time-lanes, each thread scanning TS steps of
-// CV = 4 channels in registers (level one), after which one thread per channel
-// chains the 16 lane aggregates and the carry from the previous chunk (level two)
-// and every lane applies its incoming state.  Chunks are staged through shared
-// memory by TMA (cp.async.bulk.tensor, 3-D tiles [1, rows, 64 channels]) in a
-// multi-stage mbarrier pipeline; results are written back into the stage in
-// place and leave through TMA stores.  A bounds-checked plain-load staging path
-// with the same arithmetic covers shapes TMA cannot address (D*elem % 16 != 0).
+// time axis is split over LANES (16 or 32) time-lanes, each thread scanning TS
+// steps of CV = 4 channels in registers (level one), after which one thread per
+// channel chains the lane aggregates and the carry from the previous chunk
+// (level two) and every lane applies its incoming state.  Chunks are staged
+// through shared memory by TMA (cp.async.bulk.tensor, 3-D tiles [1, rows, 64
+// channels]) in a multi-stage mbarrier pipeline; results are written back into
+// the stage in place and leave through TMA stores.  A bounds-checked plain-load
+// staging path with the same arithmetic covers shapes TMA cannot address
+// (D * element size not a multiple of 16 bytes).
+//
+// The kernels are bound by instruction issue before they are bound by HBM, so
+// the channel arithmetic is written on float2 pairs (one issue slot per two
+// fp32 operations on sm_100) and transcendental work is kept to four MUFU
+// operations per element.
 //
 // The gate epilogue follows griffin/griffin.py:237-258 of the reference, the
 // scan :280-286, the backward is the closed form of autograd over those lines
 // with the capped sqrt slope of :59-65.  All arithmetic is fp32.
+
+#include <cstdlib>
 
 #include "rglru_device.cuh"
 #include "rglru_internal.h"
 
 namespace rglru {
 
-struct ElemFlags {
-  bool reset;
-  bool inactive;
+// Per-row multipliers that realise the reset / padding masks without branches.
+struct RowMask {
+  float keep;    // 0 at a reset, else 1          (a <- a * keep, gamma <- gamma * keep + (1 - keep))
+  float live;    // 0 on padding, else 1          (a <- a * live + (1 - live), b <- b * live)
 };
 
 template <bool MASKED>
-__device__ __forceinline__ ElemFlags elem_flags(uint32_t packed, int st) {
-  ElemFlags f{false, false};
+__device__ __forceinline__ RowMask row_mask(uint32_t packed, int st) {
+  RowMask m{1.0f, 1.0f};
   if (MASKED) {
     const uint32_t byte = (packed >> (8 * (st & 3))) & 0xffu;
-    f.reset = (byte & TOK_RESET) != 0;
-    f.inactive = (byte & TOK_INACTIVE) != 0;
+    m.keep = (byte & TOK_RESET) ? 0.0f : 1.0f;
+    m.live = (byte & TOK_INACTIVE) ? 0.0f : 1.0f;
   }
-  return f;
+  return m;
 }
 
 // Flag bytes of the TS steps a thread owns, packed four per word.  Steps at or
@@ -52,11 +61,11 @@ __device__ __forceinline__ void load_flags(const uint8_t* tok, int b, int T, int
 }
 
 // Plain-load staging of one [rows, CH] tile (zero-filled outside the tensor).
-template <typename IO>
+template <typename IO, int CH>
 __device__ __forceinline__ void tile_load_plain(uint8_t* tile, const void* src, int b, int t0, int d0, int rows, int T, int D) {
   const IO* g = static_cast<const IO*>(src);
   IO* s = reinterpret_cast<IO*>(tile);
-  for (int idx = threadIdx.x; idx < rows * CH; idx += NT) {
+  for (int idx = threadIdx.x; idx < rows * CH; idx += blockDim.x) {
     const int row = idx / CH, col = idx % CH;
     const int t = t0 + row, d = d0 + col;
     IO v = Pack<IO>::from_float(0.0f);
@@ -64,86 +73,101 @@ __device__ __forceinline__ void tile_load_plain(uint8_t* tile, const void* src, 
     s[idx] = v;
   }
 }
-template <typename IO>
+template <typename IO, int CH>
 __device__ __forceinline__ void tile_store_plain(const uint8_t* tile, void* dst, int b, int t0, int d0, int rows, int T, int D) {
   IO* g = static_cast<IO*>(dst);
   const IO* s = reinterpret_cast<const IO*>(tile);
-  for (int idx = threadIdx.x; idx < rows * CH; idx += NT) {
+  for (int idx = threadIdx.x; idx < rows * CH; idx += blockDim.x) {
     const int row = idx / CH, col = idx % CH;
     const int t = t0 + row, d = d0 + col;
     if (t < T && d < D) g[(static_cast<size_t>(b) * T + t) * D + d] = s[idx];
   }
 }
 
-// Per-channel constants: K = c * logsigmoid(Lambda), 0 for channels past D.
+// Per-channel rate: -c * logsigmoid(Lambda) >= 0, and 0 for channels past D.
 __device__ __forceinline__ float decay_rate(const float* lambda, int d, int D, float c) {
   if (d >= D) return 0.0f;
   const float lam = lambda[d];
-  // logsigmoid(L) = -softplus(-L), evaluated without cancellation on either side.
-  const float ls = lam >= 0.0f ? -log1pf(expf(-lam)) : lam - log1pf(expf(lam));
-  return c * ls;
+  // softplus(-L) = -logsigmoid(L), evaluated without cancellation on either side.
+  const float sp = lam >= 0.0f ? log1pf(expf(-lam)) : log1pf(expf(lam)) - lam;
+  return c * sp;
 }
+
+template <int LANES, int CH>
+struct ChainSmem {
+  static constexpr int AGG = LANES * CH * 8;  // float2 per (lane, channel)
+  static constexpr int EIN = LANES * CH * 4;  // float per (lane, channel)
+};
 
 // ======================================================================
 // Forward
 // ======================================================================
 
-template <typename IO, int TS, bool MASKED, bool POLY>
+template <typename IO, int TS, int CH, bool MASKED, bool POLY>
 __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, const uint8_t* ti, int off0,
-                                          const float (&K)[CV], const uint32_t (&fl)[(TS + 3) / 4],
-                                          float (&P)[TS][CV], float (&S)[TS][CV]) {
+                                          const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
+                                          float2 (&P)[TS][2], float2 (&S)[TS][2]) {
   constexpr int ROWB = CH * sizeof(IO);
-  float p[CV], s[CV];
-#pragma unroll
-  for (int ch = 0; ch < CV; ++ch) { p[ch] = 1.0f; s[ch] = 0.0f; }
+  float2 p[2] = {f2(1.0f), f2(1.0f)};
+  float2 s[2] = {f2(0.0f), f2(0.0f)};
 #pragma unroll
   for (int st = 0; st < TS; ++st) {
     const int off = off0 + st * ROWB;
-    float xv[CV], rv[CV], iv[CV];
-    Pack<IO>::unpack(Pack<IO>::load(tx + off), xv);
-    Pack<IO>::unpack(Pack<IO>::load(tr + off), rv);
-    Pack<IO>::unpack(Pack<IO>::load(ti + off), iv);
-    const ElemFlags f = elem_flags<MASKED>(fl[st >> 2], st);
+    float2 xv[2], rv[2], iv[2];
+    Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
+    Pack<IO>::unpack2(Pack<IO>::load(tr + off), rv);
+    Pack<IO>::unpack2(Pack<IO>::load(ti + off), iv);
+    const RowMask m = row_mask<MASKED>(fl[st >> 2], st);
 #pragma unroll
-    for (int ch = 0; ch < CV; ++ch) {
-      float r, i;
-      sigmoid_pair(rv[ch], iv[ch], r, i);
-      const float em = expm1_nonpos<POLY>(r * K[ch]);
-      float a = 1.0f + em;
-      const float gsq = fmaxf(-em * (2.0f + em), 0.0f);
-      float b = sqrt_approx(gsq) * i * xv[ch];
+    for (int cp = 0; cp < 2; ++cp) {
+      float2 r, i;
+      sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
+      const float2 e = one_minus_exp_neg2<POLY>(mul2(r, K[cp]));   // 1 - a
+      float2 a = fma2(e, f2(-1.0f), f2(1.0f));
+      const float2 gsq = mul2(e, fma2(e, f2(-1.0f), f2(2.0f)));     // 1 - a^2
+      // sqrt(gsq) as gsq * rsqrt(gsq): one MUFU operation; the floor keeps rsqrt finite (gamma error <= 1e-15)
+      const float2 gq = make_float2(fmaxf(gsq.x, 1e-30f), fmaxf(gsq.y, 1e-30f));
+      float2 gam = mul2(gq, make_float2(rsqrt_approx(gq.x), rsqrt_approx(gq.y)));
       if (MASKED) {
-        if (f.reset) { a = 0.0f; b = i * xv[ch]; }
-        if (f.inactive) { a = 1.0f; b = 0.0f; }
+        a = fma2(mul2(a, f2(m.keep)), f2(m.live), f2(1.0f - m.live));
+        gam = mul2(fma2(gam, f2(m.keep), f2(1.0f - m.keep)), f2(m.live));
       }
-      p[ch] *= a;
-      s[ch] = fmaf(a, s[ch], b);
-      P[st][ch] = p[ch];
-      S[st][ch] = s[ch];
+      const float2 b = mul2(mul2(gam, i), xv[cp]);
+      p[cp] = mul2(p[cp], a);
+      s[cp] = fma2(a, s[cp], b);
+      P[st][cp] = p[cp];
+      S[st][cp] = s[cp];
     }
   }
 }
 
-template <typename IO, int TS, int NSTAGE>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE>
 struct FwdSmem {
   static constexpr int TC = LANES * TS;
   static constexpr int TILE = TC * CH * sizeof(IO);
   static constexpr int STAGE = 3 * TILE;
   static constexpr int OFF_AGG = NSTAGE * STAGE;
-  static constexpr int OFF_EIN = OFF_AGG + LANES * CH * 8;
-  static constexpr int OFF_BAR = OFF_EIN + LANES * CH * 4;
-  static constexpr int BYTES = OFF_BAR + NSTAGE * 8 + 16;
+  static constexpr int OFF_EIN = OFF_AGG + ChainSmem<LANES, CH>::AGG;
+  static constexpr int OFF_BAR = OFF_EIN + ChainSmem<LANES, CH>::EIN;   // full[NSTAGE], ready[NSTAGE], dead flag
+  static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-template <typename IO, int TS, int NSTAGE, bool USE_TMA>
-__global__ void __launch_bounds__(NT) rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
-  using SM = FwdSmem<IO, TS, NSTAGE>;
+// Threads [0, LANES*NCV) compute; with TMA one extra warp issues every bulk copy so that
+// no compute warp ever waits on the copy engine's instruction latency.
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA>
+__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
+    rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
+  using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE>;
+  constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
   constexpr int ROWB = CH * sizeof(IO);
+  constexpr int NCOMP = LANES * NCV;
   extern __shared__ __align__(128) uint8_t smem[];
   float2* agg = reinterpret_cast<float2*>(smem + SM::OFF_AGG);
   float* ein = reinterpret_cast<float*>(smem + SM::OFF_EIN);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+  uint64_t* ready = full + NSTAGE;
+  volatile int* dead = reinterpret_cast<volatile int*>(ready + NSTAGE);
 
   const int tid = threadIdx.x;
   const int lane_t = tid / NCV;
@@ -153,31 +177,48 @@ __global__ void __launch_bounds__(NT) rglru_fwd_kernel(const __grid_constant__ F
   const int nchunks = (p.T + TC - 1) / TC;
   const int nsave = (p.T + SAVE_EVERY - 1) / SAVE_EVERY;
 
-  float K[CV];
-  bool poly_ok = true;
-#pragma unroll
-  for (int ch = 0; ch < CV; ++ch) {
-    K[ch] = decay_rate(p.lambda, d0 + vec * CV + ch, p.D, p.c);
-    poly_ok = poly_ok && (K[ch] >= POLY_RANGE);
+  float2 K[2];
+  {
+    const int d = d0 + vec * CV;
+    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
+    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
   }
-  const bool poly = __syncthreads_and(poly_ok);
-
-  if (USE_TMA) {
-    if (tid == 0) {
-      prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
-      for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[s], 1);
+  if (tid == 0) {
+    *dead = 0;
+    if (USE_TMA) {
+      for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
       mbar_fence_init();
     }
-    __syncthreads();
-    if (tid == 0) {
-      for (int k = 0; k < NSTAGE && k < nchunks; ++k) {
-        uint8_t* st = smem + k * SM::STAGE;
-        mbar_expect_tx(&bars[k], SM::STAGE);
-        tma_load_3d(st, &maps.x, d0, k * TC, b, &bars[k]);
-        tma_load_3d(st + SM::TILE, &maps.ur, d0, k * TC, b, &bars[k]);
-        tma_load_3d(st + 2 * SM::TILE, &maps.ui, d0, k * TC, b, &bars[k]);
+  }
+  const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
+
+  if (USE_TMA && tid >= NCOMP) {
+    // ---- producer warp: loads run NSTAGE-1 chunks ahead; a stage is refilled as soon as the
+    // store of the results written into it has drained from shared memory.
+    if (tid == NCOMP) {
+      prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
+      auto issue = [&](int k) {
+        const int sidx = k % NSTAGE;
+        uint8_t* st = smem + sidx * SM::STAGE;
+        mbar_expect_tx(&full[sidx], SM::STAGE);
+        tma_load_3d(st, &maps.x, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::TILE, &maps.ur, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + 2 * SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
+      };
+      for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
+      for (int k = 0; k < nchunks; ++k) {
+        const int sidx = k % NSTAGE;
+        mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
+        tma_store_3d(&maps.y, smem + sidx * SM::STAGE, d0, k * TC, b);
+        tma_commit();
+        if (k + NSTAGE < nchunks) {
+          tma_wait_read<0>();
+          issue(k + NSTAGE);
+        }
       }
+      tma_wait_all<0>();
     }
+    return;
   }
 
   // Level-two chain state: thread `tid` < CH carries channel d0 + tid across chunks.
@@ -186,7 +227,6 @@ __global__ void __launch_bounds__(NT) rglru_fwd_kernel(const __grid_constant__ F
   if (tid < CH && dch < p.D && p.h0) carry = p.h0[static_cast<size_t>(b) * p.D + dch];
 
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
-  bool alive = true;
 
   for (int k = 0; k < nchunks; ++k) {
     const int stage = USE_TMA ? (k % NSTAGE) : 0;
@@ -197,32 +237,31 @@ __global__ void __launch_bounds__(NT) rglru_fwd_kernel(const __grid_constant__ F
     if (masked) load_flags<TS>(p.tok, b, p.T, t0 + lane_t * TS, fl);
 
     if (USE_TMA) {
-      alive = mbar_wait_bounded(&bars[stage], (k / NSTAGE) & 1);
+      mbar_wait_or_flag(&full[stage], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
     } else {
-      tile_load_plain<IO>(tiles, p.x, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO>(tiles + SM::TILE, p.ur, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO>(tiles + 2 * SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
-      __syncthreads();
+      tile_load_plain<IO, CH>(tiles, p.x, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::TILE, p.ur, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + 2 * SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
+      bar_compute(NCOMP);
     }
 
-    float P[TS][CV], S[TS][CV];
+    float2 P[TS][2], S[TS][2];
     const uint8_t* tx = tiles;
     const uint8_t* tr = tiles + SM::TILE;
     const uint8_t* ti = tiles + 2 * SM::TILE;
     if (masked) {
-      if (poly) fwd_local<IO, TS, true, true>(tx, tr, ti, off0, K, fl, P, S);
-      else fwd_local<IO, TS, true, false>(tx, tr, ti, off0, K, fl, P, S);
+      if (poly) fwd_local<IO, TS, CH, true, true>(tx, tr, ti, off0, K, fl, P, S);
+      else fwd_local<IO, TS, CH, true, false>(tx, tr, ti, off0, K, fl, P, S);
     } else {
-      if (poly) fwd_local<IO, TS, false, true>(tx, tr, ti, off0, K, fl, P, S);
-      else fwd_local<IO, TS, false, false>(tx, tr, ti, off0, K, fl, P, S);
+      if (poly) fwd_local<IO, TS, CH, false, true>(tx, tr, ti, off0, K, fl, P, S);
+      else fwd_local<IO, TS, CH, false, false>(tx, tr, ti, off0, K, fl, P, S);
     }
     {
       float4* dst = reinterpret_cast<float4*>(agg + lane_t * CH + vec * CV);
-      dst[0] = make_float4(P[TS - 1][0], S[TS - 1][0], P[TS - 1][1], S[TS - 1][1]);
-      dst[1] = make_float4(P[TS - 1][2], S[TS - 1][2], P[TS - 1][3], S[TS - 1][3]);
+      dst[0] = make_float4(P[TS - 1][0].x, S[TS - 1][0].x, P[TS - 1][0].y, S[TS - 1][0].y);
+      dst[1] = make_float4(P[TS - 1][1].x, S[TS - 1][1].x, P[TS - 1][1].y, S[TS - 1][1].y);
     }
-    alive = __syncthreads_and(alive);
-    if (!alive) break;  // a load never arrived: leave without touching the stage
+    bar_compute(NCOMP);
 
     if (tid < CH) {
       float2 ag[LANES];
@@ -241,51 +280,31 @@ __global__ void __launch_bounds__(NT) rglru_fwd_kernel(const __grid_constant__ F
       }
       carry = e;
     }
-    __syncthreads();
+    bar_compute(NCOMP);
 
     {
       const float4 e4 = *reinterpret_cast<const float4*>(ein + lane_t * CH + vec * CV);
-      const float e[CV] = {e4.x, e4.y, e4.z, e4.w};
+      const float2 e[2] = {make_float2(e4.x, e4.y), make_float2(e4.z, e4.w)};
       uint8_t* ty = tiles;  // y overwrites the x tile in place
 #pragma unroll
       for (int st = 0; st < TS; ++st) {
-        float yv[CV];
+        float2 yv[2];
 #pragma unroll
-        for (int ch = 0; ch < CV; ++ch) yv[ch] = fmaf(P[st][ch], e[ch], S[st][ch]);
-        Pack<IO>::store(ty + off0 + st * ROWB, yv);
+        for (int cp = 0; cp < 2; ++cp) yv[cp] = fma2(P[st][cp], e[cp], S[st][cp]);
+        Pack<IO>::store2(ty + off0 + st * ROWB, yv);
       }
     }
     if (USE_TMA) {
-      fence_async_smem();
-      __syncthreads();
-      if (tid == 0) {
-        tma_store_3d(&maps.y, tiles, d0, t0, b);
-        tma_commit();
-        // Refill the stage of the previous chunk once its store has drained from shared memory.
-        const int kp = k - 1;
-        if (kp >= 0 && kp + NSTAGE < nchunks) {
-          tma_wait_read<1>();
-          const int sp = kp % NSTAGE;
-          uint8_t* st = smem + sp * SM::STAGE;
-          const int kn = kp + NSTAGE;
-          mbar_expect_tx(&bars[sp], SM::STAGE);
-          tma_load_3d(st, &maps.x, d0, kn * TC, b, &bars[sp]);
-          tma_load_3d(st + SM::TILE, &maps.ur, d0, kn * TC, b, &bars[sp]);
-          tma_load_3d(st + 2 * SM::TILE, &maps.ui, d0, kn * TC, b, &bars[sp]);
-        }
-      }
+      fence_async_smem();        // make this thread's results visible to the bulk store
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
-      __syncthreads();
-      tile_store_plain<IO>(tiles, p.y, b, t0, d0, TC, p.T, p.D);
-      __syncthreads();
+      bar_compute(NCOMP);
+      tile_store_plain<IO, CH>(tiles, p.y, b, t0, d0, TC, p.T, p.D);
+      bar_compute(NCOMP);
     }
   }
-
-  if (USE_TMA && tid == 0) {
-    tma_wait_all<0>();
-    if (!alive) atomicExch(p.status, DEV_TIMEOUT_LOAD);
-  }
-  if (alive && tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;
+  if (tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;
 }
 
 // ======================================================================
@@ -294,108 +313,114 @@ __global__ void __launch_bounds__(NT) rglru_fwd_kernel(const __grid_constant__ F
 
 template <typename IO, int TS>
 struct BwdRegs {
-  float am[TS][CV];  // decay after masking
-  float hb[TS][CV];  // drive b, later the state entering the step
-  float ar[TS][CV];  // unmasked decay, zeroed where the decay receives no gradient
-  float c1[TS][CV];  // d x      = g * c1
-  float c2[TS][CV];  // d u_i    = g * c2
-  float c3[TS][CV];  // d log a  = g * (h_prev * ar - c3)
-  float rr[TS][CV];  // recurrence gate r
+  float2 am[TS][2];  // decay after masking
+  float2 hb[TS][2];  // drive b, later the state entering the step
+  float2 ar[TS][2];  // unmasked decay, zeroed where the decay receives no gradient
+  float2 c1[TS][2];  // d x      = g * c1
+  float2 c2[TS][2];  // d u_i    = g * c2
+  float2 c3[TS][2];  // d log a  = g * (h_prev * ar + c3)   (c3 <= 0 side of the sqrt slope term)
+  float2 rr[TS][2];  // recurrence gate r
   typename Pack<IO>::Raw dy[TS];
 };
 
-template <typename IO, int TS, bool MASKED, bool POLY>
+// Level one of the backward chunk: gate math, coefficients for the second pass, and the
+// lane aggregates.  aggF = (prod a, local state), aggR = (prod a, local reverse carry),
+// where the reverse carry is a_t g_t flowing from step t to step t-1.
+template <typename IO, int TS, int CH, bool MASKED, bool POLY>
 __device__ __forceinline__ void bwd_local(const uint8_t* tdy, const uint8_t* tx, const uint8_t* tr, const uint8_t* ti,
-                                          int off0, const float (&K)[CV], const uint32_t (&fl)[(TS + 3) / 4],
-                                          BwdRegs<IO, TS>& R, float (&aggF)[2][CV], float (&aggR)[2][CV]) {
+                                          int off0, const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
+                                          BwdRegs<IO, TS>& R, float2 (&prod)[2], float2 (&sfwd)[2],
+                                          float2 (&crev)[2]) {
   constexpr int ROWB = CH * sizeof(IO);
-  float p[CV], s[CV];
-#pragma unroll
-  for (int ch = 0; ch < CV; ++ch) { p[ch] = 1.0f; s[ch] = 0.0f; }
+  float2 p[2] = {f2(1.0f), f2(1.0f)};
+  float2 s[2] = {f2(0.0f), f2(0.0f)};
 #pragma unroll
   for (int st = 0; st < TS; ++st) {
     const int off = off0 + st * ROWB;
-    float xv[CV], rv[CV], iv[CV];
-    Pack<IO>::unpack(Pack<IO>::load(tx + off), xv);
-    Pack<IO>::unpack(Pack<IO>::load(tr + off), rv);
-    Pack<IO>::unpack(Pack<IO>::load(ti + off), iv);
+    float2 xv[2], rv[2], iv[2];
+    Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
+    Pack<IO>::unpack2(Pack<IO>::load(tr + off), rv);
+    Pack<IO>::unpack2(Pack<IO>::load(ti + off), iv);
     R.dy[st] = Pack<IO>::load(tdy + off);
-    const ElemFlags f = elem_flags<MASKED>(fl[st >> 2], st);
+    const RowMask m = row_mask<MASKED>(fl[st >> 2], st);
 #pragma unroll
-    for (int ch = 0; ch < CV; ++ch) {
-      float r, i;
-      sigmoid_pair(rv[ch], iv[ch], r, i);
-      const float em = expm1_nonpos<POLY>(r * K[ch]);
-      const float a = 1.0f + em;
-      const float gsq = fmaxf(-em * (2.0f + em), 0.0f);
-      const float rs = rsqrt_approx(gsq);                 // +inf at 0
-      const float gam = gsq > 0.0f ? gsq * rs : 0.0f;     // sqrt(gsq)
-      const float slope = fminf(0.5f * rs, SLOPE_CAP);    // 1/sqrt(max(4 gsq, 1e-6))
-      const float ix = i * xv[ch];
-      float am = a, ar = a;
-      float c1 = gam * i;
-      float b = gam * ix;
-      float c3 = (a * a) * (2.0f * slope) * ix;
+    for (int cp = 0; cp < 2; ++cp) {
+      float2 r, i;
+      sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
+      const float2 e = one_minus_exp_neg2<POLY>(mul2(r, K[cp]));       // 1 - a
+      const float2 a = fma2(e, f2(-1.0f), f2(1.0f));
+      float2 gsq = mul2(e, fma2(e, f2(-1.0f), f2(2.0f)));               // 1 - a^2
+      // The floor keeps rsqrt finite; it changes gamma by at most 1e-15.
+      gsq = make_float2(fmaxf(gsq.x, 1e-30f), fmaxf(gsq.y, 1e-30f));
+      const float2 rs = make_float2(rsqrt_approx(gsq.x), rsqrt_approx(gsq.y));
+      float2 gam = mul2(gsq, rs);                                       // sqrt(gsq)
+      // 2 * slope, slope = 1 / sqrt(max(4 gsq, 1e-6)) = min(rs / 2, 1000)
+      const float2 rs2 = make_float2(fminf(rs.x, 2.0f * SLOPE_CAP), fminf(rs.y, 2.0f * SLOPE_CAP));
+      const float2 ix = mul2(i, xv[cp]);
+      float2 am = a, ar = a;
+      float2 c3 = mul2(mul2(a, a), mul2(rs2, mul2(ix, f2(-1.0f))));   // stored negated
       if (MASKED) {
-        if (f.reset) { am = 0.0f; ar = 0.0f; c3 = 0.0f; c1 = i; b = ix; }
-        if (f.inactive) { am = 1.0f; ar = 0.0f; c3 = 0.0f; c1 = 0.0f; b = 0.0f; }
+        const float kl = m.keep * m.live;
+        am = fma2(mul2(a, f2(m.keep)), f2(m.live), f2(1.0f - m.live));
+        ar = mul2(a, f2(kl));
+        c3 = mul2(c3, f2(kl));
+        gam = mul2(fma2(gam, f2(m.keep), f2(1.0f - m.keep)), f2(m.live));
       }
-      R.am[st][ch] = am;
-      R.ar[st][ch] = ar;
-      R.c1[st][ch] = c1;
-      R.c2[st][ch] = b * (1.0f - i);
-      R.c3[st][ch] = c3;
-      R.rr[st][ch] = r;
-      R.hb[st][ch] = b;
-      p[ch] *= am;
-      s[ch] = fmaf(am, s[ch], b);
+      const float2 c1 = mul2(gam, i);
+      const float2 bb = mul2(gam, ix);
+      R.am[st][cp] = am;
+      R.ar[st][cp] = ar;
+      R.c1[st][cp] = c1;
+      R.c2[st][cp] = mul2(bb, fma2(i, f2(-1.0f), f2(1.0f)));
+      R.c3[st][cp] = c3;
+      R.rr[st][cp] = r;
+      R.hb[st][cp] = bb;
+      p[cp] = mul2(p[cp], am);
+      s[cp] = fma2(am, s[cp], bb);
     }
   }
-#pragma unroll
-  for (int ch = 0; ch < CV; ++ch) { aggF[0][ch] = p[ch]; aggF[1][ch] = s[ch]; }
-  // Reverse aggregate: carry_out = q * carry_in + c, where the carry is a_t g_t.
-  float q[CV], c[CV];
-#pragma unroll
-  for (int ch = 0; ch < CV; ++ch) { q[ch] = 1.0f; c[ch] = 0.0f; }
+  float2 c[2] = {f2(0.0f), f2(0.0f)};
 #pragma unroll
   for (int st = TS - 1; st >= 0; --st) {
-    float dyv[CV];
-    Pack<IO>::unpack(R.dy[st], dyv);
+    float2 dyv[2];
+    Pack<IO>::unpack2(R.dy[st], dyv);
 #pragma unroll
-    for (int ch = 0; ch < CV; ++ch) {
-      c[ch] = R.am[st][ch] * (dyv[ch] + c[ch]);
-      q[ch] *= R.am[st][ch];
-    }
+    for (int cp = 0; cp < 2; ++cp) c[cp] = mul2(R.am[st][cp], add2(dyv[cp], c[cp]));
   }
 #pragma unroll
-  for (int ch = 0; ch < CV; ++ch) { aggR[0][ch] = q[ch]; aggR[1][ch] = c[ch]; }
+  for (int cp = 0; cp < 2; ++cp) { prod[cp] = p[cp]; sfwd[cp] = s[cp]; crev[cp] = c[cp]; }
 }
 
-template <typename IO, int TS, int NSTAGE>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE>
 struct BwdSmem {
   static constexpr int TC = LANES * TS;
   static constexpr int TILE = TC * CH * sizeof(IO);
   static constexpr int STAGE = 4 * TILE;
   static constexpr int OFF_AGGF = NSTAGE * STAGE;
-  static constexpr int OFF_AGGR = OFF_AGGF + LANES * CH * 8;
-  static constexpr int OFF_EINF = OFF_AGGR + LANES * CH * 8;
-  static constexpr int OFF_EINR = OFF_EINF + LANES * CH * 4;
-  static constexpr int OFF_BAR = OFF_EINR + LANES * CH * 4;
-  static constexpr int BYTES = OFF_BAR + NSTAGE * 8 + 16;
+  static constexpr int OFF_AGGR = OFF_AGGF + ChainSmem<LANES, CH>::AGG;
+  static constexpr int OFF_EINF = OFF_AGGR + ChainSmem<LANES, CH>::AGG;
+  static constexpr int OFF_EINR = OFF_EINF + ChainSmem<LANES, CH>::EIN;
+  static constexpr int OFF_BAR = OFF_EINR + ChainSmem<LANES, CH>::EIN;   // full[NSTAGE], ready[NSTAGE], dead flag
+  static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-template <typename IO, int TS, int NSTAGE, bool USE_TMA>
-__global__ void __launch_bounds__(NT) rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
-  using SM = BwdSmem<IO, TS, NSTAGE>;
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, int MINB>
+__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
+    rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
+  using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE>;
+  constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
-  static_assert(TC == SAVE_EVERY, "backward chunk must match the saved-state spacing");
+  static_assert(TC % SAVE_EVERY == 0, "backward chunks must start on a saved state");
   constexpr int ROWB = CH * sizeof(IO);
+  constexpr int NCOMP = LANES * NCV;
   extern __shared__ __align__(128) uint8_t smem[];
   float2* aggF = reinterpret_cast<float2*>(smem + SM::OFF_AGGF);
   float2* aggR = reinterpret_cast<float2*>(smem + SM::OFF_AGGR);
   float* einF = reinterpret_cast<float*>(smem + SM::OFF_EINF);
   float* einR = reinterpret_cast<float*>(smem + SM::OFF_EINR);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+  uint64_t* ready = full + NSTAGE;
+  volatile int* dead = reinterpret_cast<volatile int*>(ready + NSTAGE);
 
   const int tid = threadIdx.x;
   const int lane_t = tid / NCV;
@@ -403,37 +428,56 @@ __global__ void __launch_bounds__(NT) rglru_bwd_kernel(const __grid_constant__ B
   const int b = blockIdx.y;
   const int d0 = blockIdx.x * CH;
   const int nchunks = (p.T + TC - 1) / TC;
+  const int nsave = (p.T + SAVE_EVERY - 1) / SAVE_EVERY;
 
-  float K[CV];
-  bool poly_ok = true;
-#pragma unroll
-  for (int ch = 0; ch < CV; ++ch) {
-    K[ch] = decay_rate(p.lambda, d0 + vec * CV + ch, p.D, p.c);
-    poly_ok = poly_ok && (K[ch] >= POLY_RANGE);
+  float2 K[2];
+  {
+    const int d = d0 + vec * CV;
+    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
+    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
   }
-  const bool poly = __syncthreads_and(poly_ok);
-
-  auto issue = [&](int q) {  // q-th chunk in processing order == chunk nchunks-1-q in time
-    const int k = nchunks - 1 - q;
-    const int sidx = q % NSTAGE;
-    uint8_t* st = smem + sidx * SM::STAGE;
-    mbar_expect_tx(&bars[sidx], SM::STAGE);
-    tma_load_3d(st, &maps.dy, d0, k * TC, b, &bars[sidx]);
-    tma_load_3d(st + SM::TILE, &maps.x, d0, k * TC, b, &bars[sidx]);
-    tma_load_3d(st + 2 * SM::TILE, &maps.ur, d0, k * TC, b, &bars[sidx]);
-    tma_load_3d(st + 3 * SM::TILE, &maps.ui, d0, k * TC, b, &bars[sidx]);
-  };
-
-  if (USE_TMA) {
-    if (tid == 0) {
-      prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
-      prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
-      for (int s = 0; s < NSTAGE; ++s) mbar_init(&bars[s], 1);
+  if (tid == 0) {
+    *dead = 0;
+    if (USE_TMA) {
+      for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
       mbar_fence_init();
     }
-    __syncthreads();
-    if (tid == 0)
+  }
+  const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
+
+  if (USE_TMA && tid >= NCOMP) {
+    // ---- producer warp (chunks are walked from the end of the sequence to its start)
+    if (tid == NCOMP) {
+      prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
+      prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
+      auto issue = [&](int q) {  // q-th chunk in processing order == chunk nchunks-1-q in time
+        const int k = nchunks - 1 - q;
+        const int sidx = q % NSTAGE;
+        uint8_t* st = smem + sidx * SM::STAGE;
+        mbar_expect_tx(&full[sidx], SM::STAGE);
+        tma_load_3d(st, &maps.dy, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::TILE, &maps.x, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + 2 * SM::TILE, &maps.ur, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + 3 * SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
+      };
       for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
+      for (int q = 0; q < nchunks; ++q) {
+        const int k = nchunks - 1 - q;
+        const int sidx = q % NSTAGE;
+        uint8_t* st = smem + sidx * SM::STAGE;
+        mbar_wait_or_flag(&ready[sidx], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
+        tma_store_3d(&maps.dx, st + SM::TILE, d0, k * TC, b);
+        tma_store_3d(&maps.dur, st + 2 * SM::TILE, d0, k * TC, b);
+        tma_store_3d(&maps.dui, st + 3 * SM::TILE, d0, k * TC, b);
+        tma_commit();
+        if (q + NSTAGE < nchunks) {
+          tma_wait_read<0>();
+          issue(q + NSTAGE);
+        }
+      }
+      tma_wait_all<0>();
+    }
+    return;
   }
 
   // Threads 0..63 chain the forward lane aggregates, threads 64..127 the reverse ones.
@@ -444,9 +488,8 @@ __global__ void __launch_bounds__(NT) rglru_bwd_kernel(const __grid_constant__ B
   float carry_rev = 0.0f;
   if (rev_chain && dch < p.D && p.dh_last) carry_rev = p.dh_last[static_cast<size_t>(b) * p.D + dch];
 
-  float dlam[CV] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float2 dlam[2] = {f2(0.0f), f2(0.0f)};
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
-  bool alive = true;
 
   for (int q = 0; q < nchunks; ++q) {
     const int k = nchunks - 1 - q;
@@ -461,44 +504,43 @@ __global__ void __launch_bounds__(NT) rglru_bwd_kernel(const __grid_constant__ B
     float enter = 0.0f;
     if (fwd_chain && dch < p.D) {
       if (k == 0) enter = p.h0 ? p.h0[static_cast<size_t>(b) * p.D + dch] : 0.0f;
-      else enter = p.states[(static_cast<size_t>(b) * nchunks + k) * p.D + dch];
+      else enter = p.states[(static_cast<size_t>(b) * nsave + t0 / SAVE_EVERY) * p.D + dch];
     }
 
     if (USE_TMA) {
-      alive = mbar_wait_bounded(&bars[stage], (q / NSTAGE) & 1);
+      mbar_wait_or_flag(&full[stage], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
     } else {
-      tile_load_plain<IO>(tiles, p.dy, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO>(tiles + SM::TILE, p.x, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO>(tiles + 2 * SM::TILE, p.ur, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO>(tiles + 3 * SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
-      __syncthreads();
+      tile_load_plain<IO, CH>(tiles, p.dy, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::TILE, p.x, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + 2 * SM::TILE, p.ur, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + 3 * SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
+      bar_compute(NCOMP);
     }
 
     BwdRegs<IO, TS> R;
-    float lf[2][CV], lr[2][CV];
+    float2 prod[2], sfwd[2], crev[2];
     {
       const uint8_t* tdy = tiles;
       const uint8_t* tx = tiles + SM::TILE;
       const uint8_t* tr = tiles + 2 * SM::TILE;
       const uint8_t* ti = tiles + 3 * SM::TILE;
       if (masked) {
-        if (poly) bwd_local<IO, TS, true, true>(tdy, tx, tr, ti, off0, K, fl, R, lf, lr);
-        else bwd_local<IO, TS, true, false>(tdy, tx, tr, ti, off0, K, fl, R, lf, lr);
+        if (poly) bwd_local<IO, TS, CH, true, true>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, true, false>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
       } else {
-        if (poly) bwd_local<IO, TS, false, true>(tdy, tx, tr, ti, off0, K, fl, R, lf, lr);
-        else bwd_local<IO, TS, false, false>(tdy, tx, tr, ti, off0, K, fl, R, lf, lr);
+        if (poly) bwd_local<IO, TS, CH, false, true>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, false, false>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
       }
     }
     {
       float4* df = reinterpret_cast<float4*>(aggF + lane_t * CH + vec * CV);
-      df[0] = make_float4(lf[0][0], lf[1][0], lf[0][1], lf[1][1]);
-      df[1] = make_float4(lf[0][2], lf[1][2], lf[0][3], lf[1][3]);
+      df[0] = make_float4(prod[0].x, sfwd[0].x, prod[0].y, sfwd[0].y);
+      df[1] = make_float4(prod[1].x, sfwd[1].x, prod[1].y, sfwd[1].y);
       float4* dr = reinterpret_cast<float4*>(aggR + lane_t * CH + vec * CV);
-      dr[0] = make_float4(lr[0][0], lr[1][0], lr[0][1], lr[1][1]);
-      dr[1] = make_float4(lr[0][2], lr[1][2], lr[0][3], lr[1][3]);
+      dr[0] = make_float4(prod[0].x, crev[0].x, prod[0].y, crev[0].y);
+      dr[1] = make_float4(prod[1].x, crev[1].x, prod[1].y, crev[1].y);
     }
-    alive = __syncthreads_and(alive);
-    if (!alive) break;
+    bar_compute(NCOMP);
 
     if (fwd_chain) {
       float2 ag[LANES];
@@ -522,81 +564,68 @@ __global__ void __launch_bounds__(NT) rglru_bwd_kernel(const __grid_constant__ B
       }
       carry_rev = e;
     }
-    __syncthreads();
+    bar_compute(NCOMP);
 
     {
       const float4 f4 = *reinterpret_cast<const float4*>(einF + lane_t * CH + vec * CV);
       const float4 r4 = *reinterpret_cast<const float4*>(einR + lane_t * CH + vec * CV);
-      float h[CV] = {f4.x, f4.y, f4.z, f4.w};
-      float c[CV] = {r4.x, r4.y, r4.z, r4.w};
+      float2 h[2] = {make_float2(f4.x, f4.y), make_float2(f4.z, f4.w)};
+      float2 c[2] = {make_float2(r4.x, r4.y), make_float2(r4.z, r4.w)};
       // States entering each step, rebuilt forward in time.
 #pragma unroll
       for (int st = 0; st < TS; ++st) {
 #pragma unroll
-        for (int ch = 0; ch < CV; ++ch) {
-          const float hin = h[ch];
-          h[ch] = fmaf(R.am[st][ch], hin, R.hb[st][ch]);
-          R.hb[st][ch] = hin;
+        for (int cp = 0; cp < 2; ++cp) {
+          const float2 hin = h[cp];
+          h[cp] = fma2(R.am[st][cp], hin, R.hb[st][cp]);
+          R.hb[st][cp] = hin;
         }
       }
       uint8_t* tdx = tiles + SM::TILE;       // over x
       uint8_t* tdr = tiles + 2 * SM::TILE;   // over u_r
       uint8_t* tdi = tiles + 3 * SM::TILE;   // over u_i
+      const float2 nK[2] = {mul2(K[0], f2(-1.0f)), mul2(K[1], f2(-1.0f))};
 #pragma unroll
       for (int st = TS - 1; st >= 0; --st) {
-        float dyv[CV], dxv[CV], drv[CV], div[CV];
-        Pack<IO>::unpack(R.dy[st], dyv);
+        float2 dyv[2], dxv[2], drv[2], div[2];
+        Pack<IO>::unpack2(R.dy[st], dyv);
 #pragma unroll
-        for (int ch = 0; ch < CV; ++ch) {
-          const float g = dyv[ch] + c[ch];
-          c[ch] = R.am[st][ch] * g;
-          dxv[ch] = g * R.c1[st][ch];
-          div[ch] = g * R.c2[st][ch];
-          const float dl = g * fmaf(R.hb[st][ch], R.ar[st][ch], -R.c3[st][ch]);
-          const float w = dl * R.rr[st][ch];
-          dlam[ch] += w;
-          drv[ch] = w * fmaf(-K[ch], R.rr[st][ch], K[ch]);
+        for (int cp = 0; cp < 2; ++cp) {
+          const float2 g = add2(dyv[cp], c[cp]);
+          c[cp] = mul2(R.am[st][cp], g);
+          dxv[cp] = mul2(g, R.c1[st][cp]);
+          div[cp] = mul2(g, R.c2[st][cp]);
+          const float2 dl = mul2(g, fma2(R.hb[st][cp], R.ar[st][cp], R.c3[st][cp]));   // c3 is stored negated
+          const float2 w = mul2(dl, R.rr[st][cp]);
+          dlam[cp] = add2(dlam[cp], w);
+          // d u_r = dl * d(log a)/d u_r = dl * (-K) r (1 - r) with K = -c logsigmoid(Lambda) >= 0
+          drv[cp] = mul2(w, fma2(K[cp], R.rr[st][cp], nK[cp]));
         }
         const int off = off0 + st * ROWB;
-        Pack<IO>::store(tdx + off, dxv);
-        Pack<IO>::store(tdr + off, drv);
-        Pack<IO>::store(tdi + off, div);
+        Pack<IO>::store2(tdx + off, dxv);
+        Pack<IO>::store2(tdr + off, drv);
+        Pack<IO>::store2(tdi + off, div);
       }
     }
     if (USE_TMA) {
       fence_async_smem();
-      __syncthreads();
-      if (tid == 0) {
-        tma_store_3d(&maps.dx, tiles + SM::TILE, d0, t0, b);
-        tma_store_3d(&maps.dur, tiles + 2 * SM::TILE, d0, t0, b);
-        tma_store_3d(&maps.dui, tiles + 3 * SM::TILE, d0, t0, b);
-        tma_commit();
-        const int qp = q - 1;
-        if (qp >= 0 && qp + NSTAGE < nchunks) {
-          tma_wait_read<1>();
-          issue(qp + NSTAGE);
-        }
-      }
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
-      __syncthreads();
-      tile_store_plain<IO>(tiles + SM::TILE, p.dx, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<IO>(tiles + 2 * SM::TILE, p.dur, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<IO>(tiles + 3 * SM::TILE, p.dui, b, t0, d0, TC, p.T, p.D);
-      __syncthreads();
+      bar_compute(NCOMP);
+      tile_store_plain<IO, CH>(tiles + SM::TILE, p.dx, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<IO, CH>(tiles + 2 * SM::TILE, p.dur, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<IO, CH>(tiles + 3 * SM::TILE, p.dui, b, t0, d0, TC, p.T, p.D);
+      bar_compute(NCOMP);
     }
   }
 
-  if (USE_TMA && tid == 0) {
-    tma_wait_all<0>();
-    if (!alive) atomicExch(p.status, DEV_TIMEOUT_LOAD);
-  }
-  if (!alive) return;
   if (rev_chain && dch < p.D && p.dh0) p.dh0[static_cast<size_t>(b) * p.D + dch] = carry_rev;
 
-  // Per-row partial of sum_t dl * r: fold the 16 time-lanes in a fixed order.
-  __syncthreads();
-  *reinterpret_cast<float4*>(einF + lane_t * CH + vec * CV) = make_float4(dlam[0], dlam[1], dlam[2], dlam[3]);
-  __syncthreads();
+  // Per-row partial of sum_t dl * r: fold the time-lanes in a fixed order.
+  bar_compute(NCOMP);
+  *reinterpret_cast<float4*>(einF + lane_t * CH + vec * CV) = make_float4(dlam[0].x, dlam[0].y, dlam[1].x, dlam[1].y);
+  bar_compute(NCOMP);
   if (tid < CH && dch < p.D) {
     float acc = 0.0f;
 #pragma unroll
@@ -605,7 +634,8 @@ __global__ void __launch_bounds__(NT) rglru_bwd_kernel(const __grid_constant__ B
   }
 }
 
-// dLambda[d] = sigmoid(-Lambda_d) * c * sum_b partial[b, d], rows added in index order.
+// dLambda[d] = d/dLambda of sum dl * r * c * logsigmoid(Lambda) = sigmoid(-Lambda_d) * c * sum_b partial[b, d],
+// rows added in index order.
 __global__ void rglru_dlambda_kernel(const float* __restrict__ part, const float* __restrict__ lambda,
                                      float* __restrict__ dlambda, int B, int D, float c) {
   const int d = blockIdx.x * blockDim.x + threadIdx.x;
@@ -622,8 +652,12 @@ __global__ void rglru_dlambda_kernel(const float* __restrict__ part, const float
 // for griffin/triton_scan.py:274-276).  Same two-level structure, no gate math.
 // ======================================================================
 
+constexpr int CH = 64;
+constexpr int NCV = CH / CV;
 constexpr int RAW_TS = 4;
-constexpr int RAW_TC = LANES * RAW_TS;
+constexpr int RAW_LANES = 16;
+constexpr int RAW_NT = RAW_LANES * NCV;
+constexpr int RAW_TC = RAW_LANES * RAW_TS;
 constexpr int RAW_TILE = RAW_TC * CH * 4;
 
 template <int NSTAGE>
@@ -631,15 +665,15 @@ struct RawSmem {
   static constexpr int NTILE = 3;
   static constexpr int STAGE = NTILE * RAW_TILE;
   static constexpr int OFF_AGG = NSTAGE * STAGE;
-  static constexpr int OFF_EIN = OFF_AGG + LANES * CH * 8;
-  static constexpr int OFF_BAR = OFF_EIN + LANES * CH * 4;
+  static constexpr int OFF_EIN = OFF_AGG + ChainSmem<RAW_LANES, CH>::AGG;
+  static constexpr int OFF_BAR = OFF_EIN + ChainSmem<RAW_LANES, CH>::EIN;
   static constexpr int BYTES = OFF_BAR + NSTAGE * 8 + 16;
 };
 
 template <int NSTAGE, bool USE_TMA>
-__global__ void __launch_bounds__(NT) rawscan_fwd_kernel(const __grid_constant__ RawFwdMaps maps, const RawScanArgs p) {
+__global__ void __launch_bounds__(RAW_NT) rawscan_fwd_kernel(const __grid_constant__ RawFwdMaps maps, const RawScanArgs p) {
   using SM = RawSmem<NSTAGE>;
-  constexpr int TS = RAW_TS, TC = RAW_TC, ROWB = CH * 4;
+  constexpr int TS = RAW_TS, TC = RAW_TC, ROWB = CH * 4, LANES = RAW_LANES;
   extern __shared__ __align__(128) uint8_t smem[];
   float2* agg = reinterpret_cast<float2*>(smem + SM::OFF_AGG);
   float* ein = reinterpret_cast<float*>(smem + SM::OFF_EIN);
@@ -677,34 +711,34 @@ __global__ void __launch_bounds__(NT) rawscan_fwd_kernel(const __grid_constant__
     if (USE_TMA) {
       alive = mbar_wait_bounded(&bars[stage], (k / NSTAGE) & 1);
     } else {
-      tile_load_plain<float>(tiles, p.drive, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<float>(tiles + RAW_TILE, p.decay, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<float, CH>(tiles, p.drive, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<float, CH>(tiles + RAW_TILE, p.decay, b, t0, d0, TC, p.T, p.D);
       __syncthreads();
     }
-    float P[TS][CV], S[TS][CV];
+    float2 P[TS][2], S[TS][2];
     {
-      float pp[CV] = {1.0f, 1.0f, 1.0f, 1.0f}, ss[CV] = {0.0f, 0.0f, 0.0f, 0.0f};
+      float2 pp[2] = {f2(1.0f), f2(1.0f)}, ss[2] = {f2(0.0f), f2(0.0f)};
 #pragma unroll
       for (int st = 0; st < TS; ++st) {
-        float bv[CV], av[CV];
-        Pack<float>::unpack(Pack<float>::load(tiles + off0 + st * ROWB), bv);
-        Pack<float>::unpack(Pack<float>::load(tiles + RAW_TILE + off0 + st * ROWB), av);
-        const bool pad = t0 + lane_t * TS + st >= p.T;  // steps past T carry the state through
+        float2 bv[2], av[2];
+        Pack<float>::unpack2(Pack<float>::load(tiles + off0 + st * ROWB), bv);
+        Pack<float>::unpack2(Pack<float>::load(tiles + RAW_TILE + off0 + st * ROWB), av);
+        const float live = (t0 + lane_t * TS + st < p.T) ? 1.0f : 0.0f;  // steps past T carry the state through
 #pragma unroll
-        for (int ch = 0; ch < CV; ++ch) {
-          const float a = pad ? 1.0f : av[ch];
-          const float bb = pad ? 0.0f : bv[ch];
-          pp[ch] *= a;
-          ss[ch] = fmaf(a, ss[ch], bb);
-          P[st][ch] = pp[ch];
-          S[st][ch] = ss[ch];
+        for (int cp = 0; cp < 2; ++cp) {
+          const float2 a = fma2(av[cp], f2(live), f2(1.0f - live));
+          const float2 bb = mul2(bv[cp], f2(live));
+          pp[cp] = mul2(pp[cp], a);
+          ss[cp] = fma2(a, ss[cp], bb);
+          P[st][cp] = pp[cp];
+          S[st][cp] = ss[cp];
         }
       }
     }
     {
       float4* dst = reinterpret_cast<float4*>(agg + lane_t * CH + vec * CV);
-      dst[0] = make_float4(P[TS - 1][0], S[TS - 1][0], P[TS - 1][1], S[TS - 1][1]);
-      dst[1] = make_float4(P[TS - 1][2], S[TS - 1][2], P[TS - 1][3], S[TS - 1][3]);
+      dst[0] = make_float4(P[TS - 1][0].x, S[TS - 1][0].x, P[TS - 1][0].y, S[TS - 1][0].y);
+      dst[1] = make_float4(P[TS - 1][1].x, S[TS - 1][1].x, P[TS - 1][1].y, S[TS - 1][1].y);
     }
     alive = __syncthreads_and(alive);
     if (!alive) break;
@@ -723,13 +757,13 @@ __global__ void __launch_bounds__(NT) rawscan_fwd_kernel(const __grid_constant__
     __syncthreads();
     {
       const float4 e4 = *reinterpret_cast<const float4*>(ein + lane_t * CH + vec * CV);
-      const float e[CV] = {e4.x, e4.y, e4.z, e4.w};
+      const float2 e[2] = {make_float2(e4.x, e4.y), make_float2(e4.z, e4.w)};
 #pragma unroll
       for (int st = 0; st < TS; ++st) {
-        float yv[CV];
+        float2 yv[2];
 #pragma unroll
-        for (int ch = 0; ch < CV; ++ch) yv[ch] = fmaf(P[st][ch], e[ch], S[st][ch]);
-        Pack<float>::store(tiles + off0 + st * ROWB, yv);
+        for (int cp = 0; cp < 2; ++cp) yv[cp] = fma2(P[st][cp], e[cp], S[st][cp]);
+        Pack<float>::store2(tiles + off0 + st * ROWB, yv);
       }
     }
     if (USE_TMA) {
@@ -746,7 +780,7 @@ __global__ void __launch_bounds__(NT) rawscan_fwd_kernel(const __grid_constant__
       }
     } else {
       __syncthreads();
-      tile_store_plain<float>(tiles, p.out, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<float, CH>(tiles, p.out, b, t0, d0, TC, p.T, p.D);
       __syncthreads();
     }
   }
@@ -759,9 +793,9 @@ __global__ void __launch_bounds__(NT) rawscan_fwd_kernel(const __grid_constant__
 // Backward of the raw scan.  Tiles per chunk: d_out, decay, and the forward output
 // shifted one step back in time (row t holds h_{t-1}; the row before t = 0 is h0).
 template <int NSTAGE, bool USE_TMA>
-__global__ void __launch_bounds__(NT) rawscan_bwd_kernel(const __grid_constant__ RawBwdMaps maps, const RawScanArgs p) {
+__global__ void __launch_bounds__(RAW_NT) rawscan_bwd_kernel(const __grid_constant__ RawBwdMaps maps, const RawScanArgs p) {
   using SM = RawSmem<NSTAGE>;
-  constexpr int TS = RAW_TS, TC = RAW_TC, ROWB = CH * 4;
+  constexpr int TS = RAW_TS, TC = RAW_TC, ROWB = CH * 4, LANES = RAW_LANES;
   extern __shared__ __align__(128) uint8_t smem[];
   float2* agg = reinterpret_cast<float2*>(smem + SM::OFF_AGG);
   float* ein = reinterpret_cast<float*>(smem + SM::OFF_EIN);
@@ -801,37 +835,40 @@ __global__ void __launch_bounds__(NT) rawscan_bwd_kernel(const __grid_constant__
     if (USE_TMA) {
       alive = mbar_wait_bounded(&bars[stage], (q / NSTAGE) & 1);
     } else {
-      tile_load_plain<float>(tiles, p.dout, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<float>(tiles + RAW_TILE, p.decay, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<float>(tiles + 2 * RAW_TILE, p.out_in, b, t0 - 1, d0, TC, p.T, p.D);
+      tile_load_plain<float, CH>(tiles, p.dout, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<float, CH>(tiles + RAW_TILE, p.decay, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<float, CH>(tiles + 2 * RAW_TILE, p.out_in, b, t0 - 1, d0, TC, p.T, p.D);
       __syncthreads();
     }
-    float av[TS][CV], gv[TS][CV], hv[TS][CV];
-    float qq[CV] = {1.0f, 1.0f, 1.0f, 1.0f}, cc[CV] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float2 av[TS][2], gv[TS][2], hv[TS][2];
+    float2 qq[2] = {f2(1.0f), f2(1.0f)}, cc[2] = {f2(0.0f), f2(0.0f)};
 #pragma unroll
     for (int st = 0; st < TS; ++st) {
-      Pack<float>::unpack(Pack<float>::load(tiles + off0 + st * ROWB), gv[st]);
-      Pack<float>::unpack(Pack<float>::load(tiles + RAW_TILE + off0 + st * ROWB), av[st]);
-      Pack<float>::unpack(Pack<float>::load(tiles + 2 * RAW_TILE + off0 + st * ROWB), hv[st]);
+      Pack<float>::unpack2(Pack<float>::load(tiles + off0 + st * ROWB), gv[st]);
+      Pack<float>::unpack2(Pack<float>::load(tiles + RAW_TILE + off0 + st * ROWB), av[st]);
+      Pack<float>::unpack2(Pack<float>::load(tiles + 2 * RAW_TILE + off0 + st * ROWB), hv[st]);
     }
     if (k == 0 && lane_t == 0) {  // the state entering t = 0
+      float h0v[CV];
 #pragma unroll
       for (int ch = 0; ch < CV; ++ch) {
         const int d = d0 + vec * CV + ch;
-        hv[0][ch] = (p.h0 && d < p.D) ? p.h0[static_cast<size_t>(b) * p.D + d] : 0.0f;
+        h0v[ch] = (p.h0 && d < p.D) ? p.h0[static_cast<size_t>(b) * p.D + d] : 0.0f;
       }
+      hv[0][0] = make_float2(h0v[0], h0v[1]);
+      hv[0][1] = make_float2(h0v[2], h0v[3]);
     }
 #pragma unroll
     for (int st = TS - 1; st >= 0; --st)
 #pragma unroll
-      for (int ch = 0; ch < CV; ++ch) {
-        cc[ch] = av[st][ch] * (gv[st][ch] + cc[ch]);
-        qq[ch] *= av[st][ch];
+      for (int cp = 0; cp < 2; ++cp) {
+        cc[cp] = mul2(av[st][cp], add2(gv[st][cp], cc[cp]));
+        qq[cp] = mul2(qq[cp], av[st][cp]);
       }
     {
       float4* dst = reinterpret_cast<float4*>(agg + lane_t * CH + vec * CV);
-      dst[0] = make_float4(qq[0], cc[0], qq[1], cc[1]);
-      dst[1] = make_float4(qq[2], cc[2], qq[3], cc[3]);
+      dst[0] = make_float4(qq[0].x, cc[0].x, qq[0].y, cc[0].y);
+      dst[1] = make_float4(qq[1].x, cc[1].x, qq[1].y, cc[1].y);
     }
     alive = __syncthreads_and(alive);
     if (!alive) break;
@@ -850,19 +887,19 @@ __global__ void __launch_bounds__(NT) rawscan_bwd_kernel(const __grid_constant__
     __syncthreads();
     {
       const float4 e4 = *reinterpret_cast<const float4*>(ein + lane_t * CH + vec * CV);
-      float c[CV] = {e4.x, e4.y, e4.z, e4.w};
+      float2 c[2] = {make_float2(e4.x, e4.y), make_float2(e4.z, e4.w)};
 #pragma unroll
       for (int st = TS - 1; st >= 0; --st) {
-        float da[CV], db[CV];
+        float2 da[2], db[2];
 #pragma unroll
-        for (int ch = 0; ch < CV; ++ch) {
-          const float g = gv[st][ch] + c[ch];
-          c[ch] = av[st][ch] * g;
-          db[ch] = g;
-          da[ch] = g * hv[st][ch];
+        for (int cp = 0; cp < 2; ++cp) {
+          const float2 g = add2(gv[st][cp], c[cp]);
+          c[cp] = mul2(av[st][cp], g);
+          db[cp] = g;
+          da[cp] = mul2(g, hv[st][cp]);
         }
-        Pack<float>::store(tiles + off0 + st * ROWB, db);
-        Pack<float>::store(tiles + RAW_TILE + off0 + st * ROWB, da);
+        Pack<float>::store2(tiles + off0 + st * ROWB, db);
+        Pack<float>::store2(tiles + RAW_TILE + off0 + st * ROWB, da);
       }
     }
     if (USE_TMA) {
@@ -880,8 +917,8 @@ __global__ void __launch_bounds__(NT) rawscan_bwd_kernel(const __grid_constant__
       }
     } else {
       __syncthreads();
-      tile_store_plain<float>(tiles, p.ddrive, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<float>(tiles + RAW_TILE, p.ddecay, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<float, CH>(tiles, p.ddrive, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<float, CH>(tiles + RAW_TILE, p.ddecay, b, t0, d0, TC, p.T, p.D);
       __syncthreads();
     }
   }
@@ -896,63 +933,118 @@ __global__ void __launch_bounds__(NT) rawscan_bwd_kernel(const __grid_constant__
 // Launchers
 // ======================================================================
 
-constexpr int FWD_TS = 4;
-constexpr int BWD_TS = 4;
-constexpr int FWD_STAGES_BF16 = 4, FWD_STAGES_F32 = 3;
-constexpr int BWD_STAGES_BF16 = 3, BWD_STAGES_F32 = 2;
+// CTA shapes.  CH channels x (LANES * TS) time-steps per chunk, LANES * CH / 4 compute threads.
+//   64 x 64 : the default; grids large enough to put two or more CTAs on every SM.
+//   32 x .. : half-width tiles double the number of CTAs for small grids, so that two CTAs
+//             (two independent barrier domains) still share an SM and overlap their phases.
+struct Shape64x16x4 { static constexpr int CH = 64, LANES = 16, TS = 4; };
+struct Shape64x32x4 { static constexpr int CH = 64, LANES = 32, TS = 4; };
+struct Shape32x32x4 { static constexpr int CH = 32, LANES = 32, TS = 4; };
+struct Shape32x16x4 { static constexpr int CH = 32, LANES = 16, TS = 4; };
+struct Shape64x32x2 { static constexpr int CH = 64, LANES = 32, TS = 2; };
 
-int scan_fwd_box_rows(bool) { return LANES * FWD_TS; }
-int scan_bwd_box_rows(bool) { return LANES * BWD_TS; }
+constexpr int NUM_VARIANTS = 4;
+static const int kFwdRows[NUM_VARIANTS] = {64, 64, 128, 64};
+static const int kFwdCols[NUM_VARIANTS] = {64, 64, 32, 32};
+static const int kBwdRows[NUM_VARIANTS] = {64, 64, 64, 64};
+static const int kBwdCols[NUM_VARIANTS] = {64, 64, 32, 32};
+
+int scan_fwd_box_rows(int v) { return kFwdRows[v]; }
+int scan_fwd_box_cols(int v) { return kFwdCols[v]; }
+int scan_bwd_box_rows(int v) { return kBwdRows[v]; }
+int scan_bwd_box_cols(int v) { return kBwdCols[v]; }
+
+static int env_override(const char* name) {
+  const char* v = getenv(name);
+  return (v && v[0] >= '0' && v[0] < '0' + NUM_VARIANTS) ? (v[0] - '0') : -1;
+}
+
+// RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT force a shape (for tuning runs).
+int scan_fwd_variant(int B, int T, int D) {
+  static const int forced = env_override("RGLRU_FWD_VARIANT");
+  if (forced >= 0) return forced;
+  const long long ctas = static_cast<long long>(B) * ((D + 63) / 64);
+  return (ctas < 2 * 148 && T >= 256) ? 2 : 0;
+}
+int scan_bwd_variant(int B, int T, int D) {
+  static const int forced = env_override("RGLRU_BWD_VARIANT");
+  if (forced >= 0) return forced;
+  const long long ctas = static_cast<long long>(B) * ((D + 63) / 64);
+  return (ctas < 2 * 148 && T >= 256) ? 2 : 0;
+}
 
 template <typename Kern>
 static cudaError_t set_smem(Kern kern, int bytes) {
+  // Ask for the largest shared-memory carveout so that occupancy is set by the kernel's own
+  // footprint, not by the default L1 / shared split.
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return e;
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-template <typename IO, int NSTAGE, bool USE_TMA>
+template <typename IO, typename V, int STAGES, bool USE_TMA>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
-  constexpr int ST = USE_TMA ? NSTAGE : 1;
-  auto kern = rglru_fwd_kernel<IO, FWD_TS, ST, USE_TMA>;
-  constexpr int bytes = FwdSmem<IO, FWD_TS, ST>::BYTES;
+  constexpr int ST = USE_TMA ? STAGES : 1;
+  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA>;
+  constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST>::BYTES;
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((a.D + CH - 1) / CH, a.B);
-  kern<<<grid, NT, bytes, s>>>(maps, a);
+  dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
+  kern<<<grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s>>>(maps, a);
   return cudaGetLastError();
 }
 
-cudaError_t launch_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
-  if (bf16) {
-    return use_tma ? launch_fwd_t<__nv_bfloat16, FWD_STAGES_BF16, true>(maps, a, s)
-                   : launch_fwd_t<__nv_bfloat16, 1, false>(maps, a, s);
+template <typename IO>
+static cudaError_t launch_fwd_io(bool use_tma, int variant, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
+  constexpr bool H = sizeof(IO) == 2;
+  if (!use_tma) return launch_fwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
+  switch (variant) {
+    case 1: return launch_fwd_t<IO, Shape64x16x4, H ? 8 : 4, true>(maps, a, s);
+    case 2: return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true>(maps, a, s);
+    case 3: return launch_fwd_t<IO, Shape32x16x4, 4, true>(maps, a, s);
+    default: return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
   }
-  return use_tma ? launch_fwd_t<float, FWD_STAGES_F32, true>(maps, a, s) : launch_fwd_t<float, 1, false>(maps, a, s);
 }
 
-template <typename IO, int NSTAGE, bool USE_TMA>
+cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps& maps, const ScanFwdArgs& a,
+                            cudaStream_t s) {
+  return bf16 ? launch_fwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_fwd_io<float>(use_tma, variant, maps, a, s);
+}
+
+template <typename IO, typename V, int STAGES, bool USE_TMA>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
-  constexpr int ST = USE_TMA ? NSTAGE : 1;
-  auto kern = rglru_bwd_kernel<IO, BWD_TS, ST, USE_TMA>;
-  constexpr int bytes = BwdSmem<IO, BWD_TS, ST>::BYTES;
+  constexpr int ST = USE_TMA ? STAGES : 1;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, 1>;
+  constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST>::BYTES;
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((a.D + CH - 1) / CH, a.B);
-  kern<<<grid, NT, bytes, s>>>(maps, a);
+  dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
+  kern<<<grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s>>>(maps, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   rglru_dlambda_kernel<<<(a.D + 255) / 256, 256, 0, s>>>(a.dlam_part, a.lambda, a.dlambda, a.B, a.D, a.c);
   return cudaGetLastError();
 }
 
-cudaError_t launch_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
-  if (bf16) {
-    return use_tma ? launch_bwd_t<__nv_bfloat16, BWD_STAGES_BF16, true>(maps, a, s)
-                   : launch_bwd_t<__nv_bfloat16, 1, false>(maps, a, s);
+template <typename IO>
+static cudaError_t launch_bwd_io(bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
+  constexpr bool H = sizeof(IO) == 2;
+  if (!use_tma) return launch_bwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
+  switch (variant) {
+    case 1: return launch_bwd_t<IO, Shape64x16x4, H ? 6 : 3, true>(maps, a, s);
+    case 2: return launch_bwd_t<IO, Shape32x16x4, H ? 4 : 3, true>(maps, a, s);
+    case 3: return launch_bwd_t<IO, Shape32x16x4, 3, true>(maps, a, s);
+    default: return launch_bwd_t<IO, Shape64x16x4, H ? 3 : 2, true>(maps, a, s);
   }
-  return use_tma ? launch_bwd_t<float, BWD_STAGES_F32, true>(maps, a, s) : launch_bwd_t<float, 1, false>(maps, a, s);
+}
+
+cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& a,
+                            cudaStream_t s) {
+  return bf16 ? launch_bwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_bwd_io<float>(use_tma, variant, maps, a, s);
 }
 
 int raw_box_rows() { return RAW_TC; }
+int raw_box_cols() { return CH; }
 
 template <int NSTAGE, bool USE_TMA>
 static cudaError_t launch_raw_fwd_t(const RawFwdMaps& maps, const RawScanArgs& a, cudaStream_t s) {
@@ -961,7 +1053,7 @@ static cudaError_t launch_raw_fwd_t(const RawFwdMaps& maps, const RawScanArgs& a
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + CH - 1) / CH, a.B);
-  kern<<<grid, NT, bytes, s>>>(maps, a);
+  kern<<<grid, RAW_NT, bytes, s>>>(maps, a);
   return cudaGetLastError();
 }
 cudaError_t launch_raw_fwd(bool use_tma, const RawFwdMaps& maps, const RawScanArgs& a, cudaStream_t s) {
@@ -974,7 +1066,7 @@ static cudaError_t launch_raw_bwd_t(const RawBwdMaps& maps, const RawScanArgs& a
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + CH - 1) / CH, a.B);
-  kern<<<grid, NT, bytes, s>>>(maps, a);
+  kern<<<grid, RAW_NT, bytes, s>>>(maps, a);
   return cudaGetLastError();
 }
 cudaError_t launch_raw_bwd(bool use_tma, const RawBwdMaps& maps, const RawScanArgs& a, cudaStream_t s) {
