@@ -174,7 +174,7 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
 
   FwdMaps maps;
   bool tma = tma_shape_ok(T, D, es) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) && aligned(y, 16);
-  const int variant = scan_fwd_variant(B, T, D);
+  const int variant = scan_fwd_variant(B, T, D, bf16);
   if (tma) {
     const int rows = scan_fwd_box_rows(variant), cols = scan_fwd_box_cols(variant);
     tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&
@@ -215,7 +215,7 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
   BwdMaps maps;
   bool tma = tma_shape_ok(T, D, es) && aligned(dy, 16) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) &&
              aligned(dx, 16) && aligned(du_r, 16) && aligned(du_i, 16);
-  const int variant = scan_bwd_variant(B, T, D);
+  const int variant = scan_bwd_variant(B, T, D, bf16);
   if (tma) {
     const int rows = scan_bwd_box_rows(variant), cols = scan_bwd_box_cols(variant);
     tma = make_map(&maps.dy, dy, bf16, B, T, D, rows, cols) && make_map(&maps.x, x, bf16, B, T, D, rows, cols) &&

@@ -127,8 +127,8 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
                             cudaStream_t s);
 cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& args,
                             cudaStream_t s);
-int scan_fwd_variant(int B, int T, int D);
-int scan_bwd_variant(int B, int T, int D);
+int scan_fwd_variant(int B, int T, int D, bool bf16);
+int scan_bwd_variant(int B, int T, int D, bool bf16);
 int scan_fwd_box_rows(int variant);
 int scan_fwd_box_cols(int variant);
 int scan_bwd_box_rows(int variant);
