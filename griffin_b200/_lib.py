@@ -19,7 +19,7 @@ F32, BF16 = 0, 1
 TOK_CUT_MASK, TOK_RESET, TOK_INACTIVE, TOK_ZERO_HISTORY = 0x03, 0x04, 0x08, 0x10
 
 (OK, ERR_NULL_POINTER, ERR_BAD_DTYPE, ERR_BAD_SHAPE, ERR_MISALIGNED, ERR_WORKSPACE, ERR_LAUNCH,
- ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED) = range(9)
+ ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED, ERR_TOO_LARGE) = range(10)
 
 _vp, _sz, _i, _f = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_float
 
@@ -38,6 +38,8 @@ SIGNATURES = {
     "rglru_conv_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rglru_conv_bwd_workspace_bytes": (_sz, [_i, _i, _i]),
     "rglru_conv_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _vp]),
+    "rglru_conv_bwd_noalloc_max_bytes": (_sz, []),
+    "rglru_conv_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "rglru_decode_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rglru_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
 }
@@ -75,7 +77,7 @@ def check(code: int, what: str) -> None:
         return
     lib = load()
     text = f"{what}: {lib.rglru_status_string(code).decode()}"
-    if code in (ERR_BAD_SHAPE, ERR_NULL_POINTER, ERR_MISALIGNED, ERR_WORKSPACE):
+    if code in (ERR_BAD_SHAPE, ERR_NULL_POINTER, ERR_MISALIGNED, ERR_WORKSPACE, ERR_TOO_LARGE):
         raise ValueError(text)
     if code == ERR_BAD_DTYPE:
         raise TypeError(text)

@@ -19,7 +19,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 SRC_DIR = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(SRC_DIR, "_build")
 LIB_PATH = os.path.join(PKG_DIR, "librglru_b200.so")
-SOURCES = ["rglru_scan.cu", "rglru_conv.cu", "rglru_api.cu"]
+SOURCES = ["rglru_scan.cu", "rglru_conv.cu", "rglru_api.cu", "rglru_noalloc.cu"]
 HEADERS = ["rglru_device.cuh", "rglru_internal.h", os.path.join("..", "..", "include", "rglru_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

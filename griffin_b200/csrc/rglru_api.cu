@@ -111,6 +111,7 @@ const char* rglru_status_string(int status) {
     case RGLRU_ERR_LAUNCH: return "CUDA launch failed";
     case RGLRU_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
     case RGLRU_ERR_UNSUPPORTED: return "unsupported device: CUDA kernels are built for sm_100a only";
+    case RGLRU_ERR_TOO_LARGE: return "problem larger than the fixed capacity of this entry point";
     default: return "unknown status";
   }
 }

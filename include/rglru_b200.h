@@ -33,7 +33,8 @@ enum rglru_status {
   RGLRU_ERR_WORKSPACE = 5,      /* workspace is missing or smaller than rglru_workspace_bytes() */
   RGLRU_ERR_LAUNCH = 6,         /* the CUDA runtime rejected a launch (see rglru_last_cuda_error) */
   RGLRU_ERR_DEVICE_TIMEOUT = 7, /* a bounded in-kernel wait expired (reported by rglru_device_status) */
-  RGLRU_ERR_UNSUPPORTED = 8     /* the device is not sm_100 or the driver lacks a required entry point */
+  RGLRU_ERR_UNSUPPORTED = 8,    /* the device is not sm_100 or the driver lacks a required entry point */
+  RGLRU_ERR_TOO_LARGE = 9       /* the problem exceeds a fixed capacity of the entry point (see rglru_conv_bwd_noalloc) */
 };
 
 /* Per-token flag byte shared by all kernels (one byte per (b, t), row-major [B, T]).
@@ -137,6 +138,26 @@ size_t rglru_conv_bwd_workspace_bytes(int B, int T, int D);
 int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, const void* conv_state,
                    const uint8_t* tok, void* dx_in, float* d_w, float* d_b, void* d_state, void* ws,
                    size_t ws_bytes, int B, int T, int D, int io_dtype, void* stream);
+
+/* Conv backward for callers that cannot allocate device memory.  (No counterpart in the reference:
+ * it exists for hosts of this library that may not call cudaMalloc or any allocating routine at the
+ * point where the backward runs -- a runtime that owns all device memory and lends none to plugins,
+ * a serving loop whose memory plan is frozen, a callback in which an allocation would synchronise
+ * the device.)  Same arguments and results as rglru_conv_bwd, minus the workspace: the partial sums
+ * live in a fixed 4 MiB array inside the library image, which every GPU that loads the library holds
+ * until the process exits.
+ *   - Limit: B * ceil(T / 256) * 5 * D <= 1,048,576 floats (rglru_conv_bwd_noalloc_max_bytes() / 4);
+ *     anything larger returns RGLRU_ERR_TOO_LARGE and launches nothing.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls share the array.  Calls on one stream are ordered and safe; calls that can overlap
+ *     on the GPU (different streams, several host threads) race on it and must be serialised by the
+ *     caller.  Nothing needs clearing between calls: every entry read is written first by the same call.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+size_t rglru_conv_bwd_noalloc_max_bytes(void);
+int rglru_conv_bwd_noalloc(const void* d_conv, const void* x_in, const float* conv_w, const void* conv_state,
+                           const uint8_t* tok, void* dx_in, float* d_w, float* d_b, void* d_state, int B, int T,
+                           int D, int io_dtype, void* stream);
 
 /* Single-token decode update: the T = 1 case of RecurrentBlock.forward with a cache,
  * griffin/griffin.py:459-528, split at the gate projections (which stay ordinary GEMMs):
