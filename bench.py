@@ -42,7 +42,7 @@ WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one rglru_bwd_kernel launch at config 1, from the
 # ncu capture summarised in profiles/ (None until a capture exists for the current kernel).
-BWD_DRAM_TRAFFIC_C1 = None
+BWD_DRAM_TRAFFIC_C1 = 195.28e6  # profiles/rglru_scan_config1_bf16.md (read 135.29 MB + write 59.99 MB)
 
 
 def measured_peak() -> tuple[float, str]:
@@ -296,8 +296,8 @@ def cpu_baseline(workload: str, steps: int = 1) -> dict:
     from oracle import rglru_oracle as orc
 
     B, T, D, G, dtype = WORKLOADS[workload]
-    sample_b = min(B, 2) if T >= 2048 else B
-    sample_t = min(T, 2048)
+    sample_b = B if B * T * D <= (1 << 24) else max(1, (1 << 24) // (T * D))
+    sample_t = min(T, 2048)  # the reference's backward is O(T^2) per row on CPU
     case = orc.make_rglru_case(sample_b, sample_t, D, G, seed=0)
     names = ("Lambda", "recurrence_gate.weight", "recurrence_gate.bias", "input_gate.weight", "input_gate.bias")
     es = 2 if dtype == torch.bfloat16 else 4
