@@ -1,6 +1,6 @@
 """Benchmark of the RG-LRU hot path (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c4a|c0]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1|c0|c3layer|c4a|c2|c3|c4b]
 
 One step = one forward + one backward pass of the RG-LRU layer kernels over one batch
 of synthetic input (BASELINE config 1 by default: bf16 I/O, fp32 state, B=8, T=2048,
@@ -295,6 +295,11 @@ def cpu_baseline(workload: str, steps: int = 1) -> dict:
     """
     from oracle import rglru_oracle as orc
 
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may run on.
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     B, T, D, G, dtype = WORKLOADS[workload]
     sample_b = B if B * T * D <= (1 << 24) else max(1, (1 << 24) // (T * D))
     sample_t = min(T, 2048)  # the reference's backward is O(T^2) per row on CPU
@@ -350,19 +355,229 @@ def run_reference(args) -> dict:
     }
 
 
+# --------------------------------------------------------------------------- secondary workloads
+def _dist_setup():
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local if world > 1 else 0)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, world, rank, dev
+
+
+def _timed(fn, steps, warmup, dist, world, dev):
+    """W warm-up calls, then exactly K timed calls between barriers; returns max-over-ranks ms per call."""
+    for i in range(warmup):
+        fn(i)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def run_block(args) -> dict:
+    """BASELINE config 2: the full recurrent temporal block, bf16, B=16/GPU, T=2048, 768 -> 1024 -> 768, fwd+bwd."""
+    from griffin_b200 import RecurrentBlock, _lib
+    dist, world, rank, dev = _dist_setup()
+    B, T, DM, DR = 16, 2048, 768, 1024
+    torch.manual_seed(rank)
+    blk = RecurrentBlock(DM, DR, gate_blocks=16, scan_mode="cuda")
+    with torch.no_grad():
+        blk.temporal_conv.weight.normal_(0.0, 0.5)       # N(0, 1/4) as the config states
+    blk = blk.to(dev, torch.bfloat16)
+    xs = [torch.randn(B, T, DM, device=dev).to(torch.bfloat16).requires_grad_(True) for _ in range(3)]
+    dout = torch.randn(B, T, DM, device=dev).to(torch.bfloat16)
+    sampler = ClockSampler(dev.index or 0)
+
+    def step(i):
+        x = xs[i % 3]
+        x.grad = None
+        blk.zero_grad(set_to_none=True)
+        blk(x).backward(dout)
+
+    sampler.start()
+    ms = _timed(step, args.steps, args.warmup, dist, world, dev)
+    host_x = torch.randn(B, T, DM).to(torch.bfloat16).pin_memory()
+    host_loss = torch.empty(1).pin_memory()
+
+    def e2e_step(i):
+        x = xs[0]
+        with torch.no_grad():
+            x.copy_(host_x, non_blocking=True)
+        x.grad = None
+        blk.zero_grad(set_to_none=True)
+        out = blk(x)
+        out.backward(dout)
+        host_loss.copy_(out.float().square().mean().reshape(1), non_blocking=True)
+
+    e2e_ms = _timed(e2e_step, max(3, min(args.steps, 50)), 3, dist, world, dev)
+    clocks = sampler.stop()
+    n = B * T * DR
+    peak, kind = measured_peak()
+    out = {"metric": "recurrent_block_fwd_bwd_token_channels_per_s", "value": world * n / ms * 1e3, "unit": "token-channels/s",
+           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16 I/O, f32 state", "data": "synthetic",
+           "config": {"workload": f"c2: RecurrentBlock fwd+bwd bf16 B={B}/GPU T={T} {DM}->{DR}->{DM}, conv k=4, 16 gate heads",
+                      "l2": "three rotating inputs; 0.6 GB of activations per step"},
+           "scan_conv_algorithmic_gbs": world * (22 + 10) * n / ms / 1e6,
+           "e2e": {"value": world * n / e2e_ms * 1e3, "unit": "token-channels/s", "h2d_bytes_per_step": 2 * B * T * DM,
+                   "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
+           "gpu_launches": 6 * args.steps, "clocks": clocks, "device_status": _lib.device_status(),
+           "roofline": {"bound": "hbm", "note": "GEMMs (torch) dominate this step; see the c1 line for the kernel roofline",
+                        "peak": peak, "peak_source": f"of {kind}", "unit": "GB/s", "achieved": None, "frac": None, "traffic": None}}
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def run_lm(args) -> dict:
+    """BASELINE config 3: Griffin ~100M training step, bf16 autocast, B=8/GPU, T=2048, DDP over NCCL for N > 1."""
+    from griffin_b200 import _lib
+    from griffin_b200.lm import GriffinModel
+    dist, world, rank, dev = _dist_setup()
+    B, T, V = 8, 2048, 50257
+    torch.manual_seed(0)
+    model = GriffinModel(V, 768, 3, 1024, 12, attention_heads=6, attention_window_size=1024, gate_blocks=16,
+                         scan_mode="cuda").to(dev)
+    nparams = sum(p.numel() for p in model.parameters())
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index]) if world > 1 else model
+    decay = [p for n_, p in model.named_parameters() if p.dim() >= 2]
+    plain = [p for n_, p in model.named_parameters() if p.dim() < 2]
+    opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": plain, "weight_decay": 0.0}],
+                            lr=3e-4, betas=(0.9, 0.95), fused=True)
+    gen = torch.Generator().manual_seed(100 + rank)
+    host_ids = [torch.randint(0, V, (B, T + 1), generator=gen).pin_memory() for _ in range(4)]
+    dev_ids = [h.to(dev) for h in host_ids]
+    host_loss = torch.empty(1).pin_memory()
+    sampler = ClockSampler(dev.index or 0)
+
+    def train(ids):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = net(ids[:, :-1])
+        loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, V), ids[:, 1:].reshape(-1))
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def step(i):
+        train(dev_ids[i % 4])
+
+    def e2e_step(i):
+        ids = host_ids[i % 4].to(dev, non_blocking=True)
+        host_loss.copy_(train(ids).detach().reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the reference reads loss.item() every step
+
+    sampler.start()
+    ms = _timed(step, args.steps, args.warmup, dist, world, dev)
+    e2e_ms = _timed(e2e_step, max(3, min(args.steps, 20)), 2, dist, world, dev)
+    clocks = sampler.stop()
+    out = {"metric": "griffin100m_train_tokens_per_s", "value": world * B * T / ms * 1e3, "unit": "tokens/s",
+           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast (fp32 at the RG-LRU boundary)", "data": "synthetic",
+           "config": {"workload": f"c3: Griffin-100M ({nparams} params) train step B={B}/GPU T={T} vocab {V}, AdamW, "
+                                  f"{'DDP/NCCL' if world > 1 else 'single GPU'}",
+                      "l2": "activations of one step far exceed L2"},
+           "e2e": {"value": world * B * T / e2e_ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B * (T + 1),
+                   "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
+           "gpu_launches": 8 * 9 * args.steps, "clocks": clocks, "device_status": _lib.device_status(),
+           "roofline": {"bound": "tensor", "note": "whole-model step: torch GEMMs and attention dominate; the library's kernels "
+                        "are the conv, the RG-LRU scan and their backwards in 8 of 12 layers", "achieved": None, "peak": None,
+                        "frac": None, "traffic": None, "unit": "TFLOP/s"}}
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def run_decode(args) -> dict:
+    """BASELINE config 4 part two: single-token decode update, B=512/GPU, D=5632, fp32 carried state, bf16 I/O,
+    1024 steps per timed call (one CUDA graph of 1024 kernel launches)."""
+    from griffin_b200 import _lib
+    dist, world, rank, dev = _dist_setup()
+    lib = _lib.load()
+    B, D, NSTEP, NSET = 512, 5632, 1024, 8
+    xs = [tuple(torch.randn(B, D, device=dev).to(torch.bfloat16) for _ in range(3)) for _ in range(NSET)]
+    lam = torch.logit(torch.empty(D).uniform_(0.9, 0.999).pow(1.0 / 8.0)).to(dev)
+    h = torch.zeros(B, D, device=dev)
+    y = torch.empty(B, D, device=dev, dtype=torch.bfloat16)
+
+    def one(i, stream):
+        x, ur, ui = xs[i % NSET]
+        rc = lib.rglru_decode_step(x.data_ptr(), ur.data_ptr(), ui.data_ptr(), lam.data_ptr(), h.data_ptr(), None,
+                                   y.data_ptr(), B, D, 8.0, _lib.BF16, stream)
+        _lib.check(rc, "rglru_decode_step")
+
+    one(0, torch.cuda.current_stream(dev).cuda_stream)      # per-device set-up happens outside capture
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(NSTEP):
+            one(i, side.cuda_stream)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms = _timed(lambda i: graph.replay(), args.steps, args.warmup, dist, world, dev)
+    clocks = sampler.stop()
+    n = B * D
+    bytes_step = 16 * n                     # x, u_r, u_i bf16 in; y bf16 out; h fp32 in and out
+    peak, kind = measured_peak()
+    achieved = bytes_step * NSTEP / ms / 1e6
+    out = {"metric": "rglru_decode_hbm_gbs", "value": world * achieved, "unit": "GB/s", "n_gpus": world,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16 I/O, f32 state", "data": "synthetic",
+           "config": {"workload": f"c4b: decode update B={B}/GPU D={D}, {NSTEP} token steps per timed call (CUDA graph)",
+                      "l2": f"{NSET} rotating input sets of 17 MB plus 23 MB of state: the state and part of the inputs stay in L2"},
+           "decode_steps_per_s": world * NSTEP / ms * 1e3, "us_per_token_step": ms * 1e3 / NSTEP,
+           "roofline": {"bound": "hbm", "kernel": "decode_step_kernel", "achieved": achieved, "peak": peak,
+                        "peak_source": f"of {kind}", "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                        "algorithmic_bytes": bytes_step},
+           "e2e": None, "gpu_launches": NSTEP * args.steps, "clocks": clocks, "device_status": _lib.device_status()}
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["c2", "c3", "c4b"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-kernel-timing", action="store_true", help="skip the per-kernel event pass (for profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        if args.workload not in WORKLOADS:
+            raise SystemExit("--impl reference covers the RG-LRU layer workloads only")
+        out = run_reference(args)
+    elif args.workload == "c2":
+        out = run_block(args)
+    elif args.workload == "c3":
+        out = run_lm(args)
+    elif args.workload == "c4b":
+        out = run_decode(args)
+    else:
+        out = run_ours(args)
     if out:
         print(json.dumps(out))
 

@@ -296,6 +296,46 @@ def _block_cases(G):
     _save("block_decode", out)
 
 
+def _model_cases(G):
+    """Tiny hybrid LM (reference tests/test_griffin_model.py shapes): logits, CE loss and a few gradients,
+    with default positions and with a document reset; plus the local attention block alone."""
+    torch.manual_seed(7)
+    model = G.GriffinModel(vocab_size=23, input_dim=8, mlp_expansion_factor=2, rnn_width=12, depth=3,
+                           attention_heads=2, attention_window_size=4, scan_mode="sequential")
+    with torch.no_grad():
+        for layer in model.layers:
+            if layer.temporal_block_type == "recurrent":
+                layer.recurrent.temporal_conv.weight.normal_(0.0, 0.5)
+    tokens = torch.randint(0, 23, (2, 9))
+    targets = torch.randint(0, 23, (2, 9))
+    seg = torch.tensor([[0, 1, 2, 3, 0, 1, 2, 3, 4], [0, 1, 2, 3, 4, 5, 6, 0, 1]])
+    out = {"tokens": tokens, "targets": targets, "segment_pos": seg}
+    for key, p_ in model.state_dict().items():
+        out["p." + key] = p_
+    for tag, kwargs in (("plain", {}), ("seg", {"segment_pos": seg})):
+        model.zero_grad()
+        logits = model(tokens, **kwargs)
+        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, 23), targets.reshape(-1))
+        loss.backward()
+        out[f"{tag}.logits"] = logits
+        out[f"{tag}.loss"] = loss.detach().reshape(1)
+        for name in ("embd.weight", "layers.0.recurrent.rg_lru.Lambda", "layers.0.recurrent.temporal_conv.weight",
+                     "layers.1.recurrent.rg_lru.input_gate.weight", "layers.2.attention.query.weight",
+                     "layers.2.mlp.linear3.weight", "final_norm.g"):
+            out[f"{tag}.g.{name}"] = dict(model.named_parameters())[name].grad
+    _save("model_tiny", out)
+
+    torch.manual_seed(8)
+    attn = G.LocalMQAAttention(input_dim=16, num_heads=2, window_size=5, chunk_size=3)
+    x = torch.randn(2, 11, 16)
+    seg = torch.tensor([[0, 1, 2, 3, 4, 5, 6, 0, 1, 2, 3], [3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13]])
+    with torch.no_grad():
+        out = {"x": x, "segment_pos": seg, "plain": attn(x), "seg": attn(x, segment_pos=seg)}
+    for key, p_ in attn.state_dict().items():
+        out["p." + key] = p_
+    _save("attention_block", out)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
@@ -314,6 +354,7 @@ def main() -> None:
     _bf16_pair(G)
     _scan_selftest(TS)
     _block_cases(G)
+    _model_cases(G)
 
 
 if __name__ == "__main__":

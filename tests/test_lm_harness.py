@@ -1,0 +1,53 @@
+"""The whole-model harness (plain-torch blocks around the CUDA recurrent block) against the reference's
+stored results: the local attention block on CPU, the tiny hybrid LM on the GPU."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import load_golden, params_of
+from oracle.rglru_oracle import rel_l2
+
+
+def test_local_attention_matches_reference_cpu():
+    from griffin_b200.lm import LocalMQAAttention
+    case = load_golden("attention_block")
+    attn = LocalMQAAttention(16, 2, window_size=5, chunk_size=3)
+    attn.load_state_dict(params_of(case))
+    with torch.no_grad():
+        plain = attn(case["x"])
+        seg = attn(case["x"], segment_pos=case["segment_pos"])
+    torch.testing.assert_close(plain, case["plain"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(seg, case["seg"], atol=2e-6, rtol=2e-5)
+
+
+def test_model_state_dict_is_the_reference_layout():
+    from griffin_b200.lm import GriffinModel
+    case = load_golden("model_tiny")
+    model = GriffinModel(23, 8, 2, 12, 3, attention_heads=2, attention_window_size=4)
+    model.load_state_dict(params_of(case), strict=True)
+    assert model.block_types == ("recurrent", "recurrent", "attention")
+    assert model.lm_head.weight is model.embd.weight
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag", ["plain", "seg"])
+def test_tiny_model_logits_loss_and_gradients_gpu(tag):
+    from griffin_b200.lm import GriffinModel
+    case = load_golden("model_tiny")
+    model = GriffinModel(23, 8, 2, 12, 3, attention_heads=2, attention_window_size=4)
+    model.load_state_dict(params_of(case), strict=True)
+    model = model.cuda()
+    tokens, targets = case["tokens"].cuda(), case["targets"].cuda()
+    seg = case["segment_pos"].cuda() if tag == "seg" else None
+    logits = model(tokens, segment_pos=seg)
+    loss = torch.nn.functional.cross_entropy(logits.reshape(-1, 23), targets.reshape(-1))
+    loss.backward()
+    torch.testing.assert_close(logits.cpu(), case[f"{tag}.logits"], atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(loss.detach().cpu().reshape(1), case[f"{tag}.loss"], atol=1e-5, rtol=1e-5)
+    grads = dict(model.named_parameters())
+    for key in case:
+        if key.startswith(f"{tag}.g."):
+            name = key[len(tag) + 3:]
+            assert rel_l2(grads[name].grad, case[key]) <= 1e-5, name
