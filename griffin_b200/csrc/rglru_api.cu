@@ -147,7 +147,7 @@ size_t rglru_workspace_bytes(int B, int T, int D, int io_dtype) {
   (void)io_dtype;
   if (B <= 0 || T <= 0 || D <= 0) return 0;
   const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
-  return (static_cast<size_t>(B) * nsave * D + static_cast<size_t>(B) * D) * sizeof(float);
+  return (static_cast<size_t>(B) * nsave * D + static_cast<size_t>(B) * D) * sizeof(float) + WS_TAIL_BYTES;
 }
 
 int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
@@ -171,6 +171,12 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
   a.x = x; a.ur = u_r; a.ui = u_i; a.y = y;
   a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
   a.states = static_cast<float*>(ws);
+  {
+    const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+    a.ticket = ws ? reinterpret_cast<unsigned*>(static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D +
+                                               static_cast<size_t>(B) * D)
+                  : nullptr;
+  }
   a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
 
   FwdMaps maps;
@@ -211,6 +217,7 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
   a.states = static_cast<const float*>(ws);
   a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
   a.dlambda = dlambda; a.dh0 = dh0;
+  a.ticket = (B <= FUSED_DLAMBDA_MAX_B) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
   a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
 
   BwdMaps maps;

@@ -119,6 +119,13 @@ __device__ __forceinline__ void prefetch_map(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
+// Programmatic dependent launch: `pdl_launch_dependents` lets the next kernel on the stream begin its
+// launch and prologue while this grid is still running; `pdl_wait` (in that next kernel) returns once
+// the preceding grid has completed and its writes are visible.  Every global access of a kernel
+// launched with the attribute must come after pdl_wait.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- fast math
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;

@@ -10,6 +10,9 @@ namespace rglru {
 
 // Time-steps between saved recurrent states == chunk length of the backward kernel.
 constexpr int SAVE_EVERY = 64;
+// Largest batch for which the backward kernel folds the dLambda rows itself (one CTA walks B x D floats).
+constexpr int FUSED_DLAMBDA_MAX_B = 64;
+constexpr size_t WS_TAIL_BYTES = 256;  // completion ticket at the end of the workspace
 
 struct ScanFwdArgs {
   const void* x;
@@ -21,6 +24,7 @@ struct ScanFwdArgs {
   const uint8_t* tok;
   float* h_last;
   float* states;  // [B, ceil(T/SAVE_EVERY), D] or nullptr
+  unsigned* ticket;  // completion counter of the workspace (zeroed here for the backward), or nullptr
   int B, T, D;
   float c;
   int* status;
@@ -42,6 +46,7 @@ struct ScanBwdArgs {
   float* dlam_part;     // [B, D] per-row partial sums of dl * r
   float* dlambda;       // [D]
   float* dh0;           // [B, D] or nullptr
+  unsigned* ticket;     // when set, the last CTA folds dlam_part into dlambda; else a second kernel does
   int B, T, D;
   float c;
   int* status;

@@ -177,18 +177,20 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
   const int nchunks = (p.T + TC - 1) / TC;
   const int nsave = (p.T + SAVE_EVERY - 1) / SAVE_EVERY;
 
-  float2 K[2];
-  {
-    const int d = d0 + vec * CV;
-    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
-    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
-  }
+  pdl_launch_dependents();
   if (tid == 0) {
     *dead = 0;
     if (USE_TMA) {
       for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
       mbar_fence_init();
     }
+  }
+  pdl_wait();   // nothing above touches global memory; everything below may depend on the previous kernel
+  float2 K[2];
+  {
+    const int d = d0 + vec * CV;
+    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
+    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
   }
   const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
@@ -220,6 +222,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     }
     return;
   }
+
+  if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && p.ticket) *p.ticket = 0u;   // consumed by the backward kernel
 
   // Level-two chain state: thread `tid` < CH carries channel d0 + tid across chunks.
   float carry = 0.0f;
@@ -430,18 +434,20 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
   const int nchunks = (p.T + TC - 1) / TC;
   const int nsave = (p.T + SAVE_EVERY - 1) / SAVE_EVERY;
 
-  float2 K[2];
-  {
-    const int d = d0 + vec * CV;
-    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
-    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
-  }
+  pdl_launch_dependents();
   if (tid == 0) {
     *dead = 0;
     if (USE_TMA) {
       for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
       mbar_fence_init();
     }
+  }
+  pdl_wait();   // nothing above touches global memory; everything below may depend on the previous kernel
+  float2 K[2];
+  {
+    const int d = d0 + vec * CV;
+    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
+    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
   }
   const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
@@ -632,6 +638,27 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
     for (int j = 0; j < LANES; ++j) acc += einF[j * CH + tid];
     p.dlam_part[static_cast<size_t>(b) * p.D + dch] = acc;
   }
+  if (!p.ticket) return;   // the caller folds the rows with rglru_dlambda_kernel
+
+  // The CTA that finishes last folds the per-row partials into dLambda (rows in index order, so the
+  // result does not depend on which CTA that is) and re-arms the ticket for the next backward call.
+  __shared__ int s_last;
+  __threadfence();
+  bar_compute(NCOMP);
+  if (tid == 0) {
+    const unsigned total = gridDim.x * gridDim.y;
+    s_last = (atomicAdd(p.ticket, 1u) == total - 1u) ? 1 : 0;
+  }
+  bar_compute(NCOMP);
+  if (!s_last) return;
+  __threadfence();
+  for (int d = tid; d < p.D; d += NCOMP) {
+    float acc = 0.0f;
+    for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + d);
+    const float lam = p.lambda[d];
+    p.dlambda[d] = (1.0f / (1.0f + expf(lam))) * p.c * acc;
+  }
+  if (tid == 0) *p.ticket = 0u;
 }
 
 // dLambda[d] = d/dLambda of sum dl * r * c * logsigmoid(Lambda) = sigmoid(-Lambda_d) * c * sum_b partial[b, d],
@@ -976,6 +1003,23 @@ int scan_bwd_variant(int B, int T, int D, bool bf16) {
   return 0;
 }
 
+// Launch with programmatic stream serialization, so that this kernel's launch and prologue may overlap
+// the tail of the kernel before it on the stream (the kernels call pdl_wait before touching memory).
+template <typename Kern, typename Maps, typename Args>
+static cudaError_t launch_pdl(Kern kern, dim3 grid, int threads, int bytes, cudaStream_t s, const Maps& maps, const Args& a) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, maps, a);
+}
+
 template <typename Kern>
 static cudaError_t set_smem(Kern kern, int bytes) {
   // Ask for the largest shared-memory carveout so that occupancy is set by the kernel's own
@@ -993,8 +1037,7 @@ static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaS
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
-  kern<<<grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s>>>(maps, a);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s, maps, a);
 }
 
 template <typename IO>
@@ -1022,9 +1065,8 @@ static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaS
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
-  kern<<<grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s>>>(maps, a);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s, maps, a);
+  if (e != cudaSuccess || a.ticket) return e;
   rglru_dlambda_kernel<<<(a.D + 255) / 256, 256, 0, s>>>(a.dlam_part, a.lambda, a.dlambda, a.B, a.D, a.c);
   return cudaGetLastError();
 }

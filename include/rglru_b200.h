@@ -64,8 +64,8 @@ int rglru_device_status(int* detail);
 int rglru_chunk_steps(int io_dtype);
 
 /* Bytes of caller-provided workspace shared by rglru_fwd and rglru_bwd of one call
- * pair: chunk-entry states [B, ceil(T/chunk), D] fp32 followed by per-row dLambda
- * partial sums [B, D] fp32.  Contents written by rglru_fwd must be left untouched
+ * pair: chunk-entry states [B, ceil(T/chunk), D] fp32, per-row dLambda partial sums
+ * [B, D] fp32, and a 256-byte tail with a completion ticket that rglru_fwd zeroes.  Contents written by rglru_fwd must be left untouched
  * until the matching rglru_bwd has run. */
 size_t rglru_workspace_bytes(int B, int T, int D, int io_dtype);
 

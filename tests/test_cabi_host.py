@@ -53,7 +53,8 @@ def test_workspace_size_and_chunk(lib):
     assert chunk > 0 and chunk % 16 == 0
     B, T, D = 3, 130, 40
     nsave = -(-T // chunk)
-    assert lib.rglru_workspace_bytes(B, T, D, _lib.F32) == 4 * (B * nsave * D + B * D)
+    # chunk-entry states, per-row dLambda partials, and a 256-byte tail holding the completion ticket
+    assert lib.rglru_workspace_bytes(B, T, D, _lib.F32) == 4 * (B * nsave * D + B * D) + 256
     assert lib.rglru_workspace_bytes(0, T, D, _lib.F32) == 0
     assert lib.rglru_conv_bwd_workspace_bytes(B, T, D) >= 4 * 5 * D * B
 
