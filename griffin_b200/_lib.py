@@ -33,6 +33,8 @@ SIGNATURES = {
     "rglru_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "rglru_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _f, _i, _vp]),
     "rglru_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "rglru_conv_scan_fwd": (_i, [_vp] * 11 + [_vp, _sz, _i, _i, _i, _f, _i, _vp]),
+    "rglru_conv_scan_bwd": (_i, [_vp] * 11 + [_vp, _sz] + [_vp] * 5 + [_i, _i, _i, _f, _i, _vp]),
     "rglru_linear_scan_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rglru_linear_scan_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rglru_conv_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -167,7 +167,7 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
   rc = device_setup(&status);
   if (rc != RGLRU_OK) return rc;
 
-  ScanFwdArgs a;
+  ScanFwdArgs a = {};
   a.x = x; a.ur = u_r; a.ui = u_i; a.y = y;
   a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
   a.states = static_cast<float*>(ws);
@@ -211,7 +211,7 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
   if (rc != RGLRU_OK) return rc;
 
   const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
-  ScanBwdArgs a;
+  ScanBwdArgs a = {};
   a.dy = dy; a.x = x; a.ur = u_r; a.ui = u_i; a.dx = dx; a.dur = du_r; a.dui = du_i;
   a.lambda = lambda; a.h0 = h0; a.dh_last = dh_last; a.tok = tok;
   a.states = static_cast<const float*>(ws);
@@ -232,6 +232,95 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
           make_map(&maps.dui, du_i, bf16, B, T, D, rows, cols);
   }
   const cudaError_t e = launch_scan_bwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_conv_scan_fwd(const void* x_in, const float* conv_w, const float* conv_b, const void* conv_state,
+                        const void* u_r, const void* u_i, const float* lambda, const float* h0, const uint8_t* tok,
+                        void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c, int io_dtype,
+                        void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x_in || !conv_w || !u_r || !u_i || !lambda || !y) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(x_in, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(y, es) || !aligned(conv_state, es) ||
+      !aligned(lambda, 4) || !aligned(conv_w, 4) || !aligned(conv_b, 4) || !aligned(h0, 4) || !aligned(h_last, 4) ||
+      !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (ws && ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  ScanFwdArgs a = {};
+  a.x = x_in; a.ur = u_r; a.ui = u_i; a.y = y;
+  a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
+  a.states = static_cast<float*>(ws);
+  a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = conv_state;
+  {
+    const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+    a.ticket = ws ? reinterpret_cast<unsigned*>(static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D +
+                                               static_cast<size_t>(B) * D)
+                  : nullptr;
+  }
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  FwdMaps maps;
+  bool tma = tma_shape_ok(T, D, es) && aligned(x_in, 16) && aligned(u_r, 16) && aligned(u_i, 16) && aligned(y, 16);
+  if (tma) {
+    const int rows = scan_fwd_box_rows(0), cols = scan_fwd_box_cols(0);
+    tma = make_map(&maps.x, x_in, bf16, B, T, D, rows + 3, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) && make_map(&maps.y, y, bf16, B, T, D, rows, cols);
+  }
+  const cudaError_t e = launch_conv_scan_fwd(bf16, tma, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_conv_scan_bwd(const void* dy, const float* dh_last, const void* x_in, const float* conv_w, const float* conv_b,
+                        const void* conv_state, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+                        const uint8_t* tok, void* ws, size_t ws_bytes, void* dx_conv, void* du_r, void* du_i,
+                        float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!dy || !x_in || !conv_w || !u_r || !u_i || !lambda || !dx_conv || !du_r || !du_i || !dlambda)
+    return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(dy, es) || !aligned(x_in, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(dx_conv, es) ||
+      !aligned(du_r, es) || !aligned(du_i, es) || !aligned(conv_state, es) || !aligned(lambda, 4) ||
+      !aligned(conv_w, 4) || !aligned(conv_b, 4) || !aligned(h0, 4) || !aligned(dh_last, 4) || !aligned(dlambda, 4) ||
+      !aligned(dh0, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (!ws || ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+  ScanBwdArgs a = {};
+  a.dy = dy; a.x = x_in; a.ur = u_r; a.ui = u_i; a.dx = dx_conv; a.dur = du_r; a.dui = du_i;
+  a.lambda = lambda; a.h0 = h0; a.dh_last = dh_last; a.tok = tok;
+  a.states = static_cast<const float*>(ws);
+  a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
+  a.dlambda = dlambda; a.dh0 = dh0;
+  a.ticket = (B <= FUSED_DLAMBDA_MAX_B) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
+  a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = conv_state;
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  BwdMaps maps;
+  bool tma = tma_shape_ok(T, D, es) && aligned(dy, 16) && aligned(x_in, 16) && aligned(u_r, 16) && aligned(u_i, 16) &&
+             aligned(dx_conv, 16) && aligned(du_r, 16) && aligned(du_i, 16);
+  if (tma) {
+    const int rows = scan_bwd_box_rows(0), cols = scan_bwd_box_cols(0);
+    tma = make_map(&maps.dy, dy, bf16, B, T, D, rows, cols) && make_map(&maps.x, x_in, bf16, B, T, D, rows + 3, cols) &&
+          make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) && make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dx, dx_conv, bf16, B, T, D, rows, cols) && make_map(&maps.dur, du_r, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dui, du_i, bf16, B, T, D, rows, cols);
+  }
+  const cudaError_t e = launch_conv_scan_bwd(bf16, tma, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
 

@@ -25,6 +25,10 @@ struct ScanFwdArgs {
   float* h_last;
   float* states;  // [B, ceil(T/SAVE_EVERY), D] or nullptr
   unsigned* ticket;  // completion counter of the workspace (zeroed here for the backward), or nullptr
+  // conv-folded variant only: x is the conv INPUT; taps [D,4], bias [D] or nullptr, carried history [B,3,D] or nullptr
+  const float* conv_w;
+  const float* conv_b;
+  const void* conv_state;
   int B, T, D;
   float c;
   int* status;
@@ -47,6 +51,9 @@ struct ScanBwdArgs {
   float* dlambda;       // [D]
   float* dh0;           // [B, D] or nullptr
   unsigned* ticket;     // when set, the last CTA folds dlam_part into dlambda; else a second kernel does
+  const float* conv_w;  // conv-folded variant only (see ScanFwdArgs)
+  const float* conv_b;
+  const void* conv_state;
   int B, T, D;
   float c;
   int* status;
@@ -132,6 +139,8 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
                             cudaStream_t s);
 cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& args,
                             cudaStream_t s);
+cudaError_t launch_conv_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
+cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
 int scan_fwd_variant(int B, int T, int D, bool bf16);
 int scan_bwd_variant(int B, int T, int D, bool bf16);
 int scan_fwd_box_rows(int variant);

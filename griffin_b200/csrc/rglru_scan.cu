@@ -99,22 +99,106 @@ struct ChainSmem {
   static constexpr int EIN = LANES * CH * 4;  // float per (lane, channel)
 };
 
+// Taps of the width-4 causal depthwise conv for the four channels a thread owns (column 3 of the
+// [D, 4] weight multiplies the current token; griffin/griffin.py:474-486 of the reference).
+struct ConvTaps {
+  float2 w[4][2];
+  float2 bias[2];
+};
+
+__device__ __forceinline__ void load_taps(const float* conv_w, const float* conv_b, int d, int D, ConvTaps& ct) {
+  float w[4][4], bz[4];
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    const bool ok = d + ch < D;
+    bz[ch] = (ok && conv_b) ? conv_b[d + ch] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w[k][ch] = ok ? conv_w[(d + ch) * 4 + k] : 0.0f;
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { ct.w[k][0] = make_float2(w[k][0], w[k][1]); ct.w[k][1] = make_float2(w[k][2], w[k][3]); }
+  ct.bias[0] = make_float2(bz[0], bz[1]);
+  ct.bias[1] = make_float2(bz[2], bz[3]);
+}
+
+// Conv folded into the load stage: the x tile carries three extra rows in front (times t0-3 .. t0-1), a
+// thread reads the TS+3 rows ending at its last step and forms the TS conv outputs in registers.
+// `hist` (non-null only for the first lane of the first chunk when a conv state is carried) replaces
+// the three rows before t = 0.  Tap l is dropped when the token's flag byte says fewer than l earlier
+// tokens belong to its document.
+template <typename IO, int TS, int CH, bool MASKED>
+__device__ __forceinline__ void conv_front(const uint8_t* tx, int off0, const ConvTaps& ct,
+                                           const uint32_t (&fl)[(TS + 3) / 4], const float2 (*hist)[2],
+                                           float2 (&xc)[TS][2]) {
+  constexpr int ROWB = CH * sizeof(IO);
+  float2 raw[TS + 3][2];
+#pragma unroll
+  for (int r = 0; r < TS + 3; ++r) Pack<IO>::unpack2(Pack<IO>::load(tx + off0 + r * ROWB), raw[r]);
+  if (hist) {
+#pragma unroll
+    for (int r = 0; r < 3; ++r) { raw[r][0] = hist[r][0]; raw[r][1] = hist[r][1]; }
+  }
+#pragma unroll
+  for (int st = 0; st < TS; ++st) {
+    float m1 = 1.0f, m2 = 1.0f, m3 = 1.0f;
+    if (MASKED) {
+      const int reach = 3 - static_cast<int>((fl[st >> 2] >> (8 * (st & 3))) & TOK_CUT_MASK);
+      m1 = reach >= 1 ? 1.0f : 0.0f;
+      m2 = reach >= 2 ? 1.0f : 0.0f;
+      m3 = reach >= 3 ? 1.0f : 0.0f;
+    }
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {
+      float2 acc = fma2(ct.w[3][cp], raw[st + 3][cp], ct.bias[cp]);
+      if (MASKED) {
+        acc = fma2(mul2(ct.w[2][cp], f2(m1)), raw[st + 2][cp], acc);
+        acc = fma2(mul2(ct.w[1][cp], f2(m2)), raw[st + 1][cp], acc);
+        acc = fma2(mul2(ct.w[0][cp], f2(m3)), raw[st][cp], acc);
+      } else {
+        acc = fma2(ct.w[2][cp], raw[st + 2][cp], acc);
+        acc = fma2(ct.w[1][cp], raw[st + 1][cp], acc);
+        acc = fma2(ct.w[0][cp], raw[st][cp], acc);
+      }
+      xc[st][cp] = acc;
+    }
+  }
+}
+
+// The three inputs before t = 0 of one batch row, from the carried conv state [B, 3, D].
+template <typename IO>
+__device__ __forceinline__ void load_hist(const void* conv_state, int b, int d, int D, float2 (&hist)[3][2]) {
+  const IO* st = static_cast<const IO*>(conv_state);
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    float v[4];
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch)
+      v[ch] = (d + ch < D) ? Pack<IO>::to_float(st[(static_cast<size_t>(b) * 3 + r) * D + d + ch]) : 0.0f;
+    hist[r][0] = make_float2(v[0], v[1]);
+    hist[r][1] = make_float2(v[2], v[3]);
+  }
+}
+
 // ======================================================================
 // Forward
 // ======================================================================
 
-template <typename IO, int TS, int CH, bool MASKED, bool POLY>
+template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV>
 __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, const uint8_t* ti, int off0,
                                           const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
+                                          const ConvTaps& ct, const float2 (*hist)[2],
                                           float2 (&P)[TS][2], float2 (&S)[TS][2]) {
   constexpr int ROWB = CH * sizeof(IO);
   float2 p[2] = {f2(1.0f), f2(1.0f)};
   float2 s[2] = {f2(0.0f), f2(0.0f)};
+  float2 xc[CONV ? TS : 1][2];
+  if (CONV) conv_front<IO, CONV ? TS : 1, CH, MASKED>(tx, off0, ct, fl, hist, xc);
 #pragma unroll
   for (int st = 0; st < TS; ++st) {
     const int off = off0 + st * ROWB;
     float2 xv[2], rv[2], iv[2];
-    Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
+    if (CONV) { xv[0] = xc[CONV ? st : 0][0]; xv[1] = xc[CONV ? st : 0][1]; }
+    else Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
     Pack<IO>::unpack2(Pack<IO>::load(tr + off), rv);
     Pack<IO>::unpack2(Pack<IO>::load(ti + off), iv);
     const RowMask m = row_mask<MASKED>(fl[st >> 2], st);
@@ -141,11 +225,13 @@ __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, 
   }
 }
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false>
 struct FwdSmem {
   static constexpr int TC = LANES * TS;
   static constexpr int TILE = TC * CH * sizeof(IO);
-  static constexpr int STAGE = 3 * TILE;
+  static constexpr int HALO = CONV ? 3 * CH * sizeof(IO) : 0;   // three rows in front of the x tile
+  static constexpr int TILEX = TILE + HALO;
+  static constexpr int STAGE = TILEX + 2 * TILE;
   static constexpr int OFF_AGG = NSTAGE * STAGE;
   static constexpr int OFF_EIN = OFF_AGG + ChainSmem<LANES, CH>::AGG;
   static constexpr int OFF_BAR = OFF_EIN + ChainSmem<LANES, CH>::EIN;   // full[NSTAGE], ready[NSTAGE], dead flag
@@ -154,10 +240,11 @@ struct FwdSmem {
 
 // Threads [0, LANES*NCV) compute; with TMA one extra warp issues every bulk copy so that
 // no compute warp ever waits on the copy engine's instruction latency.
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
-  using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE>;
+  using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV>;
+  static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
   constexpr int ROWB = CH * sizeof(IO);
@@ -203,15 +290,15 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
         const int sidx = k % NSTAGE;
         uint8_t* st = smem + sidx * SM::STAGE;
         mbar_expect_tx(&full[sidx], SM::STAGE);
-        tma_load_3d(st, &maps.x, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::TILE, &maps.ur, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + 2 * SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
+        tma_load_3d(st + SM::TILEX, &maps.ur, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
       };
       for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
       for (int k = 0; k < nchunks; ++k) {
         const int sidx = k % NSTAGE;
         mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
-        tma_store_3d(&maps.y, smem + sidx * SM::STAGE, d0, k * TC, b);
+        tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);
         tma_commit();
         if (k + NSTAGE < nchunks) {
           tma_wait_read<0>();
@@ -224,6 +311,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
   }
 
   if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && p.ticket) *p.ticket = 0u;   // consumed by the backward kernel
+
+  ConvTaps ct;
+  if (CONV) load_taps(p.conv_w, p.conv_b, d0 + vec * CV, p.D, ct);
 
   // Level-two chain state: thread `tid` < CH carries channel d0 + tid across chunks.
   float carry = 0.0f;
@@ -243,22 +333,28 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     if (USE_TMA) {
       mbar_wait_or_flag(&full[stage], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
     } else {
-      tile_load_plain<IO, CH>(tiles, p.x, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO, CH>(tiles + SM::TILE, p.ur, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO, CH>(tiles + 2 * SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles, p.x, b, t0 - (CONV ? 3 : 0), d0, TC + (CONV ? 3 : 0), p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::TILEX, p.ur, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::TILEX + SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
 
     float2 P[TS][2], S[TS][2];
     const uint8_t* tx = tiles;
-    const uint8_t* tr = tiles + SM::TILE;
-    const uint8_t* ti = tiles + 2 * SM::TILE;
+    const uint8_t* tr = tiles + SM::TILEX;
+    const uint8_t* ti = tiles + SM::TILEX + SM::TILE;
+    float2 hist_v[3][2];
+    const float2 (*hist)[2] = nullptr;
+    if (CONV && k == 0 && lane_t == 0 && p.conv_state) {   // history carried from an earlier call
+      load_hist<IO>(p.conv_state, b, d0 + vec * CV, p.D, hist_v);
+      hist = hist_v;
+    }
     if (masked) {
-      if (poly) fwd_local<IO, TS, CH, true, true>(tx, tr, ti, off0, K, fl, P, S);
-      else fwd_local<IO, TS, CH, true, false>(tx, tr, ti, off0, K, fl, P, S);
+      if (poly) fwd_local<IO, TS, CH, true, true, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
+      else fwd_local<IO, TS, CH, true, false, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
     } else {
-      if (poly) fwd_local<IO, TS, CH, false, true>(tx, tr, ti, off0, K, fl, P, S);
-      else fwd_local<IO, TS, CH, false, false>(tx, tr, ti, off0, K, fl, P, S);
+      if (poly) fwd_local<IO, TS, CH, false, true, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
+      else fwd_local<IO, TS, CH, false, false, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
     }
     {
       float4* dst = reinterpret_cast<float4*>(agg + lane_t * CH + vec * CV);
@@ -289,7 +385,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     {
       const float4 e4 = *reinterpret_cast<const float4*>(ein + lane_t * CH + vec * CV);
       const float2 e[2] = {make_float2(e4.x, e4.y), make_float2(e4.z, e4.w)};
-      uint8_t* ty = tiles;  // y overwrites the x tile in place
+      uint8_t* ty = tiles + SM::HALO;  // y overwrites the x tile in place (past its halo rows)
 #pragma unroll
       for (int st = 0; st < TS; ++st) {
         float2 yv[2];
@@ -304,7 +400,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
       bar_compute(NCOMP);
-      tile_store_plain<IO, CH>(tiles, p.y, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<IO, CH>(tiles + SM::HALO, p.y, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
   }
@@ -330,19 +426,23 @@ struct BwdRegs {
 // Level one of the backward chunk: gate math, coefficients for the second pass, and the
 // lane aggregates.  aggF = (prod a, local state), aggR = (prod a, local reverse carry),
 // where the reverse carry is a_t g_t flowing from step t to step t-1.
-template <typename IO, int TS, int CH, bool MASKED, bool POLY>
+template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV>
 __device__ __forceinline__ void bwd_local(const uint8_t* tdy, const uint8_t* tx, const uint8_t* tr, const uint8_t* ti,
                                           int off0, const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
+                                          const ConvTaps& ct, const float2 (*hist)[2],
                                           BwdRegs<IO, TS>& R, float2 (&prod)[2], float2 (&sfwd)[2],
                                           float2 (&crev)[2]) {
   constexpr int ROWB = CH * sizeof(IO);
   float2 p[2] = {f2(1.0f), f2(1.0f)};
   float2 s[2] = {f2(0.0f), f2(0.0f)};
+  float2 xc[CONV ? TS : 1][2];
+  if (CONV) conv_front<IO, CONV ? TS : 1, CH, MASKED>(tx, off0, ct, fl, hist, xc);
 #pragma unroll
   for (int st = 0; st < TS; ++st) {
     const int off = off0 + st * ROWB;
     float2 xv[2], rv[2], iv[2];
-    Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
+    if (CONV) { xv[0] = xc[CONV ? st : 0][0]; xv[1] = xc[CONV ? st : 0][1]; }
+    else Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
     Pack<IO>::unpack2(Pack<IO>::load(tr + off), rv);
     Pack<IO>::unpack2(Pack<IO>::load(ti + off), iv);
     R.dy[st] = Pack<IO>::load(tdy + off);
@@ -395,11 +495,14 @@ __device__ __forceinline__ void bwd_local(const uint8_t* tdy, const uint8_t* tx,
   for (int cp = 0; cp < 2; ++cp) { prod[cp] = p[cp]; sfwd[cp] = s[cp]; crev[cp] = c[cp]; }
 }
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false>
 struct BwdSmem {
   static constexpr int TC = LANES * TS;
   static constexpr int TILE = TC * CH * sizeof(IO);
-  static constexpr int STAGE = 4 * TILE;
+  static constexpr int HALO = CONV ? 3 * CH * sizeof(IO) : 0;   // three rows in front of the x tile
+  static constexpr int TILEX = TILE + HALO;
+  static constexpr int OFF_X = TILE, OFF_UR = TILE + TILEX, OFF_UI = 2 * TILE + TILEX;   // after the dy tile
+  static constexpr int STAGE = 3 * TILE + TILEX;
   static constexpr int OFF_AGGF = NSTAGE * STAGE;
   static constexpr int OFF_AGGR = OFF_AGGF + ChainSmem<LANES, CH>::AGG;
   static constexpr int OFF_EINF = OFF_AGGR + ChainSmem<LANES, CH>::AGG;
@@ -408,10 +511,11 @@ struct BwdSmem {
   static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, int MINB>
-__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV>
+__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
     rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
-  using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE>;
+  using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE, CONV>;
+  static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
   static_assert(TC % SAVE_EVERY == 0, "backward chunks must start on a saved state");
@@ -462,9 +566,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
         uint8_t* st = smem + sidx * SM::STAGE;
         mbar_expect_tx(&full[sidx], SM::STAGE);
         tma_load_3d(st, &maps.dy, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::TILE, &maps.x, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + 2 * SM::TILE, &maps.ur, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + 3 * SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::OFF_X, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);
+        tma_load_3d(st + SM::OFF_UR, &maps.ur, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::OFF_UI, &maps.ui, d0, k * TC, b, &full[sidx]);
       };
       for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
       for (int q = 0; q < nchunks; ++q) {
@@ -472,9 +576,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
         const int sidx = q % NSTAGE;
         uint8_t* st = smem + sidx * SM::STAGE;
         mbar_wait_or_flag(&ready[sidx], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
-        tma_store_3d(&maps.dx, st + SM::TILE, d0, k * TC, b);
-        tma_store_3d(&maps.dur, st + 2 * SM::TILE, d0, k * TC, b);
-        tma_store_3d(&maps.dui, st + 3 * SM::TILE, d0, k * TC, b);
+        tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
+        tma_store_3d(&maps.dur, st + SM::OFF_UR, d0, k * TC, b);
+        tma_store_3d(&maps.dui, st + SM::OFF_UI, d0, k * TC, b);
         tma_commit();
         if (q + NSTAGE < nchunks) {
           tma_wait_read<0>();
@@ -493,6 +597,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
   const bool rev_chain = tid >= CH && tid < 2 * CH;
   float carry_rev = 0.0f;
   if (rev_chain && dch < p.D && p.dh_last) carry_rev = p.dh_last[static_cast<size_t>(b) * p.D + dch];
+
+  ConvTaps ct;
+  if (CONV) load_taps(p.conv_w, p.conv_b, d0 + vec * CV, p.D, ct);
 
   float2 dlam[2] = {f2(0.0f), f2(0.0f)};
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
@@ -517,9 +624,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
       mbar_wait_or_flag(&full[stage], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
     } else {
       tile_load_plain<IO, CH>(tiles, p.dy, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO, CH>(tiles + SM::TILE, p.x, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO, CH>(tiles + 2 * SM::TILE, p.ur, b, t0, d0, TC, p.T, p.D);
-      tile_load_plain<IO, CH>(tiles + 3 * SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::OFF_X, p.x, b, t0 - (CONV ? 3 : 0), d0, TC + (CONV ? 3 : 0), p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::OFF_UR, p.ur, b, t0, d0, TC, p.T, p.D);
+      tile_load_plain<IO, CH>(tiles + SM::OFF_UI, p.ui, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
 
@@ -527,15 +634,21 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
     float2 prod[2], sfwd[2], crev[2];
     {
       const uint8_t* tdy = tiles;
-      const uint8_t* tx = tiles + SM::TILE;
-      const uint8_t* tr = tiles + 2 * SM::TILE;
-      const uint8_t* ti = tiles + 3 * SM::TILE;
+      const uint8_t* tx = tiles + SM::OFF_X;
+      const uint8_t* tr = tiles + SM::OFF_UR;
+      const uint8_t* ti = tiles + SM::OFF_UI;
+      float2 hist_v[3][2];
+      const float2 (*hist)[2] = nullptr;
+      if (CONV && k == 0 && lane_t == 0 && p.conv_state) {
+        load_hist<IO>(p.conv_state, b, d0 + vec * CV, p.D, hist_v);
+        hist = hist_v;
+      }
       if (masked) {
-        if (poly) bwd_local<IO, TS, CH, true, true>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
-        else bwd_local<IO, TS, CH, true, false>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
+        if (poly) bwd_local<IO, TS, CH, true, true, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, true, false, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
       } else {
-        if (poly) bwd_local<IO, TS, CH, false, true>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
-        else bwd_local<IO, TS, CH, false, false>(tdy, tx, tr, ti, off0, K, fl, R, prod, sfwd, crev);
+        if (poly) bwd_local<IO, TS, CH, false, true, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, false, false, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
       }
     }
     {
@@ -587,9 +700,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
           R.hb[st][cp] = hin;
         }
       }
-      uint8_t* tdx = tiles + SM::TILE;       // over x
-      uint8_t* tdr = tiles + 2 * SM::TILE;   // over u_r
-      uint8_t* tdi = tiles + 3 * SM::TILE;   // over u_i
+      uint8_t* tdx = tiles + SM::OFF_X + SM::HALO;   // over x (past its halo rows)
+      uint8_t* tdr = tiles + SM::OFF_UR;             // over u_r
+      uint8_t* tdi = tiles + SM::OFF_UI;             // over u_i
       const float2 nK[2] = {mul2(K[0], f2(-1.0f)), mul2(K[1], f2(-1.0f))};
 #pragma unroll
       for (int st = TS - 1; st >= 0; --st) {
@@ -619,9 +732,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), MINB)
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
       bar_compute(NCOMP);
-      tile_store_plain<IO, CH>(tiles + SM::TILE, p.dx, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<IO, CH>(tiles + 2 * SM::TILE, p.dur, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<IO, CH>(tiles + 3 * SM::TILE, p.dui, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<IO, CH>(tiles + SM::OFF_X + SM::HALO, p.dx, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<IO, CH>(tiles + SM::OFF_UR, p.dur, b, t0, d0, TC, p.T, p.D);
+      tile_store_plain<IO, CH>(tiles + SM::OFF_UI, p.dui, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
   }
@@ -1029,11 +1142,11 @@ static cudaError_t set_smem(Kern kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA>;
-  constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST>::BYTES;
+  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV>;
+  constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV>::BYTES;
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
@@ -1057,11 +1170,11 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
   return bf16 ? launch_fwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_fwd_io<float>(use_tma, variant, maps, a, s);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, 1>;
-  constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST>::BYTES;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV>;
+  constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV>::BYTES;
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
@@ -1086,6 +1199,22 @@ static cudaError_t launch_bwd_io(bool use_tma, int variant, const BwdMaps& maps,
 cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& a,
                             cudaStream_t s) {
   return bf16 ? launch_bwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_bwd_io<float>(use_tma, variant, maps, a, s);
+}
+
+// Conv folded into the load stage: one shape (64 channels x 64 steps); the x map's box has three more rows.
+cudaError_t launch_conv_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
+  if (bf16)
+    return use_tma ? launch_fwd_t<__nv_bfloat16, Shape64x16x4, 4, true, true>(maps, a, s)
+                   : launch_fwd_t<__nv_bfloat16, Shape64x16x4, 1, false, true>(maps, a, s);
+  return use_tma ? launch_fwd_t<float, Shape64x16x4, 3, true, true>(maps, a, s)
+                 : launch_fwd_t<float, Shape64x16x4, 1, false, true>(maps, a, s);
+}
+cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
+  if (bf16)
+    return use_tma ? launch_bwd_t<__nv_bfloat16, Shape64x16x4, 4, true, true>(maps, a, s)
+                   : launch_bwd_t<__nv_bfloat16, Shape64x16x4, 1, false, true>(maps, a, s);
+  return use_tma ? launch_bwd_t<float, Shape64x16x4, 3, true, true>(maps, a, s)
+                 : launch_bwd_t<float, Shape64x16x4, 1, false, true>(maps, a, s);
 }
 
 int raw_box_rows() { return RAW_TC; }

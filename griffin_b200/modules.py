@@ -199,8 +199,11 @@ class RecurrentBlock(nn.Module):
     """
 
     def __init__(self, input_dim: int, rnn_width: int, conv_kernel_size: int = 4, gate_blocks: int = 16,
-                 final_w_init_variance_scale: float = 1.0, scan_mode: str = "cuda"):
+                 final_w_init_variance_scale: float = 1.0, scan_mode: str = "cuda", *, fold_conv: bool = False):
         super().__init__()
+        # fold_conv (not in the reference): run conv, gates and scan as one autograd node whose scan kernels
+        # apply the conv while loading, so the conv output is not kept for backward (recomputed there instead).
+        self.fold_conv = fold_conv
         if conv_kernel_size <= 0:
             raise ValueError("conv_kernel_size must be positive")
         if conv_kernel_size != 4:
@@ -254,9 +257,19 @@ class RecurrentBlock(nn.Module):
             flags = token_flags(batch, steps, x.device, reset=pos == 0, active=active_mask, segment_pos=pos, padded=padded)
 
         conv_w = self.temporal_conv.weight[:, 0, :]
-        x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags)
         rnn_state = None if cache is None else cache.rnn_state
-        y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags)
+        if self.fold_conv:
+            if not x_in.is_cuda:
+                raise RuntimeError("scan_mode='cuda' requires CUDA tensors; there is no CPU fallback")
+            if rnn_state is not None and rnn_state.shape != (batch, self.rnn_width):
+                raise ValueError(f"ht_minus_1 must have shape ({batch}, {self.rnn_width}), got {tuple(rnn_state.shape)}")
+            lru = self.rg_lru
+            y, new_rnn, new_conv = ops.recurrent_core(
+                x_in, conv_w, self.temporal_conv.bias, conv_state, lru.recurrence_gate.weight, lru.recurrence_gate.bias,
+                lru.input_gate.weight, lru.input_gate.bias, lru.Lambda, rnn_state, flags, lru.c)
+        else:
+            x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags)
+            y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags)
         out = self.linear_out(y * y_branch)
         if active_mask is not None:
             out = torch.where(active_mask[..., None], out, torch.zeros_like(out))

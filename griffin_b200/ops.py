@@ -287,6 +287,127 @@ def causal_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state
     return _conv_fwd(x_in.contiguous(), w, b, st, None if tok is None else tok.contiguous())
 
 
+# ----------------------------------------------------------------------------- conv folded into the scan
+def conv_scan_fwd(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_state: Optional[Tensor], u_r: Tensor,
+                  u_i: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor], c: float, save: bool
+                  ) -> tuple[Tensor, Tensor, Tensor]:
+    """y, h_last, workspace = RG-LRU(conv(x_in) | u_r, u_i) with the conv applied while chunks are loaded
+    (``rglru_conv_scan_fwd``).  All tensors contiguous; ``conv_w`` [D,4] / ``conv_b`` / ``lam`` / ``h0`` fp32."""
+    lib = _lib.load()
+    _require_cuda(x_in, conv_w, conv_b, conv_state, u_r, u_i, lam, h0, tok)
+    dt = _io_dtype(x_in, "conv-scan forward")
+    B, T, D = x_in.shape
+    y = torch.empty_like(x_in)
+    h_last = torch.empty(B, D, device=x_in.device, dtype=torch.float32)
+    nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
+    ws = torch.empty(nbytes, device=x_in.device, dtype=torch.uint8)
+    with torch.cuda.device(x_in.device):
+        rc = lib.rglru_conv_scan_fwd(_ptr(x_in), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state), _ptr(u_r), _ptr(u_i),
+                                     _ptr(lam), _ptr(h0), _ptr(tok), _ptr(y), _ptr(h_last),
+                                     _ptr(ws) if save else None, nbytes, B, T, D, c, dt, _stream(x_in))
+    _lib.check(rc, "rglru_conv_scan_fwd")
+    return y, h_last, ws
+
+
+def conv_scan_bwd(dy: Tensor, dh_last: Optional[Tensor], x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor],
+                  conv_state: Optional[Tensor], u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor],
+                  tok: Optional[Tensor], ws: Tensor, c: float, want_dh0: bool
+                  ) -> tuple[Tensor, Tensor, Tensor, Tensor, Optional[Tensor]]:
+    """Backward of :func:`conv_scan_fwd`: (d x_conv direct path, d u_r, d u_i, d Lambda, d h0)."""
+    lib = _lib.load()
+    dt = _io_dtype(x_in, "conv-scan backward")
+    B, T, D = x_in.shape
+    dxc, du_r, du_i = torch.empty_like(x_in), torch.empty_like(x_in), torch.empty_like(x_in)
+    dlam = torch.empty(D, device=x_in.device, dtype=torch.float32)
+    dh0 = torch.empty(B, D, device=x_in.device, dtype=torch.float32) if want_dh0 else None
+    with torch.cuda.device(x_in.device):
+        rc = lib.rglru_conv_scan_bwd(_ptr(dy), _ptr(dh_last), _ptr(x_in), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state),
+                                     _ptr(u_r), _ptr(u_i), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(ws), ws.numel(),
+                                     _ptr(dxc), _ptr(du_r), _ptr(du_i), _ptr(dlam), _ptr(dh0), B, T, D, c, dt,
+                                     _stream(x_in))
+    _lib.check(rc, "rglru_conv_scan_bwd")
+    return dxc, du_r, du_i, dlam, dh0
+
+
+def _gate(x: Tensor, weight: Tensor, bias: Tensor) -> Tensor:
+    """Block-diagonal projection [.., G*in] -> [.., G*out] in x's dtype (weight [G, out, in])."""
+    g, wo, wi = weight.shape
+    rows = x.reshape(-1, g, wi).transpose(0, 1)
+    out = torch.baddbmm(bias.to(x.dtype)[:, None, :], rows, weight.to(x.dtype).transpose(1, 2))
+    return out.transpose(0, 1).reshape(*x.shape[:-1], g * wo).contiguous()   # reshape may return a strided view
+
+
+def _gate_backward(du: Tensor, x: Tensor, weight: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+    """(d x, d weight, d bias) of :func:`_gate`."""
+    g, wo, wi = weight.shape
+    rows = x.reshape(-1, g, wi).transpose(0, 1)            # [G, N, in]
+    d = du.reshape(-1, g, wo).transpose(0, 1)              # [G, N, out]
+    dx = torch.bmm(d, weight.to(du.dtype)).transpose(0, 1).reshape(x.shape).contiguous()
+    dw = torch.bmm(d.transpose(1, 2), rows).to(weight.dtype)
+    db = d.sum(dim=1, dtype=torch.float32)
+    return dx, dw, db
+
+
+class _RecurrentCore(torch.autograd.Function):
+    """conv -> gate projections -> RG-LRU as one autograd node that keeps only the conv INPUT.
+
+    Forward materialises the conv output once for the two gate GEMMs and drops it; the scan kernels read the
+    conv input and redo the four taps in their load stage.  Backward recomputes the conv output (one streaming
+    pass) for the gate-weight gradients, sums the direct and gate paths and runs a single conv backward.
+    """
+
+    @staticmethod
+    def forward(ctx, x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, tok, c):
+        x_in = x_in.contiguous()
+        cw = conv_w.to(torch.float32).contiguous()
+        cb = None if conv_b is None else conv_b.to(torch.float32).contiguous()
+        cs = None if conv_state is None else conv_state.to(x_in.dtype).contiguous()
+        lam32 = lam.to(torch.float32).contiguous()
+        h032 = None if h0 is None else h0.to(torch.float32).contiguous()
+        x_conv, new_state = _conv_fwd(x_in, cw, cb, cs, tok)
+        u_r = _gate(x_conv, w_r, b_r)
+        u_i = _gate(x_conv, w_i, b_i)
+        del x_conv
+        save = any(ctx.needs_input_grad)
+        y, h_last, ws = conv_scan_fwd(x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, float(c), save)
+        ctx.save_for_backward(x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws)
+        ctx.c = float(c)
+        ctx.meta = (conv_w.dtype, None if conv_b is None else conv_b.dtype, b_r.dtype, b_i.dtype, lam.dtype)
+        ctx.mark_non_differentiable(new_state)
+        return y, h_last, new_state
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dy, dh_last, _d_state):
+        x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws = ctx.saved_tensors
+        if ws.numel() == 0:
+            raise RuntimeError("recurrent core was run without saving its workspace; backward is unavailable")
+        dy = dy.contiguous()
+        dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
+        want_dh0 = h032 is not None and ctx.needs_input_grad[9]
+        dxc, du_r, du_i, dlam, dh0 = conv_scan_bwd(dy, dh_last, x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, ws,
+                                                   ctx.c, want_dh0)
+        x_conv, _ = _conv_fwd(x_in, cw, cb, cs, tok)          # recomputed, not saved
+        dx_r, dw_r, db_r = _gate_backward(du_r, x_conv, w_r)
+        dx_i, dw_i, db_i = _gate_backward(du_i, x_conv, w_i)
+        total = (dxc + dx_r + dx_i).contiguous()
+        want_state = cs is not None and ctx.needs_input_grad[3]
+        dx_in, d_w, d_b, d_state = _conv_bwd(total, x_in, cw, cs, tok, want_state)
+        wdt, bdt, brdt, bidt, ldt = ctx.meta
+        return (dx_in, d_w.to(wdt), None if cb is None else d_b.to(bdt), d_state if want_state else None,
+                dw_r, db_r.to(brdt), dw_i, db_i.to(bidt), dlam.to(ldt), dh0, None, None)
+
+
+def recurrent_core(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_state: Optional[Tensor],
+                   w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor, h0: Optional[Tensor] = None,
+                   tok: Optional[Tensor] = None, c: float = 8.0) -> tuple[Tensor, Tensor, Tensor]:
+    """(y, h_last, new_conv_state) of conv k=4 -> block-diagonal gates -> RG-LRU, keeping only ``x_in`` for backward."""
+    if x_in.dim() != 3 or conv_w.shape != (x_in.shape[2], 4):
+        raise ValueError("x_in must be [batch, sequence, width] and conv_w [width, 4]")
+    return _RecurrentCore.apply(x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0,
+                                None if tok is None else tok.contiguous(), c)
+
+
 # ----------------------------------------------------------------------------- decode (in-place state, no autograd)
 def decode_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state: Tensor,
                 tok: Optional[Tensor] = None) -> Tensor:

@@ -99,6 +99,26 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
               void* dx, void* du_r, void* du_i, float* dlambda, float* dh0, int B, int T, int D,
               float c, int io_dtype, void* stream);
 
+/* Conv folded into the scan's load stage.  rglru_conv_scan_fwd computes rglru_fwd(conv(x_in), u_r, u_i)
+ * and rglru_conv_scan_bwd the matching rglru_bwd, both reading the conv INPUT x_in (the output of linear_x,
+ * griffin/griffin.py:465) with a three-token halo and applying the four taps, bias and document-boundary
+ * tap masks of griffin/griffin.py:474-486 while a chunk is loaded, so the conv output need not be kept for
+ * the backward pass.  u_r / u_i are still the gate pre-activations of the conv OUTPUT (the gate GEMMs are
+ * the caller's and need that tensor once, from rglru_conv_fwd).
+ *   conv_w [D,4] fp32 (column 3 on the current token), conv_b [D] fp32 or NULL,
+ *   conv_state [B,3,D] io_dtype history before t = 0 or NULL (zeros); other arguments as rglru_fwd / rglru_bwd.
+ *   rglru_conv_scan_bwd writes dx_conv = the gradient with respect to the conv OUTPUT through b = gamma i x
+ *   only; the caller adds the gate-projection path and runs rglru_conv_bwd once on the sum.
+ * Inactive (padding) tokens are handled as in rglru_fwd; the tok bytes must carry the tap-cut bits. */
+int rglru_conv_scan_fwd(const void* x_in, const float* conv_w, const float* conv_b, const void* conv_state,
+                        const void* u_r, const void* u_i, const float* lambda, const float* h0, const uint8_t* tok,
+                        void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c, int io_dtype,
+                        void* stream);
+int rglru_conv_scan_bwd(const void* dy, const float* dh_last, const void* x_in, const float* conv_w, const float* conv_b,
+                        const void* conv_state, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+                        const uint8_t* tok, void* ws, size_t ws_bytes, void* dx_conv, void* du_r, void* du_i,
+                        float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype, void* stream);
+
 /* Raw affine scan h_t = a_t h_{t-1} + b_t on fp32 tensors: the operator
  * fused_rglru_scan(decay, current_input, initial_state) of griffin/triton_scan.py:274-276
  * (forward kernel :31-60).  decay, drive, out: [B,T,D] fp32; h0: [B,D] fp32 or NULL. */

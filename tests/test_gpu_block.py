@@ -188,3 +188,78 @@ def test_block_bf16_against_fp32_oracle():
     assert orc.rel_l2(xg.grad, xr.grad) <= BF16_REL
     for key, p in blk.named_parameters():
         assert orc.rel_l2(p.grad, params[key].grad) <= 3e-2, key
+
+
+# ---------------------------------------------------------------- conv folded into the scan's load stage
+@pytest.mark.parametrize("shape", [(2, 150, 128), (3, 67, 64), (2, 70, 72), (1, 9, 20)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_conv_scan_kernels_against_oracle(shape, dtype):
+    """rglru_conv_scan_fwd / _bwd through the C ABI: conv (with a carried state and a document boundary)
+    fused into the scan, against the oracle's conv followed by its O(T) RG-LRU backward."""
+    from griffin_b200 import ops
+    from griffin_b200.modules import token_flags
+    B, T, D = shape
+    gen = torch.Generator().manual_seed(7 * T + D)
+    x_in = torch.randn(B, T, D, generator=gen).to(dtype)
+    u_r = torch.randn(B, T, D, generator=gen).to(dtype)
+    u_i = torch.randn(B, T, D, generator=gen).to(dtype)
+    dy = torch.randn(B, T, D, generator=gen).to(dtype)
+    w = torch.randn(D, 4, generator=gen) * 0.5
+    bias = torch.randn(D, generator=gen) * 0.1
+    state = torch.randn(B, 3, D, generator=gen).to(dtype)
+    lam = orc.init_lambda(D, 8.0, gen)
+    h0 = torch.randn(B, D, generator=gen)
+    dh = torch.randn(B, D, generator=gen)
+    seg = torch.arange(T)[None, :].repeat(B, 1) + 2
+    if T > 8:
+        seg[:, T // 2:] = torch.arange(T - T // 2)
+    reset = seg == 0
+    xc_ref, _ = orc.causal_conv_dense(x_in.double(), w.double(), bias.double(), state.double(), seg)
+    want = orc.rglru_backward_linear(xc_ref, u_r.double(), u_i.double(), lam.double(), dy.double(), h0=h0, dh_last=dh,
+                                     reset=reset)
+    flags = token_flags(B, T, DEV, reset=reset.to(DEV), segment_pos=seg.to(DEV))
+    args = [t.to(DEV).contiguous() for t in (x_in, w, bias, state, u_r, u_i, lam, h0)]
+    y, h_last, ws = ops.conv_scan_fwd(*args, flags, 8.0, True)
+    dxc, du_r, du_i, dlam, dh0 = ops.conv_scan_bwd(dy.to(DEV), dh.to(DEV), *args, flags, ws, 8.0, True)
+    tol = FP32_REL if dtype == torch.float32 else BF16_REL
+    got = {"y": y, "h_last": h_last, "dx": dxc, "du_r": du_r, "du_i": du_i, "dLambda": dlam, "dh0": dh0}
+    for key, val in got.items():
+        err = orc.rel_l2(val, want[key])
+        assert err <= tol, (key, err)
+
+
+def test_folded_block_matches_reference_gradients_and_cache():
+    """RecurrentBlock(fold_conv=True): same outputs, gradients and caches as the reference's stored results."""
+    from griffin_b200 import RecurrentBlock
+    case = load_golden("block_grads")
+    blk = RecurrentBlock(16, 32, gate_blocks=4, scan_mode="cuda", fold_conv=True)
+    blk.load_state_dict(params_of(case))
+    blk = blk.to(DEV)
+    x = case["x"].to(DEV).requires_grad_(True)
+    out = blk(x)
+    (out * case["dout"].to(DEV)).sum().backward()
+    assert orc.rel_l2(out, case["out"]) <= FP32_REL
+    assert orc.rel_l2(x.grad, case["dx"]) <= FP32_REL
+    for key, p in blk.named_parameters():
+        assert orc.rel_l2(p.grad, case["g." + key]) <= FP32_REL, key
+
+    case = load_golden("block_chunked")
+    blk = RecurrentBlock(8, 12, scan_mode="cuda", fold_conv=True)
+    blk.load_state_dict(params_of(case))
+    blk = blk.to(DEV).eval()
+    x = case["x"].to(DEV)
+    with torch.no_grad():
+        a, c1 = blk(x[:, :3], return_cache=True)
+        b, c2 = blk(x[:, 3:7], c1, return_cache=True)
+        c, c3 = blk(x[:, 7:], c2, return_cache=True)
+    torch.testing.assert_close(torch.cat([a, b, c], 1).cpu(), case["chunks"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(c3.rnn_state.cpu(), case["c3.rnn"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(c3.conv_state.cpu(), case["c3.conv"], atol=1e-6, rtol=1e-6)
+
+    case = load_golden("block_reset")
+    blk = RecurrentBlock(8, 16, gate_blocks=4, scan_mode="cuda", fold_conv=True)
+    blk.load_state_dict(params_of(case))
+    blk = blk.to(DEV).eval()
+    with torch.no_grad():
+        out = blk(case["x"].to(DEV), segment_pos=case["segment_pos"].to(DEV))
+    torch.testing.assert_close(out.cpu(), case["full"], atol=2e-6, rtol=2e-5)
