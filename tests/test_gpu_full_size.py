@@ -1,0 +1,119 @@
+"""Parity and size-independent properties at the benchmark's full sizes.
+
+The reference's own backward is O(T^2) on CPU, so at these sizes the oracle's O(T) closed-form backward
+(validated against the reference's autograd on the golden cases) is the checker; channels and batch rows
+are independent recurrences, so a channel slab of a large problem can be checked on its own.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import rglru_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+BF16_REL = 2e-2
+FP32_REL = 1e-5
+
+
+def _inputs(B, T, D, dtype, seed):
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    mk = lambda: torch.randn(B, T, D, device=DEV, generator=gen).to(dtype)
+    cpu_gen = torch.Generator().manual_seed(seed)
+    lam = orc.init_lambda(D, 8.0, cpu_gen).to(DEV)
+    return mk(), mk(), mk(), mk(), lam
+
+
+def _run(x, u_r, u_i, dy, lam, h0=None, dh=None):
+    from griffin_b200 import ops
+    xs = [t.detach().clone().requires_grad_(True) for t in (x, u_r, u_i)]
+    lam = lam.detach().clone().requires_grad_(True)
+    y, h_last = ops.rglru(xs[0], xs[1], xs[2], lam, h0)
+    loss = (y.float() * dy.float()).sum()
+    if dh is not None:
+        loss = loss + (h_last * dh).sum()
+    loss.backward()
+    return {"y": y.detach(), "h_last": h_last.detach(), "dx": xs[0].grad, "du_r": xs[1].grad, "du_i": xs[2].grad,
+            "dLambda": lam.grad}
+
+
+def _oracle_slab(x, u_r, u_i, dy, lam, sl, rows):
+    cut = lambda t: t[rows, :, sl].double().cpu()
+    return orc.rglru_backward_linear(cut(x), cut(u_r), cut(u_i), lam[sl].double().cpu(), cut(dy))
+
+
+def test_config1_full_shape_bf16_against_oracle():
+    """BASELINE config 1: bf16 I/O, B=8, T=2048, D=1024 -- every output and gradient, all channels."""
+    x, u_r, u_i, dy, lam = _inputs(8, 2048, 1024, torch.bfloat16, 1)
+    got = _run(x, u_r, u_i, dy, lam)
+    want = _oracle_slab(x, u_r, u_i, dy, lam, slice(None), slice(None))
+    for key in ("y", "h_last", "dx", "du_r", "du_i", "dLambda"):
+        err = orc.rel_l2(got[key], want[key])
+        assert err <= BF16_REL, (key, err)
+
+
+def test_config3_layer_shape_fp32_against_oracle():
+    """The same shape with fp32 I/O (what the RG-LRU sees inside the 100M model): 1e-5 on everything,
+    including dLambda, a 16384-term reduction per channel."""
+    x, u_r, u_i, dy, lam = _inputs(8, 2048, 1024, torch.float32, 2)
+    got = _run(x, u_r, u_i, dy, lam)
+    want = _oracle_slab(x, u_r, u_i, dy, lam, slice(None), slice(None))
+    for key in ("y", "h_last", "dx", "du_r", "du_i", "dLambda"):
+        err = orc.rel_l2(got[key], want[key])
+        assert err <= FP32_REL, (key, err)
+
+
+def test_config4_long_wide_slab_and_properties():
+    """Config 4 geometry (T=8192, D=5632, bf16) at B=2: a 256-channel slab against the oracle, plus
+    properties that need no oracle: time-chunked == whole, backward is linear in the upstream gradient,
+    rows are independent, repeated runs are bit-identical."""
+    from griffin_b200 import ops
+    B, T, D = 2, 8192, 5632
+    x, u_r, u_i, dy, lam = _inputs(B, T, D, torch.bfloat16, 3)
+    got = _run(x, u_r, u_i, dy, lam)
+    sl = slice(2048, 2304)
+    want = _oracle_slab(x, u_r, u_i, dy, lam, sl, slice(0, 1))
+    for key in ("y", "dx", "du_r", "du_i"):
+        err = orc.rel_l2(got[key][0:1, :, sl], want[key])
+        assert err <= BF16_REL, (key, err)
+    assert orc.rel_l2(got["h_last"][0:1, sl], want["h_last"]) <= BF16_REL
+
+    with torch.no_grad():
+        # whole == two time chunks with the fp32 state carried across
+        cutp = 3000
+        ya, ha = ops.rglru(x[:, :cutp].contiguous(), u_r[:, :cutp].contiguous(), u_i[:, :cutp].contiguous(), lam)
+        yb, hb = ops.rglru(x[:, cutp:].contiguous(), u_r[:, cutp:].contiguous(), u_i[:, cutp:].contiguous(), lam, ha)
+        assert orc.rel_l2(torch.cat([ya, yb], 1), got["y"]) <= 4e-3      # bf16 outputs, fp32 state
+        assert orc.rel_l2(hb, got["h_last"]) <= 1e-5
+        # batch rows are independent: row 1 alone gives the same bits
+        y1, h1 = ops.rglru(x[1:2].contiguous(), u_r[1:2].contiguous(), u_i[1:2].contiguous(), lam)
+        assert torch.equal(y1, got["y"][1:2]) and torch.equal(h1, got["h_last"][1:2])
+    # determinism and linearity of the backward in dy
+    again = _run(x, u_r, u_i, dy, lam)
+    for key in got:
+        assert torch.equal(again[key], got[key]), key
+    doubled = _run(x, u_r, u_i, (2 * dy.float()).to(torch.bfloat16), lam)
+    for key in ("dx", "du_r", "du_i", "dLambda"):
+        assert orc.rel_l2(doubled[key].float(), 2 * got[key].float()) <= 4e-3, key
+
+
+def test_decode_steps_at_config4_batch_against_sequence_kernel():
+    """Config 4 part two geometry (B=512, D=5632, bf16, fp32 carried state): 16 single-token updates equal
+    one 16-step sequence call, and the first step equals the oracle."""
+    from griffin_b200 import ops
+    B, D, S = 512, 5632, 16
+    x, u_r, u_i, _, lam = _inputs(B, S, D, torch.bfloat16, 4)
+    h = torch.zeros(B, D, device=DEV)
+    ys = []
+    for t in range(S):
+        ys.append(ops.decode_step(x[:, t].contiguous(), u_r[:, t].contiguous(), u_i[:, t].contiguous(), lam, h))
+    with torch.no_grad():
+        y_seq, h_seq = ops.rglru(x, u_r, u_i, lam)
+    assert orc.rel_l2(torch.stack(ys, 1), y_seq) <= 4e-3
+    assert orc.rel_l2(h, h_seq) <= 2e-3      # decode gates use ex2/rcp, the sequence kernel the tanh unit
+    rows = slice(0, 4)
+    y_ref, h_ref = orc.rglru_core(x[rows, :1].float().cpu(), u_r[rows, :1].float().cpu(), u_i[rows, :1].float().cpu(),
+                                  lam.cpu())
+    assert orc.rel_l2(ys[0][rows], y_ref[:, 0]) <= BF16_REL
