@@ -491,7 +491,7 @@ def run_lm(args) -> dict:
     clocks = sampler.stop()
     out = {"metric": "griffin100m_train_tokens_per_s", "value": world * B * T / ms * 1e3, "unit": "tokens/s",
            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-           "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast (fp32 at the RG-LRU boundary)", "data": "synthetic",
+           "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast (RG-LRU: bf16 I/O, fp32 state and arithmetic)", "data": "synthetic",
            "config": {"workload": f"c3: Griffin-100M ({nparams} params) train step B={B}/GPU T={T} vocab {V}, AdamW, "
                                   f"{'DDP/NCCL' if world > 1 else 'single GPU'}",
                       "l2": "activations of one step far exceed L2"},
