@@ -187,4 +187,16 @@ class GriffinModel(nn.Module):
             x = torch.where(token_mask[..., None], x, torch.zeros_like(x))
         for layer in self.layers:
             x = layer(x, segment_pos, active_mask=token_mask)
-        return self.lm_head(self.final_norm(x))
+        return self._logits(self.final_norm(x))
+
+    def _logits(self, h: Tensor) -> Tensor:
+        """lm_head(h). On CUDA with half-precision autocast and a vocabulary that is not a multiple of 8, the
+        weight is zero-padded to the next multiple while it is cast, so the GEMMs (forward and both backward
+        ones) take the aligned tensor-core kernels; the extra columns are sliced off (a view, same values)."""
+        weight = self.lm_head.weight
+        pad = -self.vocab_size % 8
+        if pad and h.is_cuda and torch.is_autocast_enabled("cuda"):
+            half = torch.get_autocast_dtype("cuda")
+            wide = F.pad(weight.to(half), (0, 0, 0, pad))
+            return F.linear(h.to(half), wide)[..., : self.vocab_size]
+        return F.linear(h, weight)

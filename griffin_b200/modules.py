@@ -195,7 +195,10 @@ class RecurrentBlock(nn.Module):
 
     The two input projections, the GeLU branch and the output projection are ordinary
     torch GEMMs; the conv, the RG-LRU and the single-token decode run on the CUDA kernels.
-    Padding (``active_mask``) must be right padding, which is what the model passes.
+    The kernels take padding (``active_mask``) as right padding; any other mask (left padding, holes) is
+    handled by moving each row's real tokens to the front for the conv and the scan and moving the results
+    back, which is exactly the reference's rule that padding neither enters the conv history nor moves the
+    state (griffin/griffin.py:488-510).
     """
 
     def __init__(self, input_dim: int, rnn_width: int, conv_kernel_size: int = 4, gate_blocks: int = 16,
@@ -242,6 +245,15 @@ class RecurrentBlock(nn.Module):
 
         y_branch = F.gelu(self.linear_y(x), approximate="tanh")
         x_in = self.linear_x(x)
+        restore = None
+        if active_mask is not None and steps > 1 and bool((active_mask[:, 1:] & ~active_mask[:, :-1]).any()):
+            # a real token follows padding somewhere: stable partition of every row, real tokens first
+            order = torch.argsort((~active_mask).to(torch.uint8), dim=1, stable=True)
+            restore = torch.argsort(order, dim=1)
+            x_in = x_in.gather(1, order[..., None].expand(-1, -1, x_in.size(-1)))
+            kernel_pos, kernel_active = pos.gather(1, order), active_mask.gather(1, order)
+        else:
+            kernel_pos, kernel_active = pos, active_mask
         conv_state = None if cache is None else cache.conv_state
         if conv_state is not None and conv_state.shape != (batch, self.conv_kernel_size - 1, self.rnn_width):
             raise ValueError("Recurrent convolution cache has an incompatible shape")
@@ -253,8 +265,9 @@ class RecurrentBlock(nn.Module):
             flags[:, :head] = torch.tensor([3, 2, 1][:head], device=x.device, dtype=torch.uint8)
             flags[:, 0] |= _lib.TOK_RESET
         else:
-            padded = None if active_mask is None else ~active_mask.all()
-            flags = token_flags(batch, steps, x.device, reset=pos == 0, active=active_mask, segment_pos=pos, padded=padded)
+            padded = None if kernel_active is None else ~kernel_active.all()
+            flags = token_flags(batch, steps, x.device, reset=kernel_pos == 0, active=kernel_active,
+                                segment_pos=kernel_pos, padded=padded)
 
         conv_w = self.temporal_conv.weight[:, 0, :]
         rnn_state = None if cache is None else cache.rnn_state
@@ -270,6 +283,8 @@ class RecurrentBlock(nn.Module):
         else:
             x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags)
             y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags)
+        if restore is not None:
+            y = y.gather(1, restore[..., None].expand(-1, -1, y.size(-1)))
         out = self.linear_out(y * y_branch)
         if active_mask is not None:
             out = torch.where(active_mask[..., None], out, torch.zeros_like(out))

@@ -258,6 +258,33 @@ def _block_cases(G):
         out["p." + key] = p
     _save("block_padded", out)
 
+    # padding that is not right padding (left padding, holes), two cached chunks, gradients of the first
+    torch.manual_seed(6)
+    block = G.RecurrentBlock(input_dim=8, rnn_width=16, gate_blocks=4, scan_mode="sequential")
+    with torch.no_grad():
+        block.temporal_conv.weight.normal_(0.0, 0.5)
+        block.temporal_conv.bias.normal_(0.0, 0.1)
+    x = torch.randn(3, 10, 8, requires_grad=True)
+    mask = torch.tensor([[0, 0, 0, 1, 1, 1, 1, 1, 1, 1],
+                         [1, 1, 0, 1, 0, 0, 1, 1, 0, 1],
+                         [0, 1, 1, 1, 1, 0, 0, 0, 0, 0]], dtype=torch.bool)
+    x2 = torch.randn(3, 6, 8)
+    mask2 = torch.tensor([[1, 0, 1, 1, 0, 1], [0, 0, 1, 1, 1, 1], [0, 0, 0, 0, 0, 0]], dtype=torch.bool)
+    dout = torch.randn(3, 10, 8)
+    first, cache = block(x, active_mask=mask, return_cache=True)
+    (first * dout).sum().backward()
+    with torch.no_grad():
+        second, cache2 = block(x2, cache, active_mask=mask2, return_cache=True)
+    out = {"x": x, "active": mask.numpy(), "x2": x2, "active2": mask2.numpy(), "dout": dout, "first": first,
+           "second": second, "dx": x.grad,
+           "c1.rnn": cache.rnn_state, "c1.conv": cache.conv_state, "c1.pos": cache.segment_position,
+           "c2.rnn": cache2.rnn_state, "c2.conv": cache2.conv_state, "c2.pos": cache2.segment_position}
+    for key, p in block.state_dict().items():
+        out["p." + key] = p
+    for key, p in block.named_parameters():
+        out["g." + key] = p.grad
+    _save("block_ragged", out)
+
     # forward + backward through the whole block, conv weights ~ N(0, 1/4)
     torch.manual_seed(4)
     block = G.RecurrentBlock(input_dim=16, rnn_width=32, gate_blocks=4, scan_mode="sequential")

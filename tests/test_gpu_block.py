@@ -77,6 +77,30 @@ def test_right_padded_prefill_then_decode():
         assert torch.equal(cache.segment_position.cpu(), case[f"{tag}.pos"])
 
 
+@pytest.mark.parametrize("fold", [False, True])
+def test_padding_that_is_not_right_padding(fold):
+    """Left padding and holes, two cached chunks, and the gradients of the first (griffin/griffin.py:488-510)."""
+    case = load_golden("block_ragged")
+    blk = _block(case, 8, 16, 4)
+    blk.fold_conv = fold
+    x = case["x"].to(DEV).requires_grad_(True)
+    first, c1 = blk(x, active_mask=case["active"].to(DEV), return_cache=True)
+    (first * case["dout"].to(DEV)).sum().backward()
+    with torch.no_grad():
+        second, c2 = blk(case["x2"].to(DEV), c1, active_mask=case["active2"].to(DEV), return_cache=True)
+    torch.testing.assert_close(first.detach().cpu(), case["first"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(second.cpu(), case["second"], atol=2e-6, rtol=2e-5)
+    assert orc.rel_l2(x.grad.cpu(), case["dx"]) <= 1e-5
+    for tag, cache in (("c1", c1), ("c2", c2)):
+        torch.testing.assert_close(cache.rnn_state.detach().cpu(), case[f"{tag}.rnn"], atol=2e-6, rtol=2e-5)
+        torch.testing.assert_close(cache.conv_state.detach().cpu(), case[f"{tag}.conv"], atol=1e-6, rtol=1e-6)
+        assert torch.equal(cache.segment_position.cpu(), case[f"{tag}.pos"])
+    grads = dict(blk.named_parameters())
+    for key in case:
+        if key.startswith("g."):
+            assert orc.rel_l2(grads[key[2:]].grad.cpu(), case[key]) <= 1e-5, key
+
+
 def test_token_by_token_decode_matches_full():
     """tests/test_griffin_model.py:87-118 family at the block level, plus the dedicated decode kernels."""
     from griffin_b200 import ops

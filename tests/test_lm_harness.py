@@ -51,3 +51,24 @@ def test_tiny_model_logits_loss_and_gradients_gpu(tag):
         if key.startswith(f"{tag}.g."):
             name = key[len(tag) + 3:]
             assert rel_l2(grads[name].grad, case[key]) <= 1e-5, name
+
+
+@pytest.mark.gpu
+def test_padded_vocabulary_head_matches_plain_linear_gpu():
+    """Under autocast the head pads an odd vocabulary for the GEMM; values and the weight gradient must not change."""
+    from griffin_b200.lm import GriffinModel
+    torch.manual_seed(5)
+    model = GriffinModel(1003, 64, 2, 64, 1, attention_heads=2, block_types=("attention",)).cuda()
+    h = torch.randn(4, 48, 64, device="cuda")
+    dlogits = torch.randn(4, 48, 1003, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        padded = model._logits(h)
+        plain = torch.nn.functional.linear(h, model.lm_head.weight)
+    assert padded.shape == plain.shape == (4, 48, 1003) and padded.dtype == torch.bfloat16
+    assert rel_l2(padded.float(), plain.float()) <= 4e-3
+    (g_padded,) = torch.autograd.grad((padded.float() * dlogits).sum(), model.lm_head.weight)
+    (g_plain,) = torch.autograd.grad((plain.float() * dlogits).sum(), model.lm_head.weight)
+    assert g_padded.shape == model.lm_head.weight.shape
+    assert rel_l2(g_padded, g_plain) <= 4e-3
+    exact = model._logits(h)                       # no autocast: the plain fp32 path
+    assert exact.dtype == torch.float32 and rel_l2(padded.float(), exact) <= 2e-2

@@ -176,6 +176,27 @@ def test_block_chunked_reset_padded_decode():
     torch.testing.assert_close(torch.cat(outs, 1), case["steps"], **TIGHT)
 
 
+def test_block_with_padding_that_is_not_right_padding():
+    """Left padding and holes: padding must neither enter the conv history nor move the state (griffin/griffin.py:488-510)."""
+    case = load_golden("block_ragged")
+    p = {k: v.clone().requires_grad_(True) for k, v in params_of(case).items()}
+    x = case["x"].clone().requires_grad_(True)
+    first, c1 = orc.recurrent_block(x, p, active=case["active"])
+    (first * case["dout"]).sum().backward()
+    with torch.no_grad():
+        second, c2 = orc.recurrent_block(case["x2"], p, c1, active=case["active2"])
+    torch.testing.assert_close(first.detach(), case["first"], **TIGHT)
+    torch.testing.assert_close(second, case["second"], **TIGHT)
+    torch.testing.assert_close(x.grad, case["dx"], **TIGHT)
+    for tag, cache in (("c1", c1), ("c2", c2)):
+        torch.testing.assert_close(cache.rnn_state.detach(), case[f"{tag}.rnn"], **TIGHT)
+        torch.testing.assert_close(cache.conv_state.detach(), case[f"{tag}.conv"], **TIGHT)
+        assert torch.equal(cache.segment_position, case[f"{tag}.pos"])
+    for key in case:
+        if key.startswith("g."):
+            torch.testing.assert_close(p[key[2:]].grad, case[key], **TIGHT)
+
+
 def test_block_gradients():
     case = load_golden("block_grads")
     p = {k: v.clone().requires_grad_(True) for k, v in params_of(case).items()}
