@@ -397,7 +397,8 @@ def run_block(args) -> dict:
     dist, world, rank, dev = _dist_setup()
     B, T, DM, DR = 16, 2048, 768, 1024
     torch.manual_seed(rank)
-    blk = RecurrentBlock(DM, DR, gate_blocks=16, scan_mode="cuda")
+    blk = RecurrentBlock(DM, DR, gate_blocks=16, scan_mode="cuda", fold_conv=args.fold == "conv",
+                         fold_merge=args.fold == "merge")
     with torch.no_grad():
         blk.temporal_conv.weight.normal_(0.0, 0.5)       # N(0, 1/4) as the config states
     blk = blk.to(dev, torch.bfloat16)
@@ -434,6 +435,7 @@ def run_block(args) -> dict:
            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 I/O, f32 state", "data": "synthetic",
            "config": {"workload": f"c2: RecurrentBlock fwd+bwd bf16 B={B}/GPU T={T} {DM}->{DR}->{DM}, conv k=4, 16 gate heads",
+                      "fold": args.fold,
                       "l2": "three rotating inputs; 0.6 GB of activations per step"},
            "scan_conv_algorithmic_gbs": world * (22 + 10) * n / ms / 1e6,
            "e2e": {"value": world * n / e2e_ms * 1e3, "unit": "token-channels/s", "h2d_bytes_per_step": 2 * B * T * DM,
@@ -454,7 +456,11 @@ def run_lm(args) -> dict:
     B, T, V = 8, 2048, 50257
     torch.manual_seed(0)
     model = GriffinModel(V, 768, 3, 1024, 12, attention_heads=6, attention_window_size=1024, gate_blocks=16,
-                         scan_mode="cuda").to(dev)
+                         scan_mode="cuda")
+    for layer in model.layers:
+        if hasattr(layer, "recurrent"):
+            layer.recurrent.fold_conv, layer.recurrent.fold_merge = args.fold == "conv", args.fold == "merge"
+    model = model.to(dev)
     nparams = sum(p.numel() for p in model.parameters())
     net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index]) if world > 1 else model
     decay = [p for n_, p in model.named_parameters() if p.dim() >= 2]
@@ -494,7 +500,7 @@ def run_lm(args) -> dict:
            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast (RG-LRU: bf16 I/O, fp32 state and arithmetic)", "data": "synthetic",
            "config": {"workload": f"c3: Griffin-100M ({nparams} params) train step B={B}/GPU T={T} vocab {V}, AdamW, "
                                   f"{'DDP/NCCL' if world > 1 else 'single GPU'}",
-                      "l2": "activations of one step far exceed L2"},
+                      "fold": args.fold, "l2": "activations of one step far exceed L2"},
            "e2e": {"value": world * B * T / e2e_ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B * (T + 1),
                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
            "gpu_launches": 8 * 9 * args.steps, "clocks": clocks, "device_status": _lib.device_status(),
@@ -561,6 +567,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["c2", "c3", "c4b"])
+    ap.add_argument("--fold", default="none", choices=["none", "conv", "merge"],
+                    help="c2/c3: run conv (and the GeLU-branch product) inside the scan kernels")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-kernel-timing", action="store_true", help="skip the per-kernel event pass (for profiler runs)")

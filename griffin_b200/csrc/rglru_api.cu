@@ -324,6 +324,101 @@ int rglru_conv_scan_bwd(const void* dy, const float* dh_last, const void* x_in, 
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
 
+int rglru_merge_fwd(const void* x, const float* conv_w, const float* conv_b, const void* conv_state, const void* u_r,
+                    const void* u_i, const void* branch, const float* lambda, const float* h0, const uint8_t* tok,
+                    void* out, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c, int io_dtype,
+                    void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x || !u_r || !u_i || !branch || !lambda || !out) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const bool conv = conv_w != nullptr;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(x, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(branch, es) || !aligned(out, es) ||
+      !aligned(conv_state, es) || !aligned(lambda, 4) || !aligned(conv_w, 4) || !aligned(conv_b, 4) || !aligned(h0, 4) ||
+      !aligned(h_last, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (ws && ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  ScanFwdArgs a = {};
+  a.x = x; a.ur = u_r; a.ui = u_i; a.y = out; a.g = branch;
+  a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
+  a.states = static_cast<float*>(ws);
+  if (conv) { a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = conv_state; }
+  {
+    const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+    a.ticket = ws ? reinterpret_cast<unsigned*>(static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D +
+                                               static_cast<size_t>(B) * D)
+                  : nullptr;
+  }
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  FwdMaps maps;
+  bool tma = tma_shape_ok(T, D, es) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) && aligned(branch, 16) &&
+             aligned(out, 16);
+  if (tma) {
+    const int rows = scan_fwd_box_rows(0), cols = scan_fwd_box_cols(0);
+    tma = make_map(&maps.x, x, bf16, B, T, D, rows + (conv ? 3 : 0), cols) &&
+          make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) && make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.g, branch, bf16, B, T, D, rows, cols) && make_map(&maps.y, out, bf16, B, T, D, rows, cols);
+  }
+  const cudaError_t e = launch_merge_fwd(bf16, tma, conv, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_merge_bwd(const void* dout, const float* dh_last, const void* x, const float* conv_w, const float* conv_b,
+                    const void* conv_state, const void* u_r, const void* u_i, const void* branch, const float* lambda,
+                    const float* h0, const uint8_t* tok, void* ws, size_t ws_bytes, void* dx, void* du_r, void* du_i,
+                    void* dbranch, float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!dout || !x || !u_r || !u_i || !branch || !lambda || !dx || !du_r || !du_i || !dbranch || !dlambda)
+    return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const bool conv = conv_w != nullptr;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(dout, es) || !aligned(x, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(branch, es) ||
+      !aligned(dx, es) || !aligned(du_r, es) || !aligned(du_i, es) || !aligned(dbranch, es) || !aligned(conv_state, es) ||
+      !aligned(lambda, 4) || !aligned(conv_w, 4) || !aligned(conv_b, 4) || !aligned(h0, 4) || !aligned(dh_last, 4) ||
+      !aligned(dlambda, 4) || !aligned(dh0, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (!ws || ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+  ScanBwdArgs a = {};
+  a.dy = dout; a.x = x; a.ur = u_r; a.ui = u_i; a.dx = dx; a.dur = du_r; a.dui = du_i; a.g = branch; a.dg = dbranch;
+  a.lambda = lambda; a.h0 = h0; a.dh_last = dh_last; a.tok = tok;
+  a.states = static_cast<const float*>(ws);
+  a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
+  a.dlambda = dlambda; a.dh0 = dh0;
+  a.ticket = (B <= FUSED_DLAMBDA_MAX_B) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
+  if (conv) { a.conv_w = conv_w; a.conv_b = conv_b; a.conv_state = conv_state; }
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  BwdMaps maps;
+  bool tma = tma_shape_ok(T, D, es) && aligned(dout, 16) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) &&
+             aligned(branch, 16) && aligned(dx, 16) && aligned(du_r, 16) && aligned(du_i, 16) && aligned(dbranch, 16);
+  if (tma) {
+    const int rows = scan_bwd_box_rows(0), cols = scan_bwd_box_cols(0);
+    tma = make_map(&maps.dy, dout, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.x, x, bf16, B, T, D, rows + (conv ? 3 : 0), cols) &&
+          make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) && make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.g, branch, bf16, B, T, D, rows, cols) && make_map(&maps.dx, dx, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dur, du_r, bf16, B, T, D, rows, cols) && make_map(&maps.dui, du_i, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dg, dbranch, bf16, B, T, D, rows, cols);
+  }
+  const cudaError_t e = launch_merge_bwd(bf16, tma, conv, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
 int rglru_linear_scan_fwd(const float* decay, const float* drive, const float* h0, float* out, int B, int T, int D,
                           void* stream) {
   if (!decay || !drive || !out) return RGLRU_ERR_NULL_POINTER;

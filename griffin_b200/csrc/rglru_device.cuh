@@ -187,6 +187,24 @@ __device__ __forceinline__ void sigmoid_pair2(float2 ur, float2 ui, float2& r, f
   i = mul2(inv, dr);
 }
 
+// GeLU in its tanh form (griffin/griffin.py:464 of the reference): gelu(v) = v * s with
+// s = sigmoid(2 z) = (1 + tanh z) / 2 and z = k0 v (1 + k1 v^2).  Returns s; precision as sigmoid_pair2.
+constexpr float GELU_K0 = 0.7978845608028654f;   // sqrt(2 / pi)
+constexpr float GELU_K1 = 0.044715f;
+template <bool HALF_IO>
+__device__ __forceinline__ float2 gelu_sigmoid2(float2 v) {
+  const float2 z = mul2(mul2(v, f2(GELU_K0)), fma2(mul2(v, v), f2(GELU_K1), f2(1.0f)));
+  if (HALF_IO) return fma2(make_float2(tanh_approx(z.x), tanh_approx(z.y)), f2(0.5f), f2(0.5f));
+  const float2 t = mul2(z, f2(-2.0f * LOG2E));
+  const float2 d = add2(make_float2(ex2_approx(fminf(t.x, 60.0f)), ex2_approx(fminf(t.y, 60.0f))), f2(1.0f));
+  return make_float2(rcp_approx(d.x), rcp_approx(d.y));
+}
+// d gelu / d v = s + v s (1 - s) * 2 z',  2 z' = 2 k0 (1 + 3 k1 v^2)
+__device__ __forceinline__ float2 gelu_slope2(float2 v, float2 s) {
+  const float2 zp = fma2(mul2(v, v), f2(6.0f * GELU_K0 * GELU_K1), f2(2.0f * GELU_K0));
+  return fma2(mul2(mul2(v, s), fma2(s, f2(-1.0f), f2(1.0f))), zp, s);
+}
+
 // E(y) = 1 - exp(-y) for y >= 0 (y = -c r logsigmoid(Lambda)), so that the decay is
 // a = 1 - E and gamma^2 = 1 - a^2 = E (2 - E) without cancellation.
 //   POLY: y is known to lie in [0, -POLY_RANGE]; alternating degree-6 Taylor, truncation < 5e-8 relative.
@@ -254,6 +272,8 @@ struct Pack<float> {
     v[0] = make_float2(r.x, r.y);
     v[1] = make_float2(r.z, r.w);
   }
+  static __device__ __forceinline__ Raw pack2(const float2 (&v)[2]) { return make_float4(v[0].x, v[0].y, v[1].x, v[1].y); }
+  static __device__ __forceinline__ void store_raw(void* p, const Raw& r) { *reinterpret_cast<float4*>(p) = r; }
   static __device__ __forceinline__ void store2(void* p, const float2 (&v)[2]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
   }
@@ -284,6 +304,15 @@ struct Pack<__nv_bfloat16> {
     v[0] = make_float2(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u));
     v[1] = make_float2(__uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
   }
+  static __device__ __forceinline__ Raw pack2(const float2 (&v)[2]) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0].x, v[0].y);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v[1].x, v[1].y);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    return raw;
+  }
+  static __device__ __forceinline__ void store_raw(void* p, const Raw& r) { *reinterpret_cast<uint2*>(p) = r; }
   static __device__ __forceinline__ void store2(void* p, const float2 (&v)[2]) {
     __nv_bfloat162 lo = __floats2bfloat162_rn(v[0].x, v[0].y);
     __nv_bfloat162 hi = __floats2bfloat162_rn(v[1].x, v[1].y);

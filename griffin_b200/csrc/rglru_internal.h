@@ -29,6 +29,7 @@ struct ScanFwdArgs {
   const float* conv_w;
   const float* conv_b;
   const void* conv_state;
+  const void* g;     // merged variant only: pre-activation of the GeLU branch [B, T, D]; y receives h * gelu(g)
   int B, T, D;
   float c;
   int* status;
@@ -54,16 +55,18 @@ struct ScanBwdArgs {
   const float* conv_w;  // conv-folded variant only (see ScanFwdArgs)
   const float* conv_b;
   const void* conv_state;
+  const void* g;        // merged variant only: dy is then the gradient of h * gelu(g), dg receives that of g
+  void* dg;
   int B, T, D;
   float c;
   int* status;
 };
 
 struct FwdMaps {
-  CUtensorMap x, ur, ui, y;
+  CUtensorMap x, ur, ui, y, g;
 };
 struct BwdMaps {
-  CUtensorMap dy, x, ur, ui, dx, dur, dui;
+  CUtensorMap dy, x, ur, ui, dx, dur, dui, g, dg;
 };
 
 struct RawFwdMaps {
@@ -141,6 +144,8 @@ cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps&
                             cudaStream_t s);
 cudaError_t launch_conv_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
 cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
+cudaError_t launch_merge_fwd(bool bf16, bool use_tma, bool conv, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
+cudaError_t launch_merge_bwd(bool bf16, bool use_tma, bool conv, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
 int scan_fwd_variant(int B, int T, int D, bool bf16);
 int scan_bwd_variant(int B, int T, int D, bool bf16);
 int scan_fwd_box_rows(int variant);

@@ -225,13 +225,14 @@ __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, 
   }
 }
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false, bool MERGE = false>
 struct FwdSmem {
   static constexpr int TC = LANES * TS;
   static constexpr int TILE = TC * CH * sizeof(IO);
   static constexpr int HALO = CONV ? 3 * CH * sizeof(IO) : 0;   // three rows in front of the x tile
   static constexpr int TILEX = TILE + HALO;
-  static constexpr int STAGE = TILEX + 2 * TILE;
+  static constexpr int OFF_G = TILEX + 2 * TILE;                // GeLU-branch tile of the merged variant
+  static constexpr int STAGE = TILEX + 2 * TILE + (MERGE ? TILE : 0);
   static constexpr int OFF_AGG = NSTAGE * STAGE;
   static constexpr int OFF_EIN = OFF_AGG + ChainSmem<LANES, CH>::AGG;
   static constexpr int OFF_BAR = OFF_EIN + ChainSmem<LANES, CH>::EIN;   // full[NSTAGE], ready[NSTAGE], dead flag
@@ -240,10 +241,12 @@ struct FwdSmem {
 
 // Threads [0, LANES*NCV) compute; with TMA one extra warp issues every bulk copy so that
 // no compute warp ever waits on the copy engine's instruction latency.
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV>
+// MERGE: the kernel also reads the pre-activation of the block's GeLU branch and writes
+// h_t * gelu(branch_t) (griffin/griffin.py:464, 520 of the reference) instead of h_t.
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
-  using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV>;
+  using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
@@ -286,6 +289,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     // store of the results written into it has drained from shared memory.
     if (tid == NCOMP) {
       prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
+      if (MERGE) prefetch_map(&maps.g);
       auto issue = [&](int k) {
         const int sidx = k % NSTAGE;
         uint8_t* st = smem + sidx * SM::STAGE;
@@ -293,6 +297,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
         tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
         tma_load_3d(st + SM::TILEX, &maps.ur, d0, k * TC, b, &full[sidx]);
         tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
+        if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
       };
       for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
       for (int k = 0; k < nchunks; ++k) {
@@ -336,6 +341,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
       tile_load_plain<IO, CH>(tiles, p.x, b, t0 - (CONV ? 3 : 0), d0, TC + (CONV ? 3 : 0), p.T, p.D);
       tile_load_plain<IO, CH>(tiles + SM::TILEX, p.ur, b, t0, d0, TC, p.T, p.D);
       tile_load_plain<IO, CH>(tiles + SM::TILEX + SM::TILE, p.ui, b, t0, d0, TC, p.T, p.D);
+      if (MERGE) tile_load_plain<IO, CH>(tiles + SM::OFF_G, p.g, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
 
@@ -391,6 +397,12 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
         float2 yv[2];
 #pragma unroll
         for (int cp = 0; cp < 2; ++cp) yv[cp] = fma2(P[st][cp], e[cp], S[st][cp]);
+        if (MERGE) {
+          float2 gv[2];
+          Pack<IO>::unpack2(Pack<IO>::load(tiles + SM::OFF_G + off0 + st * ROWB), gv);
+#pragma unroll
+          for (int cp = 0; cp < 2; ++cp) yv[cp] = mul2(yv[cp], mul2(gv[cp], gelu_sigmoid2<sizeof(IO) == 2>(gv[cp])));
+        }
         Pack<IO>::store2(ty + off0 + st * ROWB, yv);
       }
     }
@@ -426,8 +438,11 @@ struct BwdRegs {
 // Level one of the backward chunk: gate math, coefficients for the second pass, and the
 // lane aggregates.  aggF = (prod a, local state), aggR = (prod a, local reverse carry),
 // where the reverse carry is a_t g_t flowing from step t to step t-1.
-template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV>
-__device__ __forceinline__ void bwd_local(const uint8_t* tdy, const uint8_t* tx, const uint8_t* tr, const uint8_t* ti,
+// MERGE: the incoming gradient is that of h * gelu(branch).  This pass turns it into the gradient of h
+// (kept, rounded to the I/O type, where the incoming gradient was) and leaves d_out * gelu'(branch) in the
+// branch tile; the second pass multiplies that by h_t to get the branch gradient.
+template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV, bool MERGE>
+__device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8_t* tx, const uint8_t* tr, const uint8_t* ti,
                                           int off0, const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
                                           const ConvTaps& ct, const float2 (*hist)[2],
                                           BwdRegs<IO, TS>& R, float2 (&prod)[2], float2 (&sfwd)[2],
@@ -446,6 +461,19 @@ __device__ __forceinline__ void bwd_local(const uint8_t* tdy, const uint8_t* tx,
     Pack<IO>::unpack2(Pack<IO>::load(tr + off), rv);
     Pack<IO>::unpack2(Pack<IO>::load(ti + off), iv);
     R.dy[st] = Pack<IO>::load(tdy + off);
+    if (MERGE) {
+      float2 dm[2], gv[2], q[2];
+      Pack<IO>::unpack2(R.dy[st], dm);
+      Pack<IO>::unpack2(Pack<IO>::load(tg + off), gv);
+#pragma unroll
+      for (int cp = 0; cp < 2; ++cp) {
+        const float2 sg = gelu_sigmoid2<sizeof(IO) == 2>(gv[cp]);
+        q[cp] = mul2(dm[cp], gelu_slope2(gv[cp], sg));
+        dm[cp] = mul2(dm[cp], mul2(gv[cp], sg));
+      }
+      R.dy[st] = Pack<IO>::pack2(dm);
+      Pack<IO>::store2(tg + off, q);
+    }
     const RowMask m = row_mask<MASKED>(fl[st >> 2], st);
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) {
@@ -495,14 +523,15 @@ __device__ __forceinline__ void bwd_local(const uint8_t* tdy, const uint8_t* tx,
   for (int cp = 0; cp < 2; ++cp) { prod[cp] = p[cp]; sfwd[cp] = s[cp]; crev[cp] = c[cp]; }
 }
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false, bool MERGE = false>
 struct BwdSmem {
   static constexpr int TC = LANES * TS;
   static constexpr int TILE = TC * CH * sizeof(IO);
   static constexpr int HALO = CONV ? 3 * CH * sizeof(IO) : 0;   // three rows in front of the x tile
   static constexpr int TILEX = TILE + HALO;
   static constexpr int OFF_X = TILE, OFF_UR = TILE + TILEX, OFF_UI = 2 * TILE + TILEX;   // after the dy tile
-  static constexpr int STAGE = 3 * TILE + TILEX;
+  static constexpr int OFF_G = 3 * TILE + TILEX;                // GeLU-branch tile of the merged variant
+  static constexpr int STAGE = 3 * TILE + TILEX + (MERGE ? TILE : 0);
   static constexpr int OFF_AGGF = NSTAGE * STAGE;
   static constexpr int OFF_AGGR = OFF_AGGF + ChainSmem<LANES, CH>::AGG;
   static constexpr int OFF_EINF = OFF_AGGR + ChainSmem<LANES, CH>::AGG;
@@ -511,10 +540,10 @@ struct BwdSmem {
   static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
     rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
-  using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE, CONV>;
+  using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
@@ -560,6 +589,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
     if (tid == NCOMP) {
       prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
       prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
+      if (MERGE) { prefetch_map(&maps.g); prefetch_map(&maps.dg); }
       auto issue = [&](int q) {  // q-th chunk in processing order == chunk nchunks-1-q in time
         const int k = nchunks - 1 - q;
         const int sidx = q % NSTAGE;
@@ -569,6 +599,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         tma_load_3d(st + SM::OFF_X, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);
         tma_load_3d(st + SM::OFF_UR, &maps.ur, d0, k * TC, b, &full[sidx]);
         tma_load_3d(st + SM::OFF_UI, &maps.ui, d0, k * TC, b, &full[sidx]);
+        if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
       };
       for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
       for (int q = 0; q < nchunks; ++q) {
@@ -579,6 +610,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
         tma_store_3d(&maps.dur, st + SM::OFF_UR, d0, k * TC, b);
         tma_store_3d(&maps.dui, st + SM::OFF_UI, d0, k * TC, b);
+        if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
         tma_commit();
         if (q + NSTAGE < nchunks) {
           tma_wait_read<0>();
@@ -627,13 +659,15 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
       tile_load_plain<IO, CH>(tiles + SM::OFF_X, p.x, b, t0 - (CONV ? 3 : 0), d0, TC + (CONV ? 3 : 0), p.T, p.D);
       tile_load_plain<IO, CH>(tiles + SM::OFF_UR, p.ur, b, t0, d0, TC, p.T, p.D);
       tile_load_plain<IO, CH>(tiles + SM::OFF_UI, p.ui, b, t0, d0, TC, p.T, p.D);
+      if (MERGE) tile_load_plain<IO, CH>(tiles + SM::OFF_G, p.g, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
 
     BwdRegs<IO, TS> R;
     float2 prod[2], sfwd[2], crev[2];
     {
-      const uint8_t* tdy = tiles;
+      uint8_t* tdy = tiles;
+      uint8_t* tg = tiles + SM::OFF_G;
       const uint8_t* tx = tiles + SM::OFF_X;
       const uint8_t* tr = tiles + SM::OFF_UR;
       const uint8_t* ti = tiles + SM::OFF_UI;
@@ -644,11 +678,11 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         hist = hist_v;
       }
       if (masked) {
-        if (poly) bwd_local<IO, TS, CH, true, true, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
-        else bwd_local<IO, TS, CH, true, false, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        if (poly) bwd_local<IO, TS, CH, true, true, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, true, false, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
       } else {
-        if (poly) bwd_local<IO, TS, CH, false, true, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
-        else bwd_local<IO, TS, CH, false, false, CONV>(tdy, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        if (poly) bwd_local<IO, TS, CH, false, true, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, false, false, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
       }
     }
     {
@@ -699,6 +733,14 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
           h[cp] = fma2(R.am[st][cp], hin, R.hb[st][cp]);
           R.hb[st][cp] = hin;
         }
+        if (MERGE) {   // d branch_t = d_out_t * gelu'(branch_t) * h_t, the first two factors left by the first pass
+          uint8_t* tq = tiles + SM::OFF_G + off0 + st * ROWB;
+          float2 q[2];
+          Pack<IO>::unpack2(Pack<IO>::load(tq), q);
+          q[0] = mul2(q[0], h[0]);
+          q[1] = mul2(q[1], h[1]);
+          Pack<IO>::store2(tq, q);
+        }
       }
       uint8_t* tdx = tiles + SM::OFF_X + SM::HALO;   // over x (past its halo rows)
       uint8_t* tdr = tiles + SM::OFF_UR;             // over u_r
@@ -735,6 +777,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
       tile_store_plain<IO, CH>(tiles + SM::OFF_X + SM::HALO, p.dx, b, t0, d0, TC, p.T, p.D);
       tile_store_plain<IO, CH>(tiles + SM::OFF_UR, p.dur, b, t0, d0, TC, p.T, p.D);
       tile_store_plain<IO, CH>(tiles + SM::OFF_UI, p.dui, b, t0, d0, TC, p.T, p.D);
+      if (MERGE) tile_store_plain<IO, CH>(tiles + SM::OFF_G, p.dg, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
   }
@@ -1142,11 +1185,12 @@ static cudaError_t set_smem(Kern kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV>;
-  constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV>::BYTES;
+  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE>;
+  constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
+  static_assert(bytes <= 232448, "shared memory of one CTA");
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
@@ -1170,11 +1214,12 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
   return bf16 ? launch_fwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_fwd_io<float>(use_tma, variant, maps, a, s);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV>;
-  constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV>::BYTES;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE>;
+  constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
+  static_assert(bytes <= 232448, "shared memory of one CTA");
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
@@ -1215,6 +1260,31 @@ cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, c
                    : launch_bwd_t<__nv_bfloat16, Shape64x16x4, 1, false, true>(maps, a, s);
   return use_tma ? launch_bwd_t<float, Shape64x16x4, 3, true, true>(maps, a, s)
                  : launch_bwd_t<float, Shape64x16x4, 1, false, true>(maps, a, s);
+}
+
+// Branch merge folded into the store stage (forward) and the load stage (backward), with or without the
+// conv fold: one shape (64 channels x 64 steps).  One more tile per stage, so fp32 backward keeps two stages.
+template <typename IO, bool CONV>
+static cudaError_t launch_merge_fwd_t(bool use_tma, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
+  constexpr bool H = sizeof(IO) == 2;
+  return use_tma ? launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, CONV, true>(maps, a, s)
+                 : launch_fwd_t<IO, Shape64x16x4, 1, false, CONV, true>(maps, a, s);
+}
+template <typename IO, bool CONV>
+static cudaError_t launch_merge_bwd_t(bool use_tma, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
+  constexpr bool H = sizeof(IO) == 2;
+  return use_tma ? launch_bwd_t<IO, Shape64x16x4, H ? 4 : 2, true, CONV, true>(maps, a, s)
+                 : launch_bwd_t<IO, Shape64x16x4, 1, false, CONV, true>(maps, a, s);
+}
+cudaError_t launch_merge_fwd(bool bf16, bool use_tma, bool conv, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
+  if (bf16) return conv ? launch_merge_fwd_t<__nv_bfloat16, true>(use_tma, maps, a, s)
+                        : launch_merge_fwd_t<__nv_bfloat16, false>(use_tma, maps, a, s);
+  return conv ? launch_merge_fwd_t<float, true>(use_tma, maps, a, s) : launch_merge_fwd_t<float, false>(use_tma, maps, a, s);
+}
+cudaError_t launch_merge_bwd(bool bf16, bool use_tma, bool conv, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
+  if (bf16) return conv ? launch_merge_bwd_t<__nv_bfloat16, true>(use_tma, maps, a, s)
+                        : launch_merge_bwd_t<__nv_bfloat16, false>(use_tma, maps, a, s);
+  return conv ? launch_merge_bwd_t<float, true>(use_tma, maps, a, s) : launch_merge_bwd_t<float, false>(use_tma, maps, a, s);
 }
 
 int raw_box_rows() { return RAW_TC; }

@@ -123,7 +123,8 @@ class RG_LRU(nn.Module):
             self.Lambda.copy_(torch.logit(target.pow(1.0 / self.c)))
 
     def forward(self, xt: Tensor, ht_minus_1: Optional[Tensor] = None, *, reset_mask: Optional[Tensor] = None,
-                active_mask: Optional[Tensor] = None, return_state: bool = False, _flags: Optional[Tensor] = None):
+                active_mask: Optional[Tensor] = None, return_state: bool = False, _flags: Optional[Tensor] = None,
+                _branch: Optional[Tensor] = None):
         if xt.dim() != 3:
             raise ValueError(f"RG_LRU expects [batch, sequence, width], got {tuple(xt.shape)}")
         batch, steps, width = xt.shape
@@ -149,7 +150,10 @@ class RG_LRU(nn.Module):
         u_r = self.recurrence_gate(xt).to(xt.dtype)
         u_i = self.input_gate(xt).to(xt.dtype)
         flags = _flags if _flags is not None else token_flags(batch, steps, xt.device, reset=reset_mask, active=active_mask)
-        yt, h_last = ops.rglru(xt, u_r, u_i, self.Lambda, ht_minus_1, flags, self.c)
+        if _branch is not None:   # the caller's GeLU branch, multiplied in by the kernels
+            yt, h_last = ops.rglru_merged(xt, u_r, u_i, _branch, self.Lambda, ht_minus_1, flags, self.c)
+        else:
+            yt, h_last = ops.rglru(xt, u_r, u_i, self.Lambda, ht_minus_1, flags, self.c)
         if return_state:
             return yt, h_last
         return yt
@@ -202,8 +206,12 @@ class RecurrentBlock(nn.Module):
     """
 
     def __init__(self, input_dim: int, rnn_width: int, conv_kernel_size: int = 4, gate_blocks: int = 16,
-                 final_w_init_variance_scale: float = 1.0, scan_mode: str = "cuda", *, fold_conv: bool = False):
+                 final_w_init_variance_scale: float = 1.0, scan_mode: str = "cuda", *, fold_conv: bool = False,
+                 fold_merge: bool = False):
         super().__init__()
+        # fold_merge (not in the reference): the product with the GeLU branch is formed in the scan kernels' store
+        # stage and differentiated in the backward kernel's load stage; combines with fold_conv.
+        self.fold_merge = fold_merge
         # fold_conv (not in the reference): run conv, gates and scan as one autograd node whose scan kernels
         # apply the conv while loading, so the conv output is not kept for backward (recomputed there instead).
         self.fold_conv = fold_conv
@@ -243,7 +251,9 @@ class RecurrentBlock(nn.Module):
         plain = segment_pos is None and cache is None and active_mask is None
         pos = _positions(x, segment_pos, previous, active_mask)
 
-        y_branch = F.gelu(self.linear_y(x), approximate="tanh")
+        y_branch = self.linear_y(x)
+        if not self.fold_merge:
+            y_branch = F.gelu(y_branch, approximate="tanh")
         x_in = self.linear_x(x)
         restore = None
         if active_mask is not None and steps > 1 and bool((active_mask[:, 1:] & ~active_mask[:, :-1]).any()):
@@ -251,6 +261,8 @@ class RecurrentBlock(nn.Module):
             order = torch.argsort((~active_mask).to(torch.uint8), dim=1, stable=True)
             restore = torch.argsort(order, dim=1)
             x_in = x_in.gather(1, order[..., None].expand(-1, -1, x_in.size(-1)))
+            if self.fold_merge:   # the kernels multiply by the branch, so it travels with its tokens
+                y_branch = y_branch.gather(1, order[..., None].expand(-1, -1, y_branch.size(-1)))
             kernel_pos, kernel_active = pos.gather(1, order), active_mask.gather(1, order)
         else:
             kernel_pos, kernel_active = pos, active_mask
@@ -279,13 +291,15 @@ class RecurrentBlock(nn.Module):
             lru = self.rg_lru
             y, new_rnn, new_conv = ops.recurrent_core(
                 x_in, conv_w, self.temporal_conv.bias, conv_state, lru.recurrence_gate.weight, lru.recurrence_gate.bias,
-                lru.input_gate.weight, lru.input_gate.bias, lru.Lambda, rnn_state, flags, lru.c)
+                lru.input_gate.weight, lru.input_gate.bias, lru.Lambda, rnn_state, flags, lru.c,
+                y_branch if self.fold_merge else None)
         else:
             x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags)
-            y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags)
+            y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags,
+                                     _branch=y_branch if self.fold_merge else None)
         if restore is not None:
             y = y.gather(1, restore[..., None].expand(-1, -1, y.size(-1)))
-        out = self.linear_out(y * y_branch)
+        out = self.linear_out(y if self.fold_merge else y * y_branch)
         if active_mask is not None:
             out = torch.where(active_mask[..., None], out, torch.zeros_like(out))
         if return_cache:

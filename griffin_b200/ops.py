@@ -329,6 +329,88 @@ def conv_scan_bwd(dy: Tensor, dh_last: Optional[Tensor], x_in: Tensor, conv_w: T
     return dxc, du_r, du_i, dlam, dh0
 
 
+# ----------------------------------------------------------------------------- GeLU branch merged into the scan
+def merge_scan_fwd(x: Tensor, conv_w: Optional[Tensor], conv_b: Optional[Tensor], conv_state: Optional[Tensor],
+                   u_r: Tensor, u_i: Tensor, branch: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
+                   c: float, save: bool) -> tuple[Tensor, Tensor, Tensor]:
+    """out, h_last, workspace with out = RG-LRU(...) * gelu_tanh(branch) formed in the scan's store stage
+    (``rglru_merge_fwd``).  With ``conv_w`` given, ``x`` is the conv input and the conv is applied while loading."""
+    lib = _lib.load()
+    _require_cuda(x, conv_w, conv_b, conv_state, u_r, u_i, branch, lam, h0, tok)
+    dt = _io_dtype(x, "merged scan forward")
+    B, T, D = x.shape
+    out = torch.empty_like(x)
+    h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
+    nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
+    ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
+    with torch.cuda.device(x.device):
+        rc = lib.rglru_merge_fwd(_ptr(x), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state), _ptr(u_r), _ptr(u_i),
+                                 _ptr(branch), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(out), _ptr(h_last),
+                                 _ptr(ws) if save else None, nbytes, B, T, D, c, dt, _stream(x))
+    _lib.check(rc, "rglru_merge_fwd")
+    return out, h_last, ws
+
+
+def merge_scan_bwd(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, conv_w: Optional[Tensor],
+                   conv_b: Optional[Tensor], conv_state: Optional[Tensor], u_r: Tensor, u_i: Tensor, branch: Tensor,
+                   lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor], ws: Tensor, c: float, want_dh0: bool
+                   ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Optional[Tensor]]:
+    """Backward of :func:`merge_scan_fwd`: (d x direct path, d u_r, d u_i, d branch, d Lambda, d h0)."""
+    lib = _lib.load()
+    dt = _io_dtype(x, "merged scan backward")
+    B, T, D = x.shape
+    dx, du_r, du_i, dbranch = (torch.empty_like(x) for _ in range(4))
+    dlam = torch.empty(D, device=x.device, dtype=torch.float32)
+    dh0 = torch.empty(B, D, device=x.device, dtype=torch.float32) if want_dh0 else None
+    with torch.cuda.device(x.device):
+        rc = lib.rglru_merge_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state),
+                                 _ptr(u_r), _ptr(u_i), _ptr(branch), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(ws),
+                                 ws.numel(), _ptr(dx), _ptr(du_r), _ptr(du_i), _ptr(dbranch), _ptr(dlam), _ptr(dh0),
+                                 B, T, D, c, dt, _stream(x))
+    _lib.check(rc, "rglru_merge_bwd")
+    return dx, du_r, du_i, dbranch, dlam, dh0
+
+
+class _MergedScan(torch.autograd.Function):
+    """RG-LRU whose output is multiplied by gelu_tanh(branch) inside the scan kernels (no conv fold)."""
+
+    @staticmethod
+    def forward(ctx, x, u_r, u_i, branch, lam, h0, tok, c):
+        lam32 = lam.to(torch.float32).contiguous()
+        h032 = None if h0 is None else h0.to(torch.float32).contiguous()
+        x, u_r, u_i, branch = x.contiguous(), u_r.contiguous(), u_i.contiguous(), branch.to(x.dtype).contiguous()
+        save = any(ctx.needs_input_grad)
+        out, h_last, ws = merge_scan_fwd(x, None, None, None, u_r, u_i, branch, lam32, h032, tok, float(c), save)
+        ctx.save_for_backward(x, u_r, u_i, branch, lam32, h032, tok, ws)
+        ctx.c, ctx.lam_dtype = float(c), lam.dtype
+        return out, h_last
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dout, dh_last):
+        x, u_r, u_i, branch, lam32, h032, tok, ws = ctx.saved_tensors
+        if ws.numel() == 0:
+            raise RuntimeError("merged scan was run without saving its workspace; backward is unavailable")
+        dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
+        want_dh0 = h032 is not None and ctx.needs_input_grad[5]
+        dx, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dout.contiguous(), dh_last, x, None, None, None, u_r, u_i,
+                                                            branch, lam32, h032, tok, ws, ctx.c, want_dh0)
+        return dx, du_r, du_i, dbranch, dlam.to(ctx.lam_dtype), dh0, None, None
+
+
+def rglru_merged(x: Tensor, u_r: Tensor, u_i: Tensor, branch: Tensor, lam: Tensor, h0: Optional[Tensor] = None,
+                 tok: Optional[Tensor] = None, c: float = 8.0) -> tuple[Tensor, Tensor]:
+    """(RG-LRU(x | u_r, u_i) * gelu(branch, approximate="tanh"), h_last): the recurrent block's branch merge
+    (griffin/griffin.py:464, 520 of the reference) formed and differentiated inside the scan kernels."""
+    if x.dim() != 3 or u_r.shape != x.shape or u_i.shape != x.shape or branch.shape != x.shape:
+        raise ValueError("x, u_r, u_i and branch must share shape [batch, sequence, width]")
+    if u_r.dtype != x.dtype or u_i.dtype != x.dtype:
+        raise TypeError("x, u_r and u_i must share one dtype")
+    if lam.shape != (x.shape[2],):
+        raise ValueError("Lambda must have shape [width]")
+    return _MergedScan.apply(x, u_r, u_i, branch, lam, h0, None if tok is None else tok.contiguous(), c)
+
+
 def _gate(x: Tensor, weight: Tensor, bias: Tensor) -> Tensor:
     """Block-diagonal projection [.., G*in] -> [.., G*out] in x's dtype (weight [G, out, in])."""
     g, wo, wi = weight.shape
@@ -357,7 +439,7 @@ class _RecurrentCore(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, tok, c):
+    def forward(ctx, x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch):
         x_in = x_in.contiguous()
         cw = conv_w.to(torch.float32).contiguous()
         cb = None if conv_b is None else conv_b.to(torch.float32).contiguous()
@@ -369,8 +451,12 @@ class _RecurrentCore(torch.autograd.Function):
         u_i = _gate(x_conv, w_i, b_i)
         del x_conv
         save = any(ctx.needs_input_grad)
-        y, h_last, ws = conv_scan_fwd(x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, float(c), save)
-        ctx.save_for_backward(x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws)
+        if branch is None:
+            y, h_last, ws = conv_scan_fwd(x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, float(c), save)
+        else:
+            branch = branch.to(x_in.dtype).contiguous()
+            y, h_last, ws = merge_scan_fwd(x_in, cw, cb, cs, u_r, u_i, branch, lam32, h032, tok, float(c), save)
+        ctx.save_for_backward(x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws, branch)
         ctx.c = float(c)
         ctx.meta = (conv_w.dtype, None if conv_b is None else conv_b.dtype, b_r.dtype, b_i.dtype, lam.dtype)
         ctx.mark_non_differentiable(new_state)
@@ -379,14 +465,19 @@ class _RecurrentCore(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dh_last, _d_state):
-        x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws = ctx.saved_tensors
+        x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws, branch = ctx.saved_tensors
         if ws.numel() == 0:
             raise RuntimeError("recurrent core was run without saving its workspace; backward is unavailable")
         dy = dy.contiguous()
         dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
         want_dh0 = h032 is not None and ctx.needs_input_grad[9]
-        dxc, du_r, du_i, dlam, dh0 = conv_scan_bwd(dy, dh_last, x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, ws,
-                                                   ctx.c, want_dh0)
+        dbranch = None
+        if branch is None:
+            dxc, du_r, du_i, dlam, dh0 = conv_scan_bwd(dy, dh_last, x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, ws,
+                                                       ctx.c, want_dh0)
+        else:
+            dxc, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dy, dh_last, x_in, cw, cb, cs, u_r, u_i, branch, lam32,
+                                                                 h032, tok, ws, ctx.c, want_dh0)
         x_conv, _ = _conv_fwd(x_in, cw, cb, cs, tok)          # recomputed, not saved
         dx_r, dw_r, db_r = _gate_backward(du_r, x_conv, w_r)
         dx_i, dw_i, db_i = _gate_backward(du_i, x_conv, w_i)
@@ -395,17 +486,23 @@ class _RecurrentCore(torch.autograd.Function):
         dx_in, d_w, d_b, d_state = _conv_bwd(total, x_in, cw, cs, tok, want_state)
         wdt, bdt, brdt, bidt, ldt = ctx.meta
         return (dx_in, d_w.to(wdt), None if cb is None else d_b.to(bdt), d_state if want_state else None,
-                dw_r, db_r.to(brdt), dw_i, db_i.to(bidt), dlam.to(ldt), dh0, None, None)
+                dw_r, db_r.to(brdt), dw_i, db_i.to(bidt), dlam.to(ldt), dh0, None, None, dbranch)
 
 
 def recurrent_core(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_state: Optional[Tensor],
                    w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor, h0: Optional[Tensor] = None,
-                   tok: Optional[Tensor] = None, c: float = 8.0) -> tuple[Tensor, Tensor, Tensor]:
-    """(y, h_last, new_conv_state) of conv k=4 -> block-diagonal gates -> RG-LRU, keeping only ``x_in`` for backward."""
+                   tok: Optional[Tensor] = None, c: float = 8.0, branch: Optional[Tensor] = None
+                   ) -> tuple[Tensor, Tensor, Tensor]:
+    """(y, h_last, new_conv_state) of conv k=4 -> block-diagonal gates -> RG-LRU, keeping only ``x_in`` for backward.
+
+    With ``branch`` (the pre-activation of the block's GeLU branch, same shape as ``x_in``) the first result is
+    ``y * gelu(branch, approximate="tanh")``, formed inside the scan kernels in both directions."""
+    if branch is not None and branch.shape != x_in.shape:
+        raise ValueError("branch must have the shape of x_in")
     if x_in.dim() != 3 or conv_w.shape != (x_in.shape[2], 4):
         raise ValueError("x_in must be [batch, sequence, width] and conv_w [width, 4]")
     return _RecurrentCore.apply(x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0,
-                                None if tok is None else tok.contiguous(), c)
+                                None if tok is None else tok.contiguous(), c, branch)
 
 
 # ----------------------------------------------------------------------------- decode (in-place state, no autograd)

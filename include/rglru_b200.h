@@ -119,6 +119,23 @@ int rglru_conv_scan_bwd(const void* dy, const float* dh_last, const void* x_in, 
                         const uint8_t* tok, void* ws, size_t ws_bytes, void* dx_conv, void* du_r, void* du_i,
                         float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype, void* stream);
 
+/* Branch merge folded into the scan.  The recurrent block multiplies the RG-LRU output by the GeLU branch
+ * before its output projection: linear_out(x_branch * gelu(linear_y(x), approximate="tanh")),
+ * griffin/griffin.py:464 and :520.  rglru_merge_fwd is rglru_fwd (conv_w == NULL) or rglru_conv_scan_fwd
+ * (conv_w != NULL; x is then the conv INPUT) whose store stage writes out = h * gelu(branch) instead of h;
+ * rglru_merge_bwd takes dout = the gradient of that product, forms the gradient of h while loading, and also
+ * writes dbranch = dout * h * gelu'(branch).  h_last, ws, dx, du_r, du_i, dlambda, dh0 as in the unmerged calls.
+ *   branch  : [B,T,D] io_dtype, the PRE-activation linear_y(x)        dbranch : [B,T,D] io_dtype out
+ * With bf16 I/O the gradient of h is rounded to bf16 once inside the kernel, as the unfused sequence would. */
+int rglru_merge_fwd(const void* x, const float* conv_w, const float* conv_b, const void* conv_state, const void* u_r,
+                    const void* u_i, const void* branch, const float* lambda, const float* h0, const uint8_t* tok,
+                    void* out, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c, int io_dtype,
+                    void* stream);
+int rglru_merge_bwd(const void* dout, const float* dh_last, const void* x, const float* conv_w, const float* conv_b,
+                    const void* conv_state, const void* u_r, const void* u_i, const void* branch, const float* lambda,
+                    const float* h0, const uint8_t* tok, void* ws, size_t ws_bytes, void* dx, void* du_r, void* du_i,
+                    void* dbranch, float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype, void* stream);
+
 /* Raw affine scan h_t = a_t h_{t-1} + b_t on fp32 tensors: the operator
  * fused_rglru_scan(decay, current_input, initial_state) of griffin/triton_scan.py:274-276
  * (forward kernel :31-60).  decay, drive, out: [B,T,D] fp32; h0: [B,D] fp32 or NULL. */

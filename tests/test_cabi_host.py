@@ -81,6 +81,12 @@ def test_argument_validation_codes(lib):
     assert lib.rglru_bwd(p, None, p, p, p, p, None, None, None, 0, p, p, p, p, None, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
     assert lib.rglru_conv_bwd(p, p, p, None, None, p, p, None, None, None, 0, 1, 2, 4, _lib.F32, None) == _lib.ERR_WORKSPACE
     assert lib.rglru_linear_scan_fwd(None, p, None, p, 1, 2, 4, None) == _lib.ERR_NULL_POINTER
+    # branch merge: x, conv_w, conv_b, conv_state, u_r, u_i, branch, lambda, h0, tok, out, h_last, ws, ws_bytes, ...
+    assert lib.rglru_merge_fwd(p, None, None, None, p, p, None, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_merge_fwd(p, None, None, None, p, p, p, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, 3, None) == _lib.ERR_BAD_DTYPE
+    assert lib.rglru_merge_fwd(p, None, None, None, p, p, p + 2, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_MISALIGNED
+    assert lib.rglru_merge_bwd(p, None, p, None, None, None, p, p, p, p, None, None, p, 4, p, p, p, p, p, None, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
+    assert lib.rglru_merge_bwd(p, None, p, None, None, None, p, p, p, p, None, None, p, 1 << 20, p, p, p, None, p, None, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_conv_fwd(p, None, None, None, None, p, None, 1, 2, 4, _lib.F32, None) == _lib.ERR_NULL_POINTER
 
 

@@ -252,6 +252,98 @@ def test_conv_scan_kernels_against_oracle(shape, dtype):
         assert err <= tol, (key, err)
 
 
+@pytest.mark.parametrize("conv", [False, True])
+@pytest.mark.parametrize("shape", [(2, 150, 128), (3, 67, 64), (2, 70, 72), (1, 9, 20)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_merged_scan_kernels_against_oracle(shape, dtype, conv):
+    """rglru_merge_fwd / _bwd through the C ABI: out = RG-LRU(...) * gelu_tanh(branch) formed in the store stage
+    and differentiated in the backward load stage (griffin/griffin.py:464, 520), with and without the conv fold."""
+    from griffin_b200 import ops
+    from griffin_b200.modules import token_flags
+    B, T, D = shape
+    gen = torch.Generator().manual_seed(11 * T + D + int(conv))
+    x_in = torch.randn(B, T, D, generator=gen).to(dtype)
+    u_r = torch.randn(B, T, D, generator=gen).to(dtype)
+    u_i = torch.randn(B, T, D, generator=gen).to(dtype)
+    branch = (torch.randn(B, T, D, generator=gen) * 1.5).to(dtype)
+    dout = torch.randn(B, T, D, generator=gen).to(dtype)
+    w = torch.randn(D, 4, generator=gen) * 0.5
+    bias = torch.randn(D, generator=gen) * 0.1
+    state = torch.randn(B, 3, D, generator=gen).to(dtype)
+    lam = orc.init_lambda(D, 8.0, gen)
+    h0 = torch.randn(B, D, generator=gen)
+    dh = torch.randn(B, D, generator=gen)
+    seg = torch.arange(T)[None, :].repeat(B, 1) + 2
+    if T > 8:
+        seg[:, T // 2:] = torch.arange(T - T // 2)
+    reset = seg == 0
+    bd = branch.double().requires_grad_(True)
+    gelu = torch.nn.functional.gelu(bd, approximate="tanh")
+    (slope,) = torch.autograd.grad(gelu.sum(), bd)
+    gelu = gelu.detach()
+    x_ref = orc.causal_conv_dense(x_in.double(), w.double(), bias.double(), state.double(), seg)[0] if conv else x_in.double()
+    want = orc.rglru_backward_linear(x_ref, u_r.double(), u_i.double(), lam.double(), dout.double() * gelu, h0=h0,
+                                     dh_last=dh, reset=reset)
+    want["out"] = want["y"] * gelu
+    want["dbranch"] = dout.double() * want["y"] * slope
+    flags = token_flags(B, T, DEV, reset=reset.to(DEV), segment_pos=seg.to(DEV))
+    dev = lambda t: t.to(DEV).contiguous()
+    conv_args = [dev(w), dev(bias), dev(state)] if conv else [None, None, None]
+    args = [dev(x_in), *conv_args, dev(u_r), dev(u_i), dev(branch), dev(lam), dev(h0)]
+    out, h_last, ws = ops.merge_scan_fwd(*args, flags, 8.0, True)
+    dx, du_r, du_i, dbranch, dlam, dh0 = ops.merge_scan_bwd(dev(dout), dev(dh), *args, flags, ws, 8.0, True)
+    tol = FP32_REL if dtype == torch.float32 else BF16_REL
+    got = {"out": out, "h_last": h_last, "dx": dx, "du_r": du_r, "du_i": du_i, "dbranch": dbranch, "dLambda": dlam,
+           "dh0": dh0}
+    for key, val in got.items():
+        err = orc.rel_l2(val, want[key])
+        assert err <= tol, (key, err)
+    from griffin_b200 import _lib
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("fold_conv", [False, True])
+def test_merge_folded_block_matches_reference_gradients_and_cache(fold_conv):
+    """RecurrentBlock(fold_merge=True): same outputs, gradients and caches as the reference's stored results."""
+    from griffin_b200 import RecurrentBlock as _Block
+    RecurrentBlock = lambda *a, **k: _Block(*a, fold_conv=fold_conv, **k)
+    case = load_golden("block_grads")
+    blk = RecurrentBlock(16, 32, gate_blocks=4, scan_mode="cuda", fold_merge=True)
+    blk.load_state_dict(params_of(case))
+    blk = blk.to(DEV)
+    x = case["x"].to(DEV).requires_grad_(True)
+    out = blk(x)
+    (out * case["dout"].to(DEV)).sum().backward()
+    assert orc.rel_l2(out, case["out"]) <= FP32_REL
+    assert orc.rel_l2(x.grad, case["dx"]) <= FP32_REL
+    for key, p in blk.named_parameters():
+        assert orc.rel_l2(p.grad, case["g." + key]) <= FP32_REL, key
+
+    case = load_golden("block_chunked")
+    blk = RecurrentBlock(8, 12, scan_mode="cuda", fold_merge=True)
+    blk.load_state_dict(params_of(case))
+    blk = blk.to(DEV).eval()
+    x = case["x"].to(DEV)
+    with torch.no_grad():
+        a, c1 = blk(x[:, :3], return_cache=True)
+        b, c2 = blk(x[:, 3:7], c1, return_cache=True)
+        c, c3 = blk(x[:, 7:], c2, return_cache=True)
+    torch.testing.assert_close(torch.cat([a, b, c], 1).cpu(), case["chunks"], atol=2e-6, rtol=2e-5)
+    torch.testing.assert_close(c3.rnn_state.cpu(), case["c3.rnn"], atol=2e-6, rtol=2e-5)
+
+    case = load_golden("block_ragged")
+    blk = RecurrentBlock(8, 16, gate_blocks=4, scan_mode="cuda", fold_merge=True)
+    blk.load_state_dict(params_of(case))
+    blk = blk.to(DEV)
+    x = case["x"].to(DEV).requires_grad_(True)
+    first, c1 = blk(x, active_mask=case["active"].to(DEV), return_cache=True)
+    (first * case["dout"].to(DEV)).sum().backward()
+    torch.testing.assert_close(first.detach().cpu(), case["first"], atol=2e-6, rtol=2e-5)
+    assert orc.rel_l2(x.grad.cpu(), case["dx"]) <= FP32_REL
+    for key, p in blk.named_parameters():
+        assert orc.rel_l2(p.grad.cpu(), case["g." + key]) <= FP32_REL, key
+
+
 def test_folded_block_matches_reference_gradients_and_cache():
     """RecurrentBlock(fold_conv=True): same outputs, gradients and caches as the reference's stored results."""
     from griffin_b200 import RecurrentBlock
