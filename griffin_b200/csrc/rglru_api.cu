@@ -419,6 +419,104 @@ int rglru_merge_bwd(const void* dout, const float* dh_last, const void* x, const
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
 
+// Grouped gate layout: TMA staging only, so everything the copy engine touches must be 16-byte aligned and a
+// channel tile must not straddle a gate head.
+static int check_grouped(int D, int gate_width, size_t es) {
+  if (gate_width <= 0 || D % gate_width != 0 || gate_width % grouped_box_cols() != 0) return RGLRU_ERR_BAD_SHAPE;
+  if ((static_cast<size_t>(D) * es) % 16 != 0) return RGLRU_ERR_BAD_SHAPE;
+  return RGLRU_OK;
+}
+
+int rglru_grouped_fwd(const void* x, const void* u, const float* gate_bias, const void* branch, const float* lambda,
+                      const float* h0, const uint8_t* tok, void* out, float* h_last, void* ws, size_t ws_bytes, int B,
+                      int T, int D, int gate_width, float c, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!x || !u || !lambda || !out) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const bool merge = branch != nullptr;
+  const size_t es = bf16 ? 2 : 4;
+  rc = check_grouped(D, gate_width, es);
+  if (rc != RGLRU_OK) return rc;
+  if (!aligned(x, 16) || !aligned(u, 16) || !aligned(branch, 16) || !aligned(out, 16) || !aligned(gate_bias, 16) ||
+      !aligned(lambda, 4) || !aligned(h0, 4) || !aligned(h_last, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (ws && ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  ScanFwdArgs a = {};
+  a.x = x; a.ur = u; a.ui = u; a.y = out; a.g = branch; a.gate_bias = gate_bias; a.gate_bw = gate_width;
+  a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
+  a.states = static_cast<float*>(ws);
+  {
+    const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+    a.ticket = ws ? reinterpret_cast<unsigned*>(static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D +
+                                               static_cast<size_t>(B) * D)
+                  : nullptr;
+  }
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  FwdMaps maps;
+  const int rows = scan_fwd_box_rows(0), cols = grouped_box_cols();
+  bool ok = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u, bf16, B, T, 2 * D, rows, cols) &&
+            make_map(&maps.y, out, bf16, B, T, D, rows, cols);
+  if (ok && merge) ok = make_map(&maps.g, branch, bf16, B, T, D, rows, cols);
+  if (!ok) return RGLRU_ERR_UNSUPPORTED;
+  maps.ui = maps.ur;
+  const cudaError_t e = launch_grouped_fwd(bf16, merge, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_grouped_bwd(const void* dout, const float* dh_last, const void* x, const void* u, const float* gate_bias,
+                      const void* branch, const float* lambda, const float* h0, const uint8_t* tok, void* ws,
+                      size_t ws_bytes, void* dx, void* du, void* dbranch, float* dlambda, float* dh0, int B, int T, int D,
+                      int gate_width, float c, int io_dtype, void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!dout || !x || !u || !lambda || !dx || !du || !dlambda || (branch && !dbranch)) return RGLRU_ERR_NULL_POINTER;
+  int rc = check_dims(B, T, D);
+  if (rc != RGLRU_OK) return rc;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const bool merge = branch != nullptr;
+  const size_t es = bf16 ? 2 : 4;
+  rc = check_grouped(D, gate_width, es);
+  if (rc != RGLRU_OK) return rc;
+  if (!aligned(dout, 16) || !aligned(x, 16) || !aligned(u, 16) || !aligned(branch, 16) || !aligned(dx, 16) ||
+      !aligned(du, 16) || !aligned(dbranch, 16) || !aligned(gate_bias, 16) || !aligned(lambda, 4) || !aligned(h0, 4) ||
+      !aligned(dh_last, 4) || !aligned(dlambda, 4) || !aligned(dh0, 4) || !aligned(ws, 4))
+    return RGLRU_ERR_MISALIGNED;
+  if (!ws || ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+
+  const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
+  ScanBwdArgs a = {};
+  a.dy = dout; a.x = x; a.ur = u; a.ui = u; a.dx = dx; a.dur = du; a.dui = du; a.g = branch; a.dg = dbranch;
+  a.gate_bias = gate_bias; a.gate_bw = gate_width;
+  a.lambda = lambda; a.h0 = h0; a.dh_last = dh_last; a.tok = tok;
+  a.states = static_cast<const float*>(ws);
+  a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
+  a.dlambda = dlambda; a.dh0 = dh0;
+  a.ticket = (B <= FUSED_DLAMBDA_MAX_B) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
+  a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
+
+  BwdMaps maps;
+  const int rows = scan_bwd_box_rows(0), cols = grouped_box_cols();
+  bool ok = make_map(&maps.dy, dout, bf16, B, T, D, rows, cols) && make_map(&maps.x, x, bf16, B, T, D, rows, cols) &&
+            make_map(&maps.ur, u, bf16, B, T, 2 * D, rows, cols) && make_map(&maps.dx, dx, bf16, B, T, D, rows, cols) &&
+            make_map(&maps.dur, du, bf16, B, T, 2 * D, rows, cols);
+  if (ok && merge)
+    ok = make_map(&maps.g, branch, bf16, B, T, D, rows, cols) && make_map(&maps.dg, dbranch, bf16, B, T, D, rows, cols);
+  if (!ok) return RGLRU_ERR_UNSUPPORTED;
+  maps.ui = maps.ur;
+  maps.dui = maps.dur;
+  const cudaError_t e = launch_grouped_bwd(bf16, merge, maps, a, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
 int rglru_linear_scan_fwd(const float* decay, const float* drive, const float* h0, float* out, int B, int T, int D,
                           void* stream) {
   if (!decay || !drive || !out) return RGLRU_ERR_NULL_POINTER;

@@ -187,6 +187,32 @@ __device__ __forceinline__ void sigmoid_pair2(float2 ur, float2 ui, float2& r, f
   i = mul2(inv, dr);
 }
 
+// The same with a per-channel bias added to each pre-activation.  The biases arrive pre-scaled by the
+// factor the sigmoid applies to its argument (0.5 for HALF_IO, -log2 e otherwise; see gate_bias_scale), so
+// the addition rides on the multiply that is there anyway.
+template <bool HALF_IO>
+__device__ __forceinline__ float gate_bias_scale() { return HALF_IO ? 0.5f : -LOG2E; }
+template <bool HALF_IO>
+__device__ __forceinline__ void sigmoid_pair2_biased(float2 ur, float2 ui, float2 br, float2 bi, float2& r, float2& i) {
+  if (HALF_IO) {
+    const float2 hr = fma2(ur, f2(0.5f), br);
+    const float2 hi = fma2(ui, f2(0.5f), bi);
+    r = fma2(make_float2(tanh_approx(hr.x), tanh_approx(hr.y)), f2(0.5f), f2(0.5f));
+    i = fma2(make_float2(tanh_approx(hi.x), tanh_approx(hi.y)), f2(0.5f), f2(0.5f));
+    return;
+  }
+  float2 tr = fma2(ur, f2(-LOG2E), br);
+  float2 ti = fma2(ui, f2(-LOG2E), bi);
+  const float2 er = make_float2(ex2_approx(fminf(tr.x, 60.0f)), ex2_approx(fminf(tr.y, 60.0f)));
+  const float2 ei = make_float2(ex2_approx(fminf(ti.x, 60.0f)), ex2_approx(fminf(ti.y, 60.0f)));
+  const float2 dr = add2(er, f2(1.0f));
+  const float2 di = add2(ei, f2(1.0f));
+  const float2 d = mul2(dr, di);
+  const float2 inv = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+  r = mul2(inv, di);
+  i = mul2(inv, dr);
+}
+
 // GeLU in its tanh form (griffin/griffin.py:464 of the reference): gelu(v) = v * s with
 // s = sigmoid(2 z) = (1 + tanh z) / 2 and z = k0 v (1 + k1 v^2).  Returns s; precision as sigmoid_pair2.
 constexpr float GELU_K0 = 0.7978845608028654f;   // sqrt(2 / pi)

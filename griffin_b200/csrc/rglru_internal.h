@@ -30,6 +30,10 @@ struct ScanFwdArgs {
   const float* conv_b;
   const void* conv_state;
   const void* g;     // merged variant only: pre-activation of the GeLU branch [B, T, D]; y receives h * gelu(g)
+  // grouped gate layout only: ur == ui == one [B, T, 2 D] tensor, gate_bw channels per gate head,
+  // gate_bias [2 D] fp32 in the same column layout or nullptr
+  const float* gate_bias;
+  int gate_bw;
   int B, T, D;
   float c;
   int* status;
@@ -57,6 +61,8 @@ struct ScanBwdArgs {
   const void* conv_state;
   const void* g;        // merged variant only: dy is then the gradient of h * gelu(g), dg receives that of g
   void* dg;
+  const float* gate_bias;   // grouped gate layout only (see ScanFwdArgs); dur / dui then share that layout too
+  int gate_bw;
   int B, T, D;
   float c;
   int* status;
@@ -146,6 +152,9 @@ cudaError_t launch_conv_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, c
 cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
 cudaError_t launch_merge_fwd(bool bf16, bool use_tma, bool conv, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
 cudaError_t launch_merge_bwd(bool bf16, bool use_tma, bool conv, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
+cudaError_t launch_grouped_fwd(bool bf16, bool merge, const FwdMaps& maps, const ScanFwdArgs& args, cudaStream_t s);
+cudaError_t launch_grouped_bwd(bool bf16, bool merge, const BwdMaps& maps, const ScanBwdArgs& args, cudaStream_t s);
+int grouped_box_cols();
 int scan_fwd_variant(int B, int T, int D, bool bf16);
 int scan_bwd_variant(int B, int T, int D, bool bf16);
 int scan_fwd_box_rows(int variant);

@@ -99,6 +99,27 @@ struct ChainSmem {
   static constexpr int EIN = LANES * CH * 4;  // float per (lane, channel)
 };
 
+// Grouped gate layout: both gate pre-activations come from ONE tensor [B, T, 2 D] written by a single
+// grouped GEMM with the two weight blocks of a gate head stacked, i.e. per head of width bw the columns are
+// [u_r (bw) | u_i (bw)].  The channel tile at d0 (which never straddles a head: bw is a multiple of the tile
+// width) finds its u_r columns at (d0 / bw) * 2 bw + d0 % bw and its u_i columns bw further.  The gate biases
+// (same column layout, fp32) are added in the kernel, pre-scaled for the sigmoid.
+struct GateBias {
+  float2 r[2], i[2];
+};
+__device__ __forceinline__ int grouped_col(int d0, int bw) { return (d0 / bw) * 2 * bw + d0 % bw; }
+template <bool HALF_IO>
+__device__ __forceinline__ void load_gate_bias(const float* bias, int rcol, int icol, GateBias& gb) {
+  const float sc = gate_bias_scale<HALF_IO>();
+  float4 br = make_float4(0.f, 0.f, 0.f, 0.f), bi = br;
+  if (bias) {
+    br = *reinterpret_cast<const float4*>(bias + rcol);
+    bi = *reinterpret_cast<const float4*>(bias + icol);
+  }
+  gb.r[0] = make_float2(br.x * sc, br.y * sc); gb.r[1] = make_float2(br.z * sc, br.w * sc);
+  gb.i[0] = make_float2(bi.x * sc, bi.y * sc); gb.i[1] = make_float2(bi.z * sc, bi.w * sc);
+}
+
 // Taps of the width-4 causal depthwise conv for the four channels a thread owns (column 3 of the
 // [D, 4] weight multiplies the current token; griffin/griffin.py:474-486 of the reference).
 struct ConvTaps {
@@ -183,10 +204,10 @@ __device__ __forceinline__ void load_hist(const void* conv_state, int b, int d, 
 // Forward
 // ======================================================================
 
-template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV>
+template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV, bool GROUPED>
 __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, const uint8_t* ti, int off0,
                                           const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
-                                          const ConvTaps& ct, const float2 (*hist)[2],
+                                          const ConvTaps& ct, const float2 (*hist)[2], const GateBias& gb,
                                           float2 (&P)[TS][2], float2 (&S)[TS][2]) {
   constexpr int ROWB = CH * sizeof(IO);
   float2 p[2] = {f2(1.0f), f2(1.0f)};
@@ -205,7 +226,8 @@ __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, 
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) {
       float2 r, i;
-      sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
+      if (GROUPED) sigmoid_pair2_biased<sizeof(IO) == 2>(rv[cp], iv[cp], gb.r[cp], gb.i[cp], r, i);
+      else sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
       const float2 e = one_minus_exp_neg2<POLY>(mul2(r, K[cp]));   // 1 - a
       float2 a = fma2(e, f2(-1.0f), f2(1.0f));
       const float2 gsq = mul2(e, fma2(e, f2(-1.0f), f2(2.0f)));     // 1 - a^2
@@ -243,7 +265,7 @@ struct FwdSmem {
 // no compute warp ever waits on the copy engine's instruction latency.
 // MERGE: the kernel also reads the pre-activation of the block's GeLU branch and writes
 // h_t * gelu(branch_t) (griffin/griffin.py:464, 520 of the reference) instead of h_t.
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
   using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
@@ -266,6 +288,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
   const int d0 = blockIdx.x * CH;
   const int nchunks = (p.T + TC - 1) / TC;
   const int nsave = (p.T + SAVE_EVERY - 1) / SAVE_EVERY;
+  static_assert(!GROUPED || USE_TMA, "the grouped gate layout is staged by TMA only");
+  const int rcol = GROUPED ? grouped_col(d0, p.gate_bw) : d0;   // first column of this tile's u_r / u_i
+  const int icol = GROUPED ? rcol + p.gate_bw : d0;
 
   pdl_launch_dependents();
   if (tid == 0) {
@@ -295,8 +320,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
         uint8_t* st = smem + sidx * SM::STAGE;
         mbar_expect_tx(&full[sidx], SM::STAGE);
         tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
-        tma_load_3d(st + SM::TILEX, &maps.ur, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::TILEX, &maps.ur, rcol, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, icol, k * TC, b, &full[sidx]);
         if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
       };
       for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
@@ -319,6 +344,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
 
   ConvTaps ct;
   if (CONV) load_taps(p.conv_w, p.conv_b, d0 + vec * CV, p.D, ct);
+  GateBias gb;
+  if (GROUPED) load_gate_bias<sizeof(IO) == 2>(p.gate_bias, rcol + vec * CV, icol + vec * CV, gb);
 
   // Level-two chain state: thread `tid` < CH carries channel d0 + tid across chunks.
   float carry = 0.0f;
@@ -356,11 +383,11 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
       hist = hist_v;
     }
     if (masked) {
-      if (poly) fwd_local<IO, TS, CH, true, true, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
-      else fwd_local<IO, TS, CH, true, false, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
+      if (poly) fwd_local<IO, TS, CH, true, true, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
+      else fwd_local<IO, TS, CH, true, false, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
     } else {
-      if (poly) fwd_local<IO, TS, CH, false, true, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
-      else fwd_local<IO, TS, CH, false, false, CONV>(tx, tr, ti, off0, K, fl, ct, hist, P, S);
+      if (poly) fwd_local<IO, TS, CH, false, true, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
+      else fwd_local<IO, TS, CH, false, false, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
     }
     {
       float4* dst = reinterpret_cast<float4*>(agg + lane_t * CH + vec * CV);
@@ -441,10 +468,10 @@ struct BwdRegs {
 // MERGE: the incoming gradient is that of h * gelu(branch).  This pass turns it into the gradient of h
 // (kept, rounded to the I/O type, where the incoming gradient was) and leaves d_out * gelu'(branch) in the
 // branch tile; the second pass multiplies that by h_t to get the branch gradient.
-template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV, bool MERGE>
+template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV, bool MERGE, bool GROUPED>
 __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8_t* tx, const uint8_t* tr, const uint8_t* ti,
                                           int off0, const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
-                                          const ConvTaps& ct, const float2 (*hist)[2],
+                                          const ConvTaps& ct, const float2 (*hist)[2], const GateBias& gb,
                                           BwdRegs<IO, TS>& R, float2 (&prod)[2], float2 (&sfwd)[2],
                                           float2 (&crev)[2]) {
   constexpr int ROWB = CH * sizeof(IO);
@@ -478,7 +505,8 @@ __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8
 #pragma unroll
     for (int cp = 0; cp < 2; ++cp) {
       float2 r, i;
-      sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
+      if (GROUPED) sigmoid_pair2_biased<sizeof(IO) == 2>(rv[cp], iv[cp], gb.r[cp], gb.i[cp], r, i);
+      else sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
       const float2 e = one_minus_exp_neg2<POLY>(mul2(r, K[cp]));       // 1 - a
       const float2 a = fma2(e, f2(-1.0f), f2(1.0f));
       float2 gsq = mul2(e, fma2(e, f2(-1.0f), f2(2.0f)));               // 1 - a^2
@@ -540,7 +568,7 @@ struct BwdSmem {
   static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
     rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
   using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
@@ -566,6 +594,9 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
   const int d0 = blockIdx.x * CH;
   const int nchunks = (p.T + TC - 1) / TC;
   const int nsave = (p.T + SAVE_EVERY - 1) / SAVE_EVERY;
+  static_assert(!GROUPED || USE_TMA, "the grouped gate layout is staged by TMA only");
+  const int rcol = GROUPED ? grouped_col(d0, p.gate_bw) : d0;   // first column of this tile's u_r / u_i (and du_r / du_i)
+  const int icol = GROUPED ? rcol + p.gate_bw : d0;
 
   pdl_launch_dependents();
   if (tid == 0) {
@@ -597,8 +628,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         mbar_expect_tx(&full[sidx], SM::STAGE);
         tma_load_3d(st, &maps.dy, d0, k * TC, b, &full[sidx]);
         tma_load_3d(st + SM::OFF_X, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);
-        tma_load_3d(st + SM::OFF_UR, &maps.ur, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::OFF_UI, &maps.ui, d0, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::OFF_UR, &maps.ur, rcol, k * TC, b, &full[sidx]);
+        tma_load_3d(st + SM::OFF_UI, &maps.ui, icol, k * TC, b, &full[sidx]);
         if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
       };
       for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
@@ -608,8 +639,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         uint8_t* st = smem + sidx * SM::STAGE;
         mbar_wait_or_flag(&ready[sidx], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
         tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
-        tma_store_3d(&maps.dur, st + SM::OFF_UR, d0, k * TC, b);
-        tma_store_3d(&maps.dui, st + SM::OFF_UI, d0, k * TC, b);
+        tma_store_3d(&maps.dur, st + SM::OFF_UR, rcol, k * TC, b);
+        tma_store_3d(&maps.dui, st + SM::OFF_UI, icol, k * TC, b);
         if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
         tma_commit();
         if (q + NSTAGE < nchunks) {
@@ -632,6 +663,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
 
   ConvTaps ct;
   if (CONV) load_taps(p.conv_w, p.conv_b, d0 + vec * CV, p.D, ct);
+  GateBias gb;
+  if (GROUPED) load_gate_bias<sizeof(IO) == 2>(p.gate_bias, rcol + vec * CV, icol + vec * CV, gb);
 
   float2 dlam[2] = {f2(0.0f), f2(0.0f)};
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
@@ -678,11 +711,11 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         hist = hist_v;
       }
       if (masked) {
-        if (poly) bwd_local<IO, TS, CH, true, true, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
-        else bwd_local<IO, TS, CH, true, false, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        if (poly) bwd_local<IO, TS, CH, true, true, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, true, false, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
       } else {
-        if (poly) bwd_local<IO, TS, CH, false, true, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
-        else bwd_local<IO, TS, CH, false, false, CONV, MERGE>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, R, prod, sfwd, crev);
+        if (poly) bwd_local<IO, TS, CH, false, true, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
+        else bwd_local<IO, TS, CH, false, false, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
       }
     }
     {
@@ -1185,10 +1218,10 @@ static cudaError_t set_smem(Kern kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE>;
+  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
   constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
   cudaError_t e = set_smem(kern, bytes);
@@ -1214,10 +1247,10 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
   return bf16 ? launch_fwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_fwd_io<float>(use_tma, variant, maps, a, s);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE>;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
   constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
   cudaError_t e = set_smem(kern, bytes);
@@ -1286,6 +1319,28 @@ cudaError_t launch_merge_bwd(bool bf16, bool use_tma, bool conv, const BwdMaps& 
                         : launch_merge_bwd_t<__nv_bfloat16, false>(use_tma, maps, a, s);
   return conv ? launch_merge_bwd_t<float, true>(use_tma, maps, a, s) : launch_merge_bwd_t<float, false>(use_tma, maps, a, s);
 }
+
+// Grouped gate layout (one [B, T, 2 D] gate tensor, biases added in the kernel), with or without the
+// branch merge; TMA staging only, one shape (64 channels x 64 steps).
+template <typename IO, bool MERGE>
+static cudaError_t launch_grouped_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
+  constexpr bool H = sizeof(IO) == 2;
+  return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, MERGE, true>(maps, a, s);
+}
+template <typename IO, bool MERGE>
+static cudaError_t launch_grouped_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
+  constexpr bool H = sizeof(IO) == 2;
+  return launch_bwd_t<IO, Shape64x16x4, H ? 4 : (MERGE ? 2 : 3), true, false, MERGE, true>(maps, a, s);
+}
+cudaError_t launch_grouped_fwd(bool bf16, bool merge, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
+  if (bf16) return merge ? launch_grouped_fwd_t<__nv_bfloat16, true>(maps, a, s) : launch_grouped_fwd_t<__nv_bfloat16, false>(maps, a, s);
+  return merge ? launch_grouped_fwd_t<float, true>(maps, a, s) : launch_grouped_fwd_t<float, false>(maps, a, s);
+}
+cudaError_t launch_grouped_bwd(bool bf16, bool merge, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
+  if (bf16) return merge ? launch_grouped_bwd_t<__nv_bfloat16, true>(maps, a, s) : launch_grouped_bwd_t<__nv_bfloat16, false>(maps, a, s);
+  return merge ? launch_grouped_bwd_t<float, true>(maps, a, s) : launch_grouped_bwd_t<float, false>(maps, a, s);
+}
+int grouped_box_cols() { return Shape64x16x4::CH; }
 
 int raw_box_rows() { return RAW_TC; }
 int raw_box_cols() { return CH; }

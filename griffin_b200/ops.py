@@ -411,6 +411,111 @@ def rglru_merged(x: Tensor, u_r: Tensor, u_i: Tensor, branch: Tensor, lam: Tenso
     return _MergedScan.apply(x, u_r, u_i, branch, lam, h0, None if tok is None else tok.contiguous(), c)
 
 
+# ----------------------------------------------------------------------------- both gates from one grouped GEMM
+def grouped_gates_supported(x: Tensor, gate_width: int) -> bool:
+    """Whether the grouped gate layout can be used: CUDA, a gate head that is a whole number of 64-channel
+    tiles, and rows the copy engine can address."""
+    return x.is_cuda and gate_width % 64 == 0 and (x.shape[-1] * x.element_size()) % 16 == 0
+
+
+def _aligned16(t: Optional[Tensor]) -> Optional[Tensor]:
+    return t if t is None or t.data_ptr() % 16 == 0 else t.clone()
+
+
+class _GroupedRGLRU(torch.autograd.Function):
+    """Gate projections + RG-LRU (+ optional GeLU-branch product) as one node around ONE grouped GEMM.
+
+    The two [G, bw, bw] gate weights are stacked per head and a single batched GEMM writes both gate
+    pre-activations straight into a [B, T, G, 2 bw] tensor (cuBLAS takes the strided output, so there is no
+    re-layout pass); the kernels read that layout, add the biases themselves and return the gradient in the
+    same layout, from which two more batched GEMMs give the input and weight gradients.
+    Reference: BlockDiagonalLinear griffin/griffin.py:129-154 called twice at :237-238."""
+
+    @staticmethod
+    def forward(ctx, x, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch):
+        lib = _lib.load()
+        with torch.autocast("cuda", enabled=False):
+            x = _aligned16(x.contiguous())
+            B, T, D = x.shape
+            G, bw, _ = w_r.shape
+            dt = _io_dtype(x, "grouped forward")
+            wcat = torch.cat([w_r, w_i], dim=1).to(x.dtype)                                   # [G, 2 bw, bw]
+            bias = torch.cat([b_r, b_i], dim=1).to(torch.float32).reshape(-1).contiguous()    # [2 D]
+            rows = x.view(B * T, G, bw).transpose(0, 1)                                       # [G, N, bw] view
+            u = torch.empty(B, T, 2 * D, device=x.device, dtype=x.dtype)
+            torch.bmm(rows, wcat.transpose(1, 2), out=u.view(B * T, G, 2 * bw).transpose(0, 1))
+            lam32 = lam.to(torch.float32).contiguous()
+            h032 = None if h0 is None else h0.to(torch.float32).contiguous()
+            branch = None if branch is None else _aligned16(branch.to(x.dtype).contiguous())
+            save = any(ctx.needs_input_grad)
+            out = torch.empty_like(x)
+            h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
+            nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
+            ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
+            with torch.cuda.device(x.device):
+                rc = lib.rglru_grouped_fwd(_ptr(x), _ptr(u), _ptr(bias), _ptr(branch), _ptr(lam32), _ptr(h032), _ptr(tok),
+                                           _ptr(out), _ptr(h_last), _ptr(ws) if save else None, nbytes, B, T, D, bw,
+                                           float(c), dt, _stream(x))
+            _lib.check(rc, "rglru_grouped_fwd")
+        ctx.save_for_backward(x, u, wcat, bias, lam32, h032, tok, ws, branch)
+        ctx.c = float(c)
+        ctx.meta = (w_r.dtype, b_r.dtype, w_i.dtype, b_i.dtype, lam.dtype)
+        return out, h_last
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dout, dh_last):
+        lib = _lib.load()
+        x, u, wcat, bias, lam32, h032, tok, ws, branch = ctx.saved_tensors
+        if ws.numel() == 0:
+            raise RuntimeError("grouped RG-LRU was run without saving its workspace; backward is unavailable")
+        with torch.autocast("cuda", enabled=False):
+            B, T, D = x.shape
+            G, bw2, bw = wcat.shape
+            dt = _io_dtype(x, "grouped backward")
+            dout = _aligned16(dout.to(x.dtype).contiguous())
+            dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
+            want_dh0 = h032 is not None and ctx.needs_input_grad[6]
+            dx = torch.empty_like(x)
+            du = torch.empty_like(u)
+            dbranch = None if branch is None else torch.empty_like(x)
+            dlam = torch.empty(D, device=x.device, dtype=torch.float32)
+            dh0 = torch.empty(B, D, device=x.device, dtype=torch.float32) if want_dh0 else None
+            with torch.cuda.device(x.device):
+                rc = lib.rglru_grouped_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(u), _ptr(bias), _ptr(branch),
+                                           _ptr(lam32), _ptr(h032), _ptr(tok), _ptr(ws), ws.numel(), _ptr(dx), _ptr(du),
+                                           _ptr(dbranch), _ptr(dlam), _ptr(dh0), B, T, D, bw, ctx.c, dt, _stream(x))
+            _lib.check(rc, "rglru_grouped_bwd")
+            dg = du.view(B * T, G, bw2).transpose(0, 1)                    # [G, N, 2 bw] view
+            rows = x.view(B * T, G, bw).transpose(0, 1)                    # [G, N, bw] view
+            dx.view(B * T, G, bw).transpose(0, 1).baddbmm_(dg, wcat)       # gate path added onto the direct path
+            dwcat = torch.bmm(dg.transpose(1, 2), rows)                    # [G, 2 bw, bw]
+            dbias = du.view(B * T, G, bw2).sum(dim=0, dtype=torch.float32)  # [G, 2 bw]
+        wr_dt, br_dt, wi_dt, bi_dt, lam_dt = ctx.meta
+        return (dx, dwcat[:, :bw].to(wr_dt), dbias[:, :bw].to(br_dt), dwcat[:, bw:].to(wi_dt), dbias[:, bw:].to(bi_dt),
+                dlam.to(lam_dt), dh0, None, None, dbranch)
+
+
+def rglru_grouped(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor,
+                  h0: Optional[Tensor] = None, tok: Optional[Tensor] = None, c: float = 8.0,
+                  branch: Optional[Tensor] = None) -> tuple[Tensor, Tensor]:
+    """y, h_last = RG-LRU(x) with both block-diagonal gate projections (weights [G, out, in], biases [G, out])
+    computed inside the node by one grouped GEMM; with ``branch`` the first result is y * gelu_tanh(branch)."""
+    if x.dim() != 3:
+        raise ValueError("x must be [batch, sequence, width]")
+    G, bw, bw_in = w_r.shape
+    if bw != bw_in or w_i.shape != w_r.shape or G * bw != x.shape[2] or b_r.shape != (G, bw) or b_i.shape != (G, bw):
+        raise ValueError("gate weights must be [heads, width/heads, width/heads] and biases [heads, width/heads]")
+    if lam.shape != (x.shape[2],):
+        raise ValueError("Lambda must have shape [width]")
+    if branch is not None and branch.shape != x.shape:
+        raise ValueError("branch must have the shape of x")
+    if not grouped_gates_supported(x, bw):
+        raise ValueError("the grouped gate layout needs CUDA tensors, gate heads of a multiple of 64 channels and "
+                         "rows that are a multiple of 16 bytes")
+    return _GroupedRGLRU.apply(x, w_r, b_r, w_i, b_i, lam, h0, None if tok is None else tok.contiguous(), c, branch)
+
+
 def _gate(x: Tensor, weight: Tensor, bias: Tensor) -> Tensor:
     """Block-diagonal projection [.., G*in] -> [.., G*out] in x's dtype (weight [G, out, in])."""
     g, wo, wi = weight.shape

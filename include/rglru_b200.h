@@ -136,6 +136,25 @@ int rglru_merge_bwd(const void* dout, const float* dh_last, const void* x, const
                     const float* h0, const uint8_t* tok, void* ws, size_t ws_bytes, void* dx, void* du_r, void* du_i,
                     void* dbranch, float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype, void* stream);
 
+/* Grouped gate layout.  The reference computes the two gates with two block-diagonal projections of the same
+ * input (BlockDiagonalLinear, griffin/griffin.py:129-154, called at :237-238).  Stacking the two weight blocks
+ * of every gate head ([G, 2 bw, bw]) turns them into ONE grouped GEMM whose output, written straight into a
+ * [B, T, G, 2 bw] tensor, holds per head the columns [u_r (bw) | u_i (bw)].  rglru_grouped_fwd / _bwd read (and
+ * write the gradient of) that tensor directly and add the gate biases themselves, so neither a re-layout nor a
+ * bias pass is needed.  branch / dbranch non-NULL additionally folds the branch merge (see rglru_merge_fwd).
+ *   u, du     : [B,T,2D] io_dtype in the layout above      gate_bias : [2D] fp32, same column layout, or NULL
+ *   gate_width: bw = D / G, a multiple of 64; D * sizeof(element) a multiple of 16 (else RGLRU_ERR_BAD_SHAPE)
+ *   x, u, branch, out, dout, dx, du, dbranch and gate_bias must be 16-byte aligned (else RGLRU_ERR_MISALIGNED).
+ * Everything else as rglru_fwd / rglru_bwd; the caller's GEMMs turn du into the input and weight gradients and
+ * its column sums into the bias gradients. */
+int rglru_grouped_fwd(const void* x, const void* u, const float* gate_bias, const void* branch, const float* lambda,
+                      const float* h0, const uint8_t* tok, void* out, float* h_last, void* ws, size_t ws_bytes, int B,
+                      int T, int D, int gate_width, float c, int io_dtype, void* stream);
+int rglru_grouped_bwd(const void* dout, const float* dh_last, const void* x, const void* u, const float* gate_bias,
+                      const void* branch, const float* lambda, const float* h0, const uint8_t* tok, void* ws,
+                      size_t ws_bytes, void* dx, void* du, void* dbranch, float* dlambda, float* dh0, int B, int T, int D,
+                      int gate_width, float c, int io_dtype, void* stream);
+
 /* Raw affine scan h_t = a_t h_{t-1} + b_t on fp32 tensors: the operator
  * fused_rglru_scan(decay, current_input, initial_state) of griffin/triton_scan.py:274-276
  * (forward kernel :31-60).  decay, drive, out: [B,T,D] fp32; h0: [B,D] fp32 or NULL. */

@@ -81,6 +81,15 @@ def test_argument_validation_codes(lib):
     assert lib.rglru_bwd(p, None, p, p, p, p, None, None, None, 0, p, p, p, p, None, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
     assert lib.rglru_conv_bwd(p, p, p, None, None, p, p, None, None, None, 0, 1, 2, 4, _lib.F32, None) == _lib.ERR_WORKSPACE
     assert lib.rglru_linear_scan_fwd(None, p, None, p, 1, 2, 4, None) == _lib.ERR_NULL_POINTER
+    # grouped gate layout: x, u, gate_bias, branch, lambda, h0, tok, out, h_last, ws, ws_bytes, B, T, D, gate_width, ...
+    big = (ctypes.c_float * 4096)()
+    q = (ctypes.addressof(big) + 15) // 16 * 16
+    assert lib.rglru_grouped_fwd(q, q, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 48, 8.0, _lib.F32, None) == _lib.ERR_BAD_SHAPE
+    assert lib.rglru_grouped_fwd(q, q, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, 5, None) == _lib.ERR_BAD_DTYPE
+    assert lib.rglru_grouped_fwd(q, q + 4, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_MISALIGNED
+    assert lib.rglru_grouped_fwd(q, None, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_grouped_bwd(q, None, q, q, None, q, q, None, None, q, 1 << 20, q, q, None, q, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_grouped_bwd(q, None, q, q, None, None, q, None, None, q, 8, q, q, None, q, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
     # branch merge: x, conv_w, conv_b, conv_state, u_r, u_i, branch, lambda, h0, tok, out, h_last, ws, ws_bytes, ...
     assert lib.rglru_merge_fwd(p, None, None, None, p, p, None, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_merge_fwd(p, None, None, None, p, p, p, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, 3, None) == _lib.ERR_BAD_DTYPE

@@ -344,6 +344,59 @@ def test_merge_folded_block_matches_reference_gradients_and_cache(fold_conv):
         assert orc.rel_l2(p.grad.cpu(), case["g." + key]) <= FP32_REL, key
 
 
+@pytest.mark.parametrize("merge", [False, True])
+@pytest.mark.parametrize("shape", [(2, 150, 128, 2), (1, 70, 256, 2), (3, 33, 192, 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_grouped_gate_layout_against_oracle(shape, dtype, merge):
+    """ops.rglru_grouped (rglru_grouped_fwd / _bwd): both block-diagonal gates from one grouped GEMM, biases
+    added in the kernel, against the oracle's RG_LRU.forward (griffin/griffin.py:129-154, 237-286) and autograd."""
+    from griffin_b200 import ops, _lib
+    from griffin_b200.modules import token_flags
+    B, T, D, G = shape
+    bw = D // G
+    gen = torch.Generator().manual_seed(13 * T + D + int(merge))
+    rnd = lambda *sz: torch.randn(*sz, generator=gen)
+    x = rnd(B, T, D).to(dtype)
+    branch = (rnd(B, T, D) * 1.5).to(dtype)
+    dout = rnd(B, T, D).to(dtype)
+    params = {"recurrence_gate.weight": rnd(G, bw, bw) / bw ** 0.5, "recurrence_gate.bias": rnd(G, bw) * 0.3,
+              "input_gate.weight": rnd(G, bw, bw) / bw ** 0.5, "input_gate.bias": rnd(G, bw) * 0.3,
+              "Lambda": orc.init_lambda(D, 8.0, gen)}
+    if dtype == torch.bfloat16:   # the GEMM sees bf16 weights; give the oracle the same rounded values
+        for k in ("recurrence_gate.weight", "input_gate.weight"):
+            params[k] = params[k].to(dtype).float()
+    h0, dh = rnd(B, D), rnd(B, D)
+    reset = torch.zeros(B, T, dtype=torch.bool)
+    reset[:, T // 2] = True
+    ref_p = {k: v.double().requires_grad_(True) for k, v in params.items()}
+    xd = x.double().requires_grad_(True)
+    bd = branch.double().requires_grad_(True)
+    h0d = h0.double().requires_grad_(True)
+    y_ref, hl_ref = orc.rglru_layer(xd, ref_p, h0d, reset=reset)
+    out_ref = y_ref * torch.nn.functional.gelu(bd, approximate="tanh") if merge else y_ref
+    ((out_ref * dout.double()).sum() + (hl_ref * dh.double()).sum()).backward()
+
+    dev_p = {k: v.to(DEV).requires_grad_(True) for k, v in params.items()}
+    xg = x.to(DEV).requires_grad_(True)
+    bg = branch.to(DEV).requires_grad_(True)
+    h0g = h0.to(DEV).requires_grad_(True)
+    flags = token_flags(B, T, DEV, reset=reset.to(DEV))
+    out, h_last = ops.rglru_grouped(xg, dev_p["recurrence_gate.weight"], dev_p["recurrence_gate.bias"],
+                                    dev_p["input_gate.weight"], dev_p["input_gate.bias"], dev_p["Lambda"], h0g, flags, 8.0,
+                                    bg if merge else None)
+    ((out.float() * dout.to(DEV).float()).sum() + (h_last * dh.to(DEV)).sum()).backward()
+    tol = FP32_REL if dtype == torch.float32 else BF16_REL
+    pairs = {"out": (out, out_ref), "h_last": (h_last, hl_ref), "dx": (xg.grad, xd.grad), "dh0": (h0g.grad, h0d.grad)}
+    if merge:
+        pairs["dbranch"] = (bg.grad, bd.grad)
+    for k in params:
+        pairs["d" + k] = (dev_p[k].grad, ref_p[k].grad)
+    for key, (got, want) in pairs.items():
+        err = orc.rel_l2(got, want)
+        assert err <= tol, (key, err)
+    assert _lib.device_status() == 0
+
+
 def test_folded_block_matches_reference_gradients_and_cache():
     """RecurrentBlock(fold_conv=True): same outputs, gradients and caches as the reference's stored results."""
     from griffin_b200 import RecurrentBlock
