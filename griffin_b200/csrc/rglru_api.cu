@@ -586,7 +586,7 @@ int rglru_conv_fwd(const void* x_in, const float* conv_w, const float* conv_b, c
   a.x_in = x_in; a.w = conv_w; a.bias = conv_b; a.state = conv_state; a.tok = tok; a.out = x_conv;
   a.new_state = new_state; a.B = B; a.T = T; a.D = D;
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(x_in, 16) && aligned(x_conv, 16) &&
-                aligned(conv_state, 16);
+                aligned(conv_state, 16) && aligned(conv_w, 16);
   const cudaError_t e = launch_conv_fwd(bf16, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
@@ -617,7 +617,7 @@ int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, co
   a.d_w = d_w; a.d_b = d_b; a.d_state = d_state; a.part = static_cast<float*>(ws);
   a.B = B; a.T = T; a.D = D;
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(d_conv, 16) && aligned(x_in, 16) &&
-                aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16);
+                aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16) && aligned(conv_w, 16);
   const cudaError_t e = launch_conv_bwd(bf16, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }

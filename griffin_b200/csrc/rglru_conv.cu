@@ -1,8 +1,10 @@
 // Causal depthwise convolution (kernel width 4) in front of the RG-LRU, its
 // backward, and the two single-token decode kernels.  All are streaming
-// kernels bound by HBM bandwidth: every activation is read once and written
-// once with 16-byte accesses, each thread sliding a 4-row register window over
-// a run of time-steps so the three-row halo is re-read once per run.
+// kernels: every activation is read once and written once, each thread owning
+// four channels and sliding a 4-row register window over a run of time-steps
+// (the three-row halo is re-read once per run).  A thread issues the loads of
+// several steps before it touches the first of them, and batches made only of
+// ordinary tokens (no document boundary, no padding) take a mask-free path.
 //
 // Reference behaviour: griffin/griffin.py:474-487 (dense path), :488-510
 // (right-padded path), :459-528 at T = 1 (decode).
@@ -13,53 +15,104 @@
 namespace rglru {
 
 constexpr int CONV_TAPS = 4;
+// Time-steps whose loads a thread issues together: 8 rows of 8 bytes for bf16, 4 rows of 16 bytes for fp32
+// (measured on B200: deeper batches spill for fp32, shallower ones leave bf16 latency-bound).
+template <typename IO>
+struct ConvUnroll { static constexpr int value = sizeof(IO) == 2 ? 8 : 4; };
 
+template <int BYTES> struct RawWord { using type = uint32_t; };
+template <> struct RawWord<8> { using type = uint2; };
+template <> struct RawWord<16> { using type = uint4; };
+
+// VEC channels of IO as one aligned 8- or 16-byte access (VEC == 1: scalar fallback for odd widths).  The
+// raw form is what a thread keeps in registers while several loads are in flight.
 template <typename IO, int VEC>
 struct Vec {
-  // VEC channels of IO as one aligned access (VEC == 1: scalar fallback for odd widths).
-  static __device__ __forceinline__ void load(const IO* p, float (&v)[VEC]) {
-    if (VEC == 1) {
-      v[0] = Pack<IO>::to_float(p[0]);
-    } else if (sizeof(IO) == 4) {
-      const float4 r = *reinterpret_cast<const float4*>(p);
-      v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  static constexpr int BYTES = VEC * static_cast<int>(sizeof(IO));
+  static_assert(VEC == 1 || BYTES == 8 || BYTES == 16, "one 8- or 16-byte access per thread and row");
+  using Raw = typename RawWord<VEC == 1 ? 4 : BYTES>::type;
+
+  static __device__ __forceinline__ Raw load_raw(const IO* p) {
+    if constexpr (VEC == 1) {
+      if constexpr (sizeof(IO) == 4) return __float_as_uint(p[0]);
+      else return static_cast<uint32_t>(*reinterpret_cast<const unsigned short*>(p)) << 16;
     } else {
-      const uint4 r = *reinterpret_cast<const uint4*>(p);
-      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+      return *reinterpret_cast<const Raw*>(p);
+    }
+  }
+  static __device__ __forceinline__ void unpack(const Raw& r, float (&v)[VEC]) {
+    if constexpr (VEC == 1) {
+      v[0] = __uint_as_float(r);
+    } else {
+      constexpr int NW = BYTES / 4;
+      uint32_t w[NW];
+      if constexpr (NW == 2) { w[0] = r.x; w[1] = r.y; }
+      else { w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w; }
+      if constexpr (sizeof(IO) == 4) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        v[(2 * k) % VEC] = __uint_as_float(w[k] << 16);
-        v[(2 * k + 1) % VEC] = __uint_as_float(w[k] & 0xffff0000u);
+        for (int k = 0; k < NW; ++k) v[k] = __uint_as_float(w[k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < NW; ++k) {
+          v[2 * k] = __uint_as_float(w[k] << 16);
+          v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
       }
     }
   }
+  static __device__ __forceinline__ void load(const IO* p, float (&v)[VEC]) { unpack(load_raw(p), v); }
   static __device__ __forceinline__ void store(IO* p, const float (&v)[VEC]) {
-    if (VEC == 1) {
+    if constexpr (VEC == 1) {
       p[0] = Pack<IO>::from_float(v[0]);
-    } else if (sizeof(IO) == 4) {
-      *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
     } else {
-      uint32_t w[4];
+      constexpr int NW = BYTES / 4;
+      uint32_t w[NW];
+      if constexpr (sizeof(IO) == 4) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(v[(2 * k) % VEC], v[(2 * k + 1) % VEC]);
-        w[k] = *reinterpret_cast<uint32_t*>(&h);
+        for (int k = 0; k < NW; ++k) w[k] = __float_as_uint(v[k]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < NW; ++k) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+          w[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
       }
-      *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+      if constexpr (NW == 2) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+      else *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 };
 
+// Channels per thread of the conv kernels: 4 for both element types (8-byte accesses for bf16), which keeps
+// the per-thread weights, windows and raw batch small enough for several resident blocks per SM.  The decode
+// kernels, with nothing to keep, use full 16-byte accesses.
 template <typename IO>
 constexpr int vec_width() { return 16 / sizeof(IO); }
+constexpr int CONV_VEC = 4;
+
+// The four taps of VEC channels starting at d: wt[k][v] = w[d + v, k] (one 16-byte load per channel).
+template <int VEC>
+__device__ __forceinline__ void load_conv_weights(const float* __restrict__ w, int d, float (&wt)[CONV_TAPS][VEC]) {
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    if constexpr (VEC == 1) {
+#pragma unroll
+      for (int k = 0; k < CONV_TAPS; ++k) wt[k][v] = w[(d + v) * CONV_TAPS + k];
+    } else {
+      const float4 q = *reinterpret_cast<const float4*>(w + static_cast<size_t>(d + v) * CONV_TAPS);
+      wt[0][v] = q.x; wt[1][v] = q.y; wt[2][v] = q.z; wt[3][v] = q.w;
+    }
+  }
+}
 
 // ---------------------------------------------------------------- forward
 // Thread = (batch row, run of RUN time-steps, VEC channels).
 template <typename IO, int VEC, int RUN>
-__global__ void __launch_bounds__(256) conv_fwd_kernel(const IO* __restrict__ xin, const float* __restrict__ w,
+__global__ void __launch_bounds__(256, 3) conv_fwd_kernel(const IO* __restrict__ xin, const float* __restrict__ w,
                                                        const float* __restrict__ bias, const IO* __restrict__ state,
                                                        const uint8_t* __restrict__ tok, IO* __restrict__ out, int B,
                                                        int T, int D) {
+  constexpr int UNROLL = ConvUnroll<IO>::value;
   const int nvec = D / VEC;
   const int nrun = (T + RUN - 1) / RUN;
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -72,12 +125,9 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(const IO* __restrict__ xi
   const int t_end = min(T, t_begin + RUN);
 
   float wt[CONV_TAPS][VEC], bs[VEC];
+  load_conv_weights<VEC>(w, d, wt);
 #pragma unroll
-  for (int v = 0; v < VEC; ++v) {
-    bs[v] = bias ? bias[d + v] : 0.0f;
-#pragma unroll
-    for (int k = 0; k < CONV_TAPS; ++k) wt[k][v] = w[(d + v) * CONV_TAPS + k];
-  }
+  for (int v = 0; v < VEC; ++v) bs[v] = bias ? bias[d + v] : 0.0f;
   // hist[l-1] holds the input l steps before the current one.
   float hist[CONV_TAPS - 1][VEC];
 #pragma unroll
@@ -92,26 +142,68 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(const IO* __restrict__ xi
       for (int v = 0; v < VEC; ++v) hist[l - 1][v] = 0.0f;
     }
   }
-  for (int t = t_begin; t < t_end; ++t) {
-    const size_t at = (static_cast<size_t>(b) * T + t) * D + d;
-    float cur[VEC], acc[VEC];
-    Vec<IO, VEC>::load(xin + at, cur);
-    const uint32_t f = tok ? tok[static_cast<size_t>(b) * T + t] : 0u;
-    const int reach = 3 - static_cast<int>(f & TOK_CUT_MASK);  // taps with lag <= reach stay inside the document
+  // Steps are taken UNROLL at a time with all of a batch's loads issued before its arithmetic, so that
+  // every thread keeps several 16-byte requests in flight.
+  for (int t0 = t_begin; t0 < t_end; t0 += UNROLL) {
+    typename Vec<IO, VEC>::Raw raw[UNROLL];
+    uint32_t fl[UNROLL];
+    uint32_t any_flag = 0u;
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) {
-      float a = fmaf(wt[3][v], cur[v], bs[v]);
-      if (reach >= 1) a = fmaf(wt[2][v], hist[0][v], a);
-      if (reach >= 2) a = fmaf(wt[1][v], hist[1][v], a);
-      if (reach >= 3) a = fmaf(wt[0][v], hist[2][v], a);
-      acc[v] = (f & TOK_INACTIVE) ? 0.0f : a;
+    for (int u = 0; u < UNROLL; ++u) {
+      const int t = t0 + u;
+      fl[u] = 0u;
+      if (t < t_end) {
+        raw[u] = Vec<IO, VEC>::load_raw(xin + (static_cast<size_t>(b) * T + t) * D + d);
+        if (tok) fl[u] = tok[static_cast<size_t>(b) * T + t];
+      }
+      any_flag |= fl[u];
     }
-    Vec<IO, VEC>::store(out + at, acc);
+    if (any_flag == 0u && t0 + UNROLL <= t_end) {
+      // Ordinary tokens only (uniform across the warp, whose threads share the time range): all four taps.
 #pragma unroll
-    for (int v = 0; v < VEC; ++v) {
-      hist[2][v] = hist[1][v];
-      hist[1][v] = hist[0][v];
-      hist[0][v] = cur[v];
+      for (int u = 0; u < UNROLL; ++u) {
+        float acc[VEC], cur[VEC];
+        Vec<IO, VEC>::unpack(raw[u], cur);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          float a = fmaf(wt[3][v], cur[v], bs[v]);
+          a = fmaf(wt[2][v], hist[0][v], a);
+          a = fmaf(wt[1][v], hist[1][v], a);
+          acc[v] = fmaf(wt[0][v], hist[2][v], a);
+        }
+        Vec<IO, VEC>::store(out + (static_cast<size_t>(b) * T + t0 + u) * D + d, acc);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          hist[2][v] = hist[1][v];
+          hist[1][v] = hist[0][v];
+          hist[0][v] = cur[v];
+        }
+      }
+      continue;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int t = t0 + u;
+      if (t >= t_end) break;
+      const uint32_t f = fl[u];
+      const int reach = 3 - static_cast<int>(f & TOK_CUT_MASK);  // taps with lag <= reach stay inside the document
+      float acc[VEC], cur[VEC];
+      Vec<IO, VEC>::unpack(raw[u], cur);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        float a = fmaf(wt[3][v], cur[v], bs[v]);
+        if (reach >= 1) a = fmaf(wt[2][v], hist[0][v], a);
+        if (reach >= 2) a = fmaf(wt[1][v], hist[1][v], a);
+        if (reach >= 3) a = fmaf(wt[0][v], hist[2][v], a);
+        acc[v] = (f & TOK_INACTIVE) ? 0.0f : a;
+      }
+      Vec<IO, VEC>::store(out + (static_cast<size_t>(b) * T + t) * D + d, acc);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        hist[2][v] = hist[1][v];
+        hist[1][v] = hist[0][v];
+        hist[0][v] = cur[v];
+      }
     }
   }
 }
@@ -160,12 +252,13 @@ __global__ void conv_state_kernel(const IO* __restrict__ xin, const IO* __restri
 // Block = 8 runs x 32 channel vectors; the 8 runs are folded in shared memory so one
 // partial row [5, D] is written per (row, 8*RUN time-steps).
 template <typename IO, int VEC, int RUN>
-__global__ void __launch_bounds__(256) conv_bwd_kernel(const IO* __restrict__ dconv, const IO* __restrict__ xin,
+__global__ void __launch_bounds__(256, 2) conv_bwd_kernel(const IO* __restrict__ dconv, const IO* __restrict__ xin,
                                                        const float* __restrict__ w, const IO* __restrict__ state,
                                                        const uint8_t* __restrict__ tok, IO* __restrict__ dxin,
                                                        IO* __restrict__ dstate, float* __restrict__ part, int B, int T,
                                                        int D) {
   constexpr int RUNS_PER_BLOCK = 8, VECS_PER_BLOCK = 32;
+  constexpr int UNROLL = ConvUnroll<IO>::value;
   __shared__ float red[RUNS_PER_BLOCK][5][VECS_PER_BLOCK * VEC + 1];
   const int nvec = D / VEC;
   const int vslot = threadIdx.x % VECS_PER_BLOCK;
@@ -186,10 +279,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(const IO* __restrict__ dc
 
   if (live && t_begin < T) {
     float wt[CONV_TAPS][VEC];
-#pragma unroll
-    for (int v = 0; v < VEC; ++v)
-#pragma unroll
-      for (int k = 0; k < CONV_TAPS; ++k) wt[k][v] = w[(d + v) * CONV_TAPS + k];
+    load_conv_weights<VEC>(w, d, wt);
 
     auto load_in = [&](int t, float (&v)[VEC]) {
       if (t >= 0) Vec<IO, VEC>::load(xin + (static_cast<size_t>(b) * T + t) * D + d, v);
@@ -210,6 +300,16 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(const IO* __restrict__ dc
       if (f & TOK_INACTIVE) return;
       reach = 3 - static_cast<int>(f & TOK_CUT_MASK);
       Vec<IO, VEC>::load(dconv + (static_cast<size_t>(b) * T + t) * D + d, g);
+    };
+    // The same in raw form: reach < 0 means "contributes nothing" and the raw value is then unspecified.
+    using Raw = typename Vec<IO, VEC>::Raw;
+    auto load_grad_raw = [&](int t, Raw& g, int& reach) {
+      reach = -1;
+      if (t < 0 || t >= T) return;
+      const uint32_t f = tok ? tok[static_cast<size_t>(b) * T + t] : 0u;
+      if (f & TOK_INACTIVE) return;
+      reach = 3 - static_cast<int>(f & TOK_CUT_MASK);
+      g = Vec<IO, VEC>::load_raw(dconv + (static_cast<size_t>(b) * T + t) * D + d);
     };
 
     // Sliding windows: xin at t-1..t-3 (for d_w) and dconv at t+1..t+3 (for dx_in).
@@ -244,31 +344,83 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(const IO* __restrict__ dc
       }
     }
 
-    for (int t = t_begin; t < t_end; ++t) {
-      float cur[VEC], dx[VEC];
-      load_in(t, cur);
-      load_grad(t + 3, g3, r3);
+    // UNROLL steps at a time, loads first (see the forward kernel).
+    for (int t0 = t_begin; t0 < t_end; t0 += UNROLL) {
+      Raw curs[UNROLL], gin[UNROLL];
+      int rin[UNROLL];
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) {
-        float a = 0.0f;
-        if (r0 >= 0) a = wt[3][v] * g0[v];
-        if (r1 >= 1) a = fmaf(wt[2][v], g1[v], a);
-        if (r2 >= 2) a = fmaf(wt[1][v], g2[v], a);
-        if (r3 >= 3) a = fmaf(wt[0][v], g3[v], a);
-        dx[v] = a;
-        gw[4][v] += g0[v];
-        gw[3][v] = fmaf(g0[v], cur[v], gw[3][v]);
-        if (r0 >= 1) gw[2][v] = fmaf(g0[v], hist[0][v], gw[2][v]);
-        if (r0 >= 2) gw[1][v] = fmaf(g0[v], hist[1][v], gw[1][v]);
-        if (r0 >= 3) gw[0][v] = fmaf(g0[v], hist[2][v], gw[0][v]);
+      for (int u = 0; u < UNROLL; ++u) {
+        rin[u] = -1;
+        if (t0 + u < t_end) {   // t0 + u >= 0 here, so the input row comes from xin itself
+          curs[u] = Vec<IO, VEC>::load_raw(xin + (static_cast<size_t>(b) * T + t0 + u) * D + d);
+          load_grad_raw(t0 + u + 3, gin[u], rin[u]);
+        }
       }
-      Vec<IO, VEC>::store(dxin + (static_cast<size_t>(b) * T + t) * D + d, dx);
+      bool ordinary = (t0 + UNROLL <= t_end) && r0 == 3 && r1 == 3 && r2 == 3;
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) {
-        hist[2][v] = hist[1][v]; hist[1][v] = hist[0][v]; hist[0][v] = cur[v];
-        g0[v] = g1[v]; g1[v] = g2[v]; g2[v] = g3[v];
+      for (int u = 0; u < UNROLL; ++u) ordinary = ordinary && rin[u] == 3;
+      if (ordinary) {
+        // Every token that touches this batch is an ordinary one (uniform across the warp): no tap masks.
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          float dx[VEC], cur[VEC];
+          Vec<IO, VEC>::unpack(curs[u], cur);
+          Vec<IO, VEC>::unpack(gin[u], g3);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            float a = wt[3][v] * g0[v];
+            a = fmaf(wt[2][v], g1[v], a);
+            a = fmaf(wt[1][v], g2[v], a);
+            dx[v] = fmaf(wt[0][v], g3[v], a);
+            gw[4][v] += g0[v];
+            gw[3][v] = fmaf(g0[v], cur[v], gw[3][v]);
+            gw[2][v] = fmaf(g0[v], hist[0][v], gw[2][v]);
+            gw[1][v] = fmaf(g0[v], hist[1][v], gw[1][v]);
+            gw[0][v] = fmaf(g0[v], hist[2][v], gw[0][v]);
+          }
+          Vec<IO, VEC>::store(dxin + (static_cast<size_t>(b) * T + t0 + u) * D + d, dx);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            hist[2][v] = hist[1][v]; hist[1][v] = hist[0][v]; hist[0][v] = cur[v];
+            g0[v] = g1[v]; g1[v] = g2[v]; g2[v] = g3[v];
+          }
+        }
+        continue;
       }
-      r0 = r1; r1 = r2; r2 = r3;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int t = t0 + u;
+        if (t >= t_end) break;
+        float dx[VEC], cur[VEC];
+        r3 = rin[u];
+        Vec<IO, VEC>::unpack(curs[u], cur);
+        if (r3 >= 0) Vec<IO, VEC>::unpack(gin[u], g3);
+        else {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) g3[v] = 0.0f;
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          float a = 0.0f;
+          if (r0 >= 0) a = wt[3][v] * g0[v];
+          if (r1 >= 1) a = fmaf(wt[2][v], g1[v], a);
+          if (r2 >= 2) a = fmaf(wt[1][v], g2[v], a);
+          if (r3 >= 3) a = fmaf(wt[0][v], g3[v], a);
+          dx[v] = a;
+          gw[4][v] += g0[v];
+          gw[3][v] = fmaf(g0[v], cur[v], gw[3][v]);
+          if (r0 >= 1) gw[2][v] = fmaf(g0[v], hist[0][v], gw[2][v]);
+          if (r0 >= 2) gw[1][v] = fmaf(g0[v], hist[1][v], gw[1][v]);
+          if (r0 >= 3) gw[0][v] = fmaf(g0[v], hist[2][v], gw[0][v]);
+        }
+        Vec<IO, VEC>::store(dxin + (static_cast<size_t>(b) * T + t) * D + d, dx);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          hist[2][v] = hist[1][v]; hist[1][v] = hist[0][v]; hist[0][v] = cur[v];
+          g0[v] = g1[v]; g1[v] = g2[v]; g2[v] = g3[v];
+        }
+        r0 = r1; r1 = r2; r2 = r3;
+      }
     }
   }
 
@@ -393,7 +545,7 @@ constexpr int CONV_RUN = 32;
 
 template <typename IO>
 static cudaError_t conv_fwd_t(const ConvArgs& a, cudaStream_t s) {
-  constexpr int V = vec_width<IO>();
+  constexpr int V = CONV_VEC;
   const bool vec_ok = a.vector_ok;
   const int nvec = vec_ok ? a.D / V : a.D;
   const int nrun = (a.T + CONV_RUN - 1) / CONV_RUN;
@@ -419,7 +571,7 @@ int conv_bwd_partial_rows(int B, int T) { return B * ((T + 8 * CONV_RUN - 1) / (
 
 template <typename IO>
 static cudaError_t conv_bwd_t(const ConvBwdArgs& a, cudaStream_t s) {
-  constexpr int V = vec_width<IO>();
+  constexpr int V = CONV_VEC;
   const bool vec_ok = a.vector_ok;
   const int nvec = vec_ok ? a.D / V : a.D;
   const int tblocks = (a.T + 8 * CONV_RUN - 1) / (8 * CONV_RUN);

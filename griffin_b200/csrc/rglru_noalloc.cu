@@ -84,7 +84,7 @@ int rglru_conv_bwd_noalloc(const void* d_conv, const void* x_in, const float* co
   a.d_w = d_w; a.d_b = d_b; a.d_state = d_state; a.part = scratch;
   a.B = B; a.T = T; a.D = D;
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(d_conv, 16) && aligned(x_in, 16) &&
-                aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16);
+                aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16) && aligned(conv_w, 16);
   const cudaError_t e = launch_conv_bwd(bf16, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : RGLRU_ERR_LAUNCH;
 }
