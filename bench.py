@@ -475,8 +475,8 @@ def run_lm(args) -> dict:
 
     def train(ids):
         with torch.autocast("cuda", dtype=torch.bfloat16):
-            logits = net(ids[:, :-1])
-        loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, V), ids[:, 1:].reshape(-1))
+            logits = net(ids[:, :-1], pad_vocab=True)       # vocabulary padded to a multiple of 8, -inf in the padding
+        loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.size(-1)), ids[:, 1:].reshape(-1))
         loss.backward()
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()

@@ -178,7 +178,11 @@ class GriffinModel(nn.Module):
         if tie_embeddings:
             self.lm_head.weight = self.embd.weight
 
-    def forward(self, token_ids: Tensor, segment_pos: Optional[Tensor] = None, *, token_mask: Optional[Tensor] = None) -> Tensor:
+    def forward(self, token_ids: Tensor, segment_pos: Optional[Tensor] = None, *, token_mask: Optional[Tensor] = None,
+                pad_vocab: bool = False) -> Tensor:
+        """Logits [B, T, vocab].  ``pad_vocab=True`` (not in the reference) returns them with the vocabulary axis
+        padded to a multiple of 8 and -inf in the padding, which a cross-entropy treats as absent classes; a
+        training loop that takes them this way skips the slice and its zero-filling backward."""
         if segment_pos is not None and segment_pos.shape != token_ids.shape:
             raise ValueError("segment_pos must have the same [batch, sequence] shape as token_ids")
         x = self.embd(token_ids) * self.embedding_scale
@@ -187,9 +191,9 @@ class GriffinModel(nn.Module):
             x = torch.where(token_mask[..., None], x, torch.zeros_like(x))
         for layer in self.layers:
             x = layer(x, segment_pos, active_mask=token_mask)
-        return self._logits(self.final_norm(x))
+        return self._logits(self.final_norm(x), pad_vocab)
 
-    def _logits(self, h: Tensor) -> Tensor:
+    def _logits(self, h: Tensor, keep_padding: bool = False) -> Tensor:
         """lm_head(h). On CUDA with half-precision autocast and a vocabulary that is not a multiple of 8, the
         weight is zero-padded to the next multiple while it is cast, so the GEMMs (forward and both backward
         ones) take the aligned tensor-core kernels; the extra columns are sliced off (a view, same values)."""
@@ -198,5 +202,12 @@ class GriffinModel(nn.Module):
         if pad and h.is_cuda and torch.is_autocast_enabled("cuda"):
             half = torch.get_autocast_dtype("cuda")
             wide = F.pad(weight.to(half), (0, 0, 0, pad))
+            if keep_padding:   # -inf through the GEMM's own bias epilogue
+                mask = torch.zeros(self.vocab_size + pad, device=h.device, dtype=half)
+                mask[self.vocab_size:] = float("-inf")
+                return F.linear(h.to(half), wide, mask)
             return F.linear(h.to(half), wide)[..., : self.vocab_size]
-        return F.linear(h, weight)
+        logits = F.linear(h, weight)
+        if keep_padding and pad:
+            logits = F.pad(logits, (0, pad), value=float("-inf"))
+        return logits

@@ -70,5 +70,17 @@ def test_padded_vocabulary_head_matches_plain_linear_gpu():
     (g_plain,) = torch.autograd.grad((plain.float() * dlogits).sum(), model.lm_head.weight)
     assert g_padded.shape == model.lm_head.weight.shape
     assert rel_l2(g_padded, g_plain) <= 4e-3
+    # padded form: same loss and the same weight gradient as the sliced form
+    targets = torch.randint(0, 1003, (4 * 48,), device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        wide = model._logits(h, keep_padding=True)
+        padded = model._logits(h)
+    assert wide.shape == (4, 48, 1008) and torch.isinf(wide[..., 1003:]).all()
+    ce = torch.nn.functional.cross_entropy
+    loss_wide, loss_plain = ce(wide.float().reshape(-1, 1008), targets), ce(padded.float().reshape(-1, 1003), targets)
+    torch.testing.assert_close(loss_wide, loss_plain, atol=1e-6, rtol=1e-6)
+    (gw,) = torch.autograd.grad(loss_wide, model.lm_head.weight)
+    (gp,) = torch.autograd.grad(loss_plain, model.lm_head.weight)
+    assert torch.isfinite(gw).all() and rel_l2(gw, gp) <= 1e-5
     exact = model._logits(h)                       # no autocast: the plain fp32 path
     assert exact.dtype == torch.float32 and rel_l2(padded.float(), exact) <= 2e-2
