@@ -494,49 +494,84 @@ __global__ void __launch_bounds__(256) decode_conv_kernel(const IO* __restrict__
   }
 }
 
+// One token of the RG-LRU for every batch row.  A thread owns VEC channels of DECODE_ROWS consecutive batch
+// rows: the per-channel rate c * logsigmoid(Lambda) is formed once per thread instead of once per element,
+// and the loads of all its rows are in flight before the first is used.
+constexpr int DECODE_ROWS = 2;
+
 template <typename IO, int VEC>
 __global__ void __launch_bounds__(256) decode_step_kernel(const IO* __restrict__ x, const IO* __restrict__ ur,
                                                           const IO* __restrict__ ui, const float* __restrict__ lambda,
                                                           float* __restrict__ h, const uint8_t* __restrict__ tok,
                                                           IO* __restrict__ y, int B, int D, float c) {
+  using V = Vec<IO, VEC>;
   const int nvec = D / VEC;
+  const int ngroup = (B + DECODE_ROWS - 1) / DECODE_ROWS;
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= static_cast<long long>(B) * nvec) return;
-  const int b = static_cast<int>(gid / nvec);
+  if (gid >= static_cast<long long>(ngroup) * nvec) return;
+  const int b0 = static_cast<int>(gid / nvec) * DECODE_ROWS;
   const int d = static_cast<int>(gid % nvec) * VEC;
-  const size_t at = static_cast<size_t>(b) * D + d;
-  const uint32_t f = tok ? tok[b] : 0u;
-  float xv[VEC], rv[VEC], iv[VEC], hv[VEC], yv[VEC];
-  Vec<IO, VEC>::load(x + at, xv);
-  Vec<IO, VEC>::load(ur + at, rv);
-  Vec<IO, VEC>::load(ui + at, iv);
+
+  typename V::Raw xr[DECODE_ROWS], rr[DECODE_ROWS], ir[DECODE_ROWS];
+  float hv[DECODE_ROWS][VEC];
+  uint32_t fl[DECODE_ROWS];
 #pragma unroll
-  for (int v = 0; v < VEC; v += 4) {
-    if (VEC == 1) { hv[0] = h[at]; }
-    else {
-      const float4 t4 = *reinterpret_cast<const float4*>(h + at + v);
-      hv[v] = t4.x; hv[(v + 1) % VEC] = t4.y; hv[(v + 2) % VEC] = t4.z; hv[(v + 3) % VEC] = t4.w;
+  for (int q = 0; q < DECODE_ROWS; ++q) {
+    const int b = b0 + q;
+    fl[q] = 0u;
+    if (b < B) {
+      const size_t at = static_cast<size_t>(b) * D + d;
+      xr[q] = V::load_raw(x + at);
+      rr[q] = V::load_raw(ur + at);
+      ir[q] = V::load_raw(ui + at);
+      if (tok) fl[q] = tok[b];
+      if constexpr (VEC == 1) {
+        hv[q][0] = h[at];
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; v += 4) {
+          const float4 t4 = *reinterpret_cast<const float4*>(h + at + v);
+          hv[q][v] = t4.x; hv[q][v + 1] = t4.y; hv[q][v + 2] = t4.z; hv[q][v + 3] = t4.w;
+        }
+      }
     }
   }
+  float rate[VEC];   // c * logsigmoid(Lambda) <= 0
 #pragma unroll
   for (int v = 0; v < VEC; ++v) {
     const float lam = lambda[d + v];
-    const float ls = lam >= 0.0f ? -log1pf(__expf(-lam)) : lam - log1pf(__expf(lam));
-    float r, i;
-    sigmoid_pair(rv[v], iv[v], r, i);
-    const float em = expm1_nonpos<false>(r * (c * ls));
-    float a = 1.0f + em;
-    float bdrive = sqrt_approx(fmaxf(-em * (2.0f + em), 0.0f)) * i * xv[v];
-    if (f & TOK_RESET) { a = 0.0f; bdrive = i * xv[v]; }
-    if (f & TOK_INACTIVE) { a = 1.0f; bdrive = 0.0f; }
-    hv[v] = fmaf(a, hv[v], bdrive);
-    yv[v] = hv[v];
+    rate[v] = c * (lam >= 0.0f ? -log1pf(__expf(-lam)) : lam - log1pf(__expf(lam)));
   }
-  Vec<IO, VEC>::store(y + at, yv);
 #pragma unroll
-  for (int v = 0; v < VEC; v += 4) {
-    if (VEC == 1) { h[at] = hv[0]; }
-    else *reinterpret_cast<float4*>(h + at + v) = make_float4(hv[v], hv[(v + 1) % VEC], hv[(v + 2) % VEC], hv[(v + 3) % VEC]);
+  for (int q = 0; q < DECODE_ROWS; ++q) {
+    const int b = b0 + q;
+    if (b >= B) break;
+    const size_t at = static_cast<size_t>(b) * D + d;
+    const uint32_t f = fl[q];
+    float xv[VEC], rv[VEC], iv[VEC], yv[VEC];
+    V::unpack(xr[q], xv);
+    V::unpack(rr[q], rv);
+    V::unpack(ir[q], iv);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float r, i;
+      sigmoid_pair(rv[v], iv[v], r, i);
+      const float em = expm1_nonpos<false>(r * rate[v]);
+      float a = 1.0f + em;
+      float bdrive = sqrt_approx(fmaxf(-em * (2.0f + em), 0.0f)) * i * xv[v];
+      if (f & TOK_RESET) { a = 0.0f; bdrive = i * xv[v]; }
+      if (f & TOK_INACTIVE) { a = 1.0f; bdrive = 0.0f; }
+      hv[q][v] = fmaf(a, hv[q][v], bdrive);
+      yv[v] = hv[q][v];
+    }
+    V::store(y + at, yv);
+    if constexpr (VEC == 1) {
+      h[at] = hv[q][0];
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; v += 4)
+        *reinterpret_cast<float4*>(h + at + v) = make_float4(hv[q][v], hv[q][v + 1], hv[q][v + 2], hv[q][v + 3]);
+    }
   }
 }
 
@@ -615,14 +650,14 @@ template <typename IO>
 static cudaError_t decode_step_t(const DecodeArgs& a, cudaStream_t s) {
   constexpr int V = vec_width<IO>();
   const int nvec = a.vector_ok ? a.D / V : a.D;
-  const long long total = static_cast<long long>(a.B) * nvec;
-  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  const long long total = static_cast<long long>((a.B + DECODE_ROWS - 1) / DECODE_ROWS) * nvec;
+  const unsigned blocks = static_cast<unsigned>((total + 127) / 128);   // small blocks: an even spread over the SMs
   const IO* x = static_cast<const IO*>(a.x);
   const IO* ur = static_cast<const IO*>(a.ur);
   const IO* ui = static_cast<const IO*>(a.ui);
   IO* y = static_cast<IO*>(a.y);
-  if (a.vector_ok) decode_step_kernel<IO, V><<<blocks, 256, 0, s>>>(x, ur, ui, a.lambda, a.h, a.tok, y, a.B, a.D, a.c);
-  else decode_step_kernel<IO, 1><<<blocks, 256, 0, s>>>(x, ur, ui, a.lambda, a.h, a.tok, y, a.B, a.D, a.c);
+  if (a.vector_ok) decode_step_kernel<IO, V><<<blocks, 128, 0, s>>>(x, ur, ui, a.lambda, a.h, a.tok, y, a.B, a.D, a.c);
+  else decode_step_kernel<IO, 1><<<blocks, 128, 0, s>>>(x, ur, ui, a.lambda, a.h, a.tok, y, a.B, a.D, a.c);
   return cudaGetLastError();
 }
 
