@@ -42,7 +42,7 @@ WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one rglru_bwd_kernel launch at config 1, from the
 # ncu capture summarised in profiles/ (None until a capture exists for the current kernel).
-BWD_DRAM_TRAFFIC_C1 = 195.28e6  # profiles/rglru_scan_config1_bf16.md (read 135.29 MB + write 59.99 MB)
+BWD_DRAM_TRAFFIC_C1 = 193.45e6  # profiles/rglru_scan_config1_bf16.md (read 135.30 MB + write 58.15 MB)
 
 
 def measured_peak() -> tuple[float, str]:
