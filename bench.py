@@ -567,7 +567,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["c2", "c3", "c4b"])
-    ap.add_argument("--fold", default="none", choices=["none", "conv", "merge"],
+    ap.add_argument("--fold", default="merge", choices=["none", "conv", "merge"],
                     help="c2/c3: run conv (and the GeLU-branch product) inside the scan kernels")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -30,8 +30,7 @@ class RMSNorm(nn.Module):
         self.g = nn.Parameter(torch.zeros(dim))
 
     def forward(self, x: Tensor) -> Tensor:
-        scale = torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + self.eps)
-        return x * scale * (1.0 + self.g)
+        return F.rms_norm(x, (x.size(-1),), weight=(1.0 + self.g).to(x.dtype), eps=self.eps)
 
 
 class GatedMLPBlock(nn.Module):
