@@ -88,6 +88,10 @@ static bool tma_shape_ok(int T, int D, size_t es) {
   return (pitch % 16 == 0) && (pitch * static_cast<unsigned long long>(T) < (1ull << 40));
 }
 
+// The TMA-staged conv kernels run one CTA per (batch row, 64-channel tile) over the whole sequence; they pay
+// once those pairs fill the 148 SMs, below that the kernels that also split the time axis are used.
+static bool conv_tma_pays(int B, int D) { return static_cast<long long>(B) * ((D + 63) / 64) >= 148; }
+
 static int check_dims(int B, int T, int D) {
   if (B <= 0 || T <= 0 || D <= 0) return RGLRU_ERR_BAD_SHAPE;
   if (B > 65535) return RGLRU_ERR_BAD_SHAPE;  // batch rows map to gridDim.y
@@ -582,11 +586,18 @@ int rglru_conv_fwd(const void* x_in, const float* conv_w, const float* conv_b, c
   int* status = nullptr;
   rc = device_setup(&status);
   if (rc != RGLRU_OK) return rc;
-  ConvArgs a;
+  ConvArgs a = {};
   a.x_in = x_in; a.w = conv_w; a.bias = conv_b; a.state = conv_state; a.tok = tok; a.out = x_conv;
   a.new_state = new_state; a.B = B; a.T = T; a.D = D;
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(x_in, 16) && aligned(x_conv, 16) &&
                 aligned(conv_state, 16) && aligned(conv_w, 16);
+  ConvMaps maps;
+  a.maps = nullptr;
+  a.status = status;
+  if (conv_tma_pays(B, D) && tma_shape_ok(T, D, es) && aligned(x_in, 16) && aligned(x_conv, 16) &&
+      make_map(&maps.in0, x_in, bf16, B, T, D, conv_tma_box_rows(), conv_tma_box_cols()) &&
+      make_map(&maps.out0, x_conv, bf16, B, T, D, conv_tma_box_rows() - 3, conv_tma_box_cols()))
+    a.maps = &maps;
   const cudaError_t e = launch_conv_fwd(bf16, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
@@ -612,12 +623,20 @@ int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, co
   int* status = nullptr;
   rc = device_setup(&status);
   if (rc != RGLRU_OK) return rc;
-  ConvBwdArgs a;
+  ConvBwdArgs a = {};
   a.d_conv = d_conv; a.x_in = x_in; a.w = conv_w; a.state = conv_state; a.tok = tok; a.dx_in = dx_in;
   a.d_w = d_w; a.d_b = d_b; a.d_state = d_state; a.part = static_cast<float*>(ws);
   a.B = B; a.T = T; a.D = D;
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(d_conv, 16) && aligned(x_in, 16) &&
                 aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16) && aligned(conv_w, 16);
+  ConvMaps maps;
+  a.maps = nullptr;
+  a.status = status;
+  if (conv_tma_pays(B, D) && tma_shape_ok(T, D, es) && aligned(d_conv, 16) && aligned(x_in, 16) && aligned(dx_in, 16) &&
+      make_map(&maps.in0, d_conv, bf16, B, T, D, conv_tma_box_rows(), conv_tma_box_cols()) &&
+      make_map(&maps.in1, x_in, bf16, B, T, D, conv_tma_box_rows(), conv_tma_box_cols()) &&
+      make_map(&maps.out0, dx_in, bf16, B, T, D, conv_tma_box_rows() - 3, conv_tma_box_cols()))
+    a.maps = &maps;
   const cudaError_t e = launch_conv_bwd(bf16, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
@@ -635,7 +654,7 @@ int rglru_decode_conv(const void* x_in, const float* conv_w, const float* conv_b
   int* status = nullptr;
   int rc = device_setup(&status);
   if (rc != RGLRU_OK) return rc;
-  ConvArgs a;
+  ConvArgs a = {};
   a.x_in = x_in; a.w = conv_w; a.bias = conv_b; a.state = nullptr; a.tok = tok; a.out = x_conv;
   a.new_state = conv_state; a.B = B; a.T = 1; a.D = D;
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(x_in, 16) && aligned(x_conv, 16) &&

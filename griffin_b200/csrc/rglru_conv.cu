@@ -589,9 +589,16 @@ static cudaError_t conv_fwd_t(const ConvArgs& a, cudaStream_t s) {
   const IO* xin = static_cast<const IO*>(a.x_in);
   const IO* st = static_cast<const IO*>(a.state);
   IO* out = static_cast<IO*>(a.out);
-  if (vec_ok) conv_fwd_kernel<IO, V, CONV_RUN><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.T, a.D);
-  else conv_fwd_kernel<IO, 1, CONV_RUN><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.T, a.D);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (a.maps) {   // enough (row, channel-tile) pairs to fill the machine: the TMA-staged kernel
+    ConvTmaArgs t = {};
+    t.w = a.w; t.bias = a.bias; t.state = a.state; t.tok = a.tok; t.B = a.B; t.T = a.T; t.D = a.D; t.status = a.status;
+    e = launch_conv_tma_fwd(sizeof(IO) == 2, *a.maps, t, s);
+  } else {
+    if (vec_ok) conv_fwd_kernel<IO, V, CONV_RUN><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.T, a.D);
+    else conv_fwd_kernel<IO, 1, CONV_RUN><<<blocks, 256, 0, s>>>(xin, a.w, a.bias, st, a.tok, out, a.B, a.T, a.D);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess || !a.new_state) return e;
   dim3 grid((a.D + 255) / 256, a.B);
   conv_state_kernel<IO><<<grid, 256, 0, s>>>(xin, st, a.tok, static_cast<IO*>(a.new_state), a.T, a.D);
@@ -616,11 +623,21 @@ static cudaError_t conv_bwd_t(const ConvBwdArgs& a, cudaStream_t s) {
   const IO* st = static_cast<const IO*>(a.state);
   IO* dx = static_cast<IO*>(a.dx_in);
   IO* ds = static_cast<IO*>(a.d_state);
-  if (vec_ok) conv_bwd_kernel<IO, V, CONV_RUN><<<grid, 256, 0, s>>>(dc, xin, a.w, st, a.tok, dx, ds, a.part, a.B, a.T, a.D);
-  else conv_bwd_kernel<IO, 1, CONV_RUN><<<grid, 256, 0, s>>>(dc, xin, a.w, st, a.tok, dx, ds, a.part, a.B, a.T, a.D);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  int part_rows = a.B * tblocks;
+  if (a.maps) {   // the TMA-staged kernel leaves one partial row per batch row
+    ConvTmaArgs t = {};
+    t.w = a.w; t.state = a.state; t.tok = a.tok; t.d_state = a.d_state; t.part = a.part;
+    t.B = a.B; t.T = a.T; t.D = a.D; t.status = a.status;
+    e = launch_conv_tma_bwd(sizeof(IO) == 2, *a.maps, t, s);
+    part_rows = a.B;
+  } else {
+    if (vec_ok) conv_bwd_kernel<IO, V, CONV_RUN><<<grid, 256, 0, s>>>(dc, xin, a.w, st, a.tok, dx, ds, a.part, a.B, a.T, a.D);
+    else conv_bwd_kernel<IO, 1, CONV_RUN><<<grid, 256, 0, s>>>(dc, xin, a.w, st, a.tok, dx, ds, a.part, a.B, a.T, a.D);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) return e;
-  conv_bwd_reduce_kernel<<<(5 * a.D + 255) / 256, 256, 0, s>>>(a.part, a.d_w, a.d_b, a.B * tblocks, a.D);
+  conv_bwd_reduce_kernel<<<(5 * a.D + 255) / 256, 256, 0, s>>>(a.part, a.d_w, a.d_b, part_rows, a.D);
   return cudaGetLastError();
 }
 

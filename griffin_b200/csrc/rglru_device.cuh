@@ -93,6 +93,11 @@ __device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ void bar_compute(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
+// Named barrier 2: compute warps and the producer warp together (nthreads counts all of them).
+__device__ __forceinline__ void bar_all(int nthreads) {
+  __syncwarp();
+  asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* dst, const void* map, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"

@@ -95,6 +95,22 @@ struct RawScanArgs {
   int* status;
 };
 
+// TMA-staged conv kernels: forward uses in0 = input (box of 67 rows), out0 = result; backward uses
+// in0 = upstream gradient (67 rows), in1 = input (67 rows), out0 = input gradient.
+struct ConvMaps {
+  CUtensorMap in0, in1, out0;
+};
+struct ConvTmaArgs {
+  const float* w;
+  const float* bias;
+  const void* state;     // [B, 3, D] history before t = 0 or nullptr
+  const uint8_t* tok;
+  void* d_state;         // backward only: gradient of the history, or nullptr
+  float* part;           // backward only: partial rows [B, 5, D]
+  int B, T, D;
+  int* status;
+};
+
 struct ConvArgs {
   const void* x_in;
   const float* w;
@@ -105,6 +121,8 @@ struct ConvArgs {
   void* new_state;  // decode: the in/out state
   int B, T, D;
   bool vector_ok;   // D and all pointers allow 16-byte accesses
+  const ConvMaps* maps;   // non-null: the shape is staged by TMA (see launch_conv_tma_fwd)
+  int* status;
 };
 struct ConvBwdArgs {
   const void* d_conv;
@@ -119,6 +137,8 @@ struct ConvBwdArgs {
   float* part;
   int B, T, D;
   bool vector_ok;
+  const ConvMaps* maps;   // non-null: the shape is staged by TMA (see launch_conv_tma_bwd)
+  int* status;
 };
 struct DecodeArgs {
   const void* x;
@@ -139,6 +159,10 @@ int raw_box_rows();
 cudaError_t launch_conv_fwd(bool bf16, const ConvArgs& a, cudaStream_t s);
 cudaError_t launch_conv_bwd(bool bf16, const ConvBwdArgs& a, cudaStream_t s);
 int conv_bwd_partial_rows(int B, int T);
+cudaError_t launch_conv_tma_fwd(bool bf16, const ConvMaps& maps, const ConvTmaArgs& a, cudaStream_t s);
+cudaError_t launch_conv_tma_bwd(bool bf16, const ConvMaps& maps, const ConvTmaArgs& a, cudaStream_t s);
+int conv_tma_box_rows();
+int conv_tma_box_cols();
 cudaError_t launch_decode_conv(bool bf16, const ConvArgs& a, cudaStream_t s);
 cudaError_t launch_decode_step(bool bf16, const DecodeArgs& a, cudaStream_t s);
 

@@ -79,7 +79,7 @@ int rglru_conv_bwd_noalloc(const void* d_conv, const void* x_in, const float* co
   // Nothing in the scratch has to start at zero: the backward kernel writes every partial-sum entry
   // that the reduction kernel of the same call then reads, so stale contents of an earlier call are
   // never observed.
-  ConvBwdArgs a;
+  ConvBwdArgs a = {};
   a.d_conv = d_conv; a.x_in = x_in; a.w = conv_w; a.state = conv_state; a.tok = tok; a.dx_in = dx_in;
   a.d_w = d_w; a.d_b = d_b; a.d_state = d_state; a.part = scratch;
   a.B = B; a.T = T; a.D = D;

@@ -1146,6 +1146,309 @@ __global__ void __launch_bounds__(RAW_NT) rawscan_bwd_kernel(const __grid_consta
 }
 
 // ======================================================================
+// The conv alone (griffin/griffin.py:474-487 of the reference), staged like the scan:
+// a CTA owns 64 channels of one batch row and walks the sequence in 64-step chunks
+// that a producer warp moves through shared memory with TMA; there is no cross-thread
+// dependence, so the only synchronisation is the mbarrier pipeline itself.
+// Used when B * ceil(D / 64) CTAs fill the machine; otherwise the per-run kernels of
+// rglru_conv.cu, which also split the time axis, are the better fit.
+// ======================================================================
+
+template <typename IO, int NSTAGE>
+struct ConvFwdSmem {
+  static constexpr int TS = 4, LANES = 16, CH = 64, TC = LANES * TS;
+  static constexpr int TILE = TC * CH * sizeof(IO);
+  static constexpr int HALO = 3 * CH * sizeof(IO);
+  static constexpr int TILEX = TILE + HALO;     // input rows t0-3 .. t0+TC-1
+  static constexpr int STAGE = TILEX + TILE;    // + the result tile
+  static constexpr int OFF_BAR = NSTAGE * STAGE;
+  static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
+};
+
+template <typename IO, int NSTAGE>
+__global__ void __launch_bounds__(288) conv_tma_fwd_kernel(const __grid_constant__ ConvMaps maps, const ConvTmaArgs p) {
+  using SM = ConvFwdSmem<IO, NSTAGE>;
+  constexpr int TS = SM::TS, CH = SM::CH, TC = SM::TC, NCV = CH / CV, NCOMP = SM::LANES * NCV;
+  constexpr int ROWB = CH * sizeof(IO);
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+  uint64_t* ready = full + NSTAGE;
+  volatile int* dead = reinterpret_cast<volatile int*>(ready + NSTAGE);
+  const int tid = threadIdx.x, lane_t = tid / NCV, vec = tid % NCV;
+  const int b = blockIdx.y, d0 = blockIdx.x * CH;
+  const int nchunks = (p.T + TC - 1) / TC;
+
+  if (tid == 0) {
+    *dead = 0;
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (tid >= NCOMP) {
+    if (tid == NCOMP) {
+      prefetch_map(&maps.in0); prefetch_map(&maps.out0);
+      auto issue = [&](int k) {
+        const int sidx = k % NSTAGE;
+        mbar_expect_tx(&full[sidx], SM::TILEX);
+        tma_load_3d(smem + sidx * SM::STAGE, &maps.in0, d0, k * TC - 3, b, &full[sidx]);   // rows before t = 0 read as zero
+      };
+      for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
+      for (int k = 0; k < nchunks; ++k) {
+        const int sidx = k % NSTAGE;
+        mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
+        tma_store_3d(&maps.out0, smem + sidx * SM::STAGE + SM::TILEX, d0, k * TC, b);
+        tma_commit();
+        if (k + NSTAGE < nchunks) {
+          tma_wait_read<0>();
+          issue(k + NSTAGE);
+        }
+      }
+      tma_wait_all<0>();
+    }
+    return;
+  }
+
+  ConvTaps ct;
+  load_taps(p.w, p.bias, d0 + vec * CV, p.D, ct);
+  const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
+
+  for (int k = 0; k < nchunks; ++k) {
+    const int stage = k % NSTAGE;
+    uint8_t* tiles = smem + stage * SM::STAGE;
+    const int t0 = k * TC;
+    uint32_t fl[1];
+    const bool masked = (p.tok != nullptr) || (t0 + TC > p.T);
+    if (masked) load_flags<TS>(p.tok, b, p.T, t0 + lane_t * TS, fl);
+    float2 hist_v[3][2];
+    const float2 (*hist)[2] = nullptr;
+    if (k == 0 && lane_t == 0 && p.state) {
+      load_hist<IO>(p.state, b, d0 + vec * CV, p.D, hist_v);
+      hist = hist_v;
+    }
+    mbar_wait_or_flag(&full[stage], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
+    float2 xc[TS][2];
+    if (masked) conv_front<IO, TS, CH, true>(tiles, off0, ct, fl, hist, xc);
+    else conv_front<IO, TS, CH, false>(tiles, off0, ct, fl, hist, xc);
+    uint8_t* to = tiles + SM::TILEX;
+#pragma unroll
+    for (int st = 0; st < TS; ++st) {
+      if (masked && ((fl[0] >> (8 * st)) & TOK_INACTIVE)) { xc[st][0] = f2(0.0f); xc[st][1] = f2(0.0f); }   // padding emits zero
+      Pack<IO>::store2(to + off0 + st * ROWB, xc[st]);
+    }
+    fence_async_smem();
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(&ready[stage]);
+  }
+}
+
+// The TS steps of one thread in the conv backward.  Two sliding four-row windows: ga = upstream gradient of
+// tokens (step .. step+3), xa = input at times (step-3 .. step); each step loads one new row of each.
+// `fb` holds the flag bytes of the TS + 3 tokens whose gradient is read; `dstate` (first lane of the first
+// chunk only) receives the gradient of the carried history, whose rows only tokens 0 .. 2 reach.
+template <typename IO, int TS, int CH, bool MASKED>
+__device__ __forceinline__ void conv_bwd_steps(const uint8_t* tg, const uint8_t* tx, uint8_t* tdx, int off0,
+                                               const ConvTaps& ct, const uint32_t (&fb)[TS + 3], const float2 (*hist)[2],
+                                               IO* dstate, int D, int channels_left, float2 (&gw)[5][2]) {
+  constexpr int ROWB = CH * sizeof(IO);
+  auto grad_row = [&](int j, float2 (&v)[2]) {
+    Pack<IO>::unpack2(Pack<IO>::load(tg + off0 + j * ROWB), v);
+    if (MASKED && (fb[j] & TOK_INACTIVE)) { v[0] = f2(0.0f); v[1] = f2(0.0f); }
+  };
+  auto reach_of = [&](int j) { return MASKED ? 3 - static_cast<int>(fb[j] & TOK_CUT_MASK) : 3; };
+  float2 ga[4][2], xa[4][2];
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    grad_row(j, ga[j]);
+    Pack<IO>::unpack2(Pack<IO>::load(tx + off0 + j * ROWB), xa[j]);
+    if (hist) { xa[j][0] = hist[j][0]; xa[j][1] = hist[j][1]; }
+  }
+  if (dstate) {
+#pragma unroll
+    for (int slot = 0; slot < 3; ++slot) {
+      float2 acc[2] = {f2(0.0f), f2(0.0f)};
+#pragma unroll
+      for (int u = 0; u <= slot; ++u) {               // token u reads time slot-3 with lag u + 3 - slot
+        const int lag = u + 3 - slot;
+        const float m = reach_of(u) >= lag ? 1.0f : 0.0f;
+#pragma unroll
+        for (int cp = 0; cp < 2; ++cp) acc[cp] = fma2(mul2(ct.w[3 - lag][cp], f2(m)), ga[u][cp], acc[cp]);
+      }
+      const float v4[4] = {acc[0].x, acc[0].y, acc[1].x, acc[1].y};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch)
+        if (ch < channels_left) dstate[static_cast<size_t>(slot) * D + ch] = Pack<IO>::from_float(v4[ch]);
+    }
+  }
+#pragma unroll
+  for (int st = 0; st < TS; ++st) {
+    grad_row(st + 3, ga[3]);
+    Pack<IO>::unpack2(Pack<IO>::load(tx + off0 + (st + 3) * ROWB), xa[3]);   // input at the step's own time
+    float2 dx[2];
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {
+      if (MASKED) {
+        float2 a = mul2(ct.w[3][cp], ga[0][cp]);
+        a = fma2(mul2(ct.w[2][cp], f2(reach_of(st + 1) >= 1 ? 1.0f : 0.0f)), ga[1][cp], a);
+        a = fma2(mul2(ct.w[1][cp], f2(reach_of(st + 2) >= 2 ? 1.0f : 0.0f)), ga[2][cp], a);
+        dx[cp] = fma2(mul2(ct.w[0][cp], f2(reach_of(st + 3) >= 3 ? 1.0f : 0.0f)), ga[3][cp], a);
+      } else {
+        float2 a = mul2(ct.w[3][cp], ga[0][cp]);
+        a = fma2(ct.w[2][cp], ga[1][cp], a);
+        a = fma2(ct.w[1][cp], ga[2][cp], a);
+        dx[cp] = fma2(ct.w[0][cp], ga[3][cp], a);
+      }
+    }
+    Pack<IO>::store2(tdx + off0 + st * ROWB, dx);
+    // tap gradients of the step's own token (its flag decides how far back it reaches)
+    const int reach = reach_of(st);
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {
+      const float2 g0 = ga[0][cp];
+      gw[4][cp] = add2(gw[4][cp], g0);
+      gw[3][cp] = fma2(g0, xa[3][cp], gw[3][cp]);
+      if (MASKED) {
+        gw[2][cp] = fma2(mul2(g0, f2(reach >= 1 ? 1.0f : 0.0f)), xa[2][cp], gw[2][cp]);
+        gw[1][cp] = fma2(mul2(g0, f2(reach >= 2 ? 1.0f : 0.0f)), xa[1][cp], gw[1][cp]);
+        gw[0][cp] = fma2(mul2(g0, f2(reach >= 3 ? 1.0f : 0.0f)), xa[0][cp], gw[0][cp]);
+      } else {
+        gw[2][cp] = fma2(g0, xa[2][cp], gw[2][cp]);
+        gw[1][cp] = fma2(g0, xa[1][cp], gw[1][cp]);
+        gw[0][cp] = fma2(g0, xa[0][cp], gw[0][cp]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      ga[j][0] = ga[j + 1][0]; ga[j][1] = ga[j + 1][1];
+      xa[j][0] = xa[j + 1][0]; xa[j][1] = xa[j + 1][1];
+    }
+  }
+}
+
+// Backward of the conv.  Per chunk: the upstream gradient rows t0 .. t0+TC+2 (three rows of look-ahead, zero
+// past T), the input rows t0-3 .. t0+TC-1, and the result tile.
+//   dx[t]     = sum_lag w[3-lag] g[t+lag] [token t+lag reaches back lag steps]
+//   dw[3-lag] += g[t] x[t-lag] [token t reaches back lag steps],   db += g[t]
+// with g zero on padding.  The tap gradients stay in registers over the whole sequence and are folded
+// across the CTA's time-lanes in a fixed order at the end: one partial row [5, D] per batch row.
+template <typename IO, int NSTAGE>
+struct ConvBwdSmem {
+  static constexpr int TS = 4, LANES = 16, CH = 64, TC = LANES * TS;
+  static constexpr int TILE = TC * CH * sizeof(IO);
+  static constexpr int HALO = 3 * CH * sizeof(IO);
+  static constexpr int TILEX = TILE + HALO;
+  static constexpr int OFF_X = TILEX, OFF_DX = 2 * TILEX;
+  static constexpr int STAGE = 2 * TILEX + TILE;
+  static constexpr int OFF_BAR = NSTAGE * STAGE;
+  static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
+  static_assert(NSTAGE * STAGE >= LANES * 5 * CH * 4, "the final fold reuses the stage memory");
+};
+
+template <typename IO, int NSTAGE>
+__global__ void __maxnreg__(96) conv_tma_bwd_kernel(const __grid_constant__ ConvMaps maps, const ConvTmaArgs p) {
+  using SM = ConvBwdSmem<IO, NSTAGE>;
+  constexpr int TS = SM::TS, CH = SM::CH, TC = SM::TC, NCV = CH / CV, NCOMP = SM::LANES * NCV, LANES = SM::LANES;
+  constexpr int ROWB = CH * sizeof(IO);
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
+  uint64_t* ready = full + NSTAGE;
+  volatile int* dead = reinterpret_cast<volatile int*>(ready + NSTAGE);
+  const int tid = threadIdx.x, lane_t = tid / NCV, vec = tid % NCV;
+  const int b = blockIdx.y, d0 = blockIdx.x * CH;
+  const int nchunks = (p.T + TC - 1) / TC;
+
+  if (tid == 0) {
+    *dead = 0;
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (tid >= NCOMP) {
+    if (tid == NCOMP) {
+      prefetch_map(&maps.in0); prefetch_map(&maps.in1); prefetch_map(&maps.out0);
+      auto issue = [&](int k) {
+        const int sidx = k % NSTAGE;
+        uint8_t* st = smem + sidx * SM::STAGE;
+        mbar_expect_tx(&full[sidx], 2 * SM::TILEX);
+        tma_load_3d(st, &maps.in0, d0, k * TC, b, &full[sidx]);                   // gradient, rows past T read as zero
+        tma_load_3d(st + SM::OFF_X, &maps.in1, d0, k * TC - 3, b, &full[sidx]);   // input, rows before 0 read as zero
+      };
+      for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
+      for (int k = 0; k < nchunks; ++k) {
+        const int sidx = k % NSTAGE;
+        mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
+        tma_store_3d(&maps.out0, smem + sidx * SM::STAGE + SM::OFF_DX, d0, k * TC, b);
+        tma_commit();
+        if (k + NSTAGE < nchunks) {
+          tma_wait_read<0>();
+          issue(k + NSTAGE);
+        }
+      }
+      tma_wait_all<0>();
+    }
+    bar_all(NCOMP + 32);   // the final fold below reuses stage memory: every bulk store has left it
+    return;
+  }
+
+  ConvTaps ct;
+  load_taps(p.w, nullptr, d0 + vec * CV, p.D, ct);
+  float2 gw[5][2];
+#pragma unroll
+  for (int q = 0; q < 5; ++q) { gw[q][0] = f2(0.0f); gw[q][1] = f2(0.0f); }
+  const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
+
+  for (int k = 0; k < nchunks; ++k) {
+    const int stage = k % NSTAGE;
+    uint8_t* tiles = smem + stage * SM::STAGE;
+    const int t0 = k * TC;
+    // flag bytes of the TS + 3 tokens whose gradient this thread reads (steps at or past T count as padding)
+    uint32_t fb[TS + 3];
+    const bool masked = (p.tok != nullptr) || (t0 + TC + 3 > p.T);
+#pragma unroll
+    for (int j = 0; j < TS + 3; ++j) {
+      fb[j] = 0u;
+      if (masked) {
+        const int t = t0 + lane_t * TS + j;
+        fb[j] = t < p.T ? (p.tok ? p.tok[static_cast<size_t>(b) * p.T + t] : 0u) : TOK_INACTIVE;
+      }
+    }
+    float2 hist_v[3][2];
+    const bool use_hist = (k == 0 && lane_t == 0 && p.state != nullptr);
+    if (use_hist) load_hist<IO>(p.state, b, d0 + vec * CV, p.D, hist_v);
+    mbar_wait_or_flag(&full[stage], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
+
+    IO* dstate = nullptr;
+    if (k == 0 && lane_t == 0 && p.d_state)
+      dstate = static_cast<IO*>(p.d_state) + static_cast<size_t>(b) * 3 * p.D + d0 + vec * CV;
+    const float2 (*hist)[2] = use_hist ? hist_v : nullptr;
+    if (masked) conv_bwd_steps<IO, TS, CH, true>(tiles, tiles + SM::OFF_X, tiles + SM::OFF_DX, off0, ct, fb, hist, dstate,
+                                                 p.D, p.D - (d0 + vec * CV), gw);
+    else conv_bwd_steps<IO, TS, CH, false>(tiles, tiles + SM::OFF_X, tiles + SM::OFF_DX, off0, ct, fb, hist, dstate,
+                                           p.D, p.D - (d0 + vec * CV), gw);
+    fence_async_smem();
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(&ready[stage]);
+  }
+
+  // Fold the time-lanes in index order; the stage memory is free once the producer has drained its stores.
+  bar_all(NCOMP + 32);
+  float* red = reinterpret_cast<float*>(smem);          // [LANES][5][CH]
+#pragma unroll
+  for (int q = 0; q < 5; ++q)
+    *reinterpret_cast<float4*>(red + (lane_t * 5 + q) * CH + vec * CV) = make_float4(gw[q][0].x, gw[q][0].y, gw[q][1].x, gw[q][1].y);
+  bar_compute(NCOMP);
+  for (int idx = tid; idx < 5 * CH; idx += NCOMP) {
+    const int q = idx / CH, cc = idx % CH;
+    if (d0 + cc >= p.D) continue;
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < LANES; ++j) acc += red[(j * 5 + q) * CH + cc];
+    p.part[(static_cast<size_t>(b) * 5 + q) * p.D + d0 + cc] = acc;
+  }
+}
+
+// ======================================================================
 // Launchers
 // ======================================================================
 
@@ -1370,6 +1673,37 @@ static cudaError_t launch_raw_bwd_t(const RawBwdMaps& maps, const RawScanArgs& a
 }
 cudaError_t launch_raw_bwd(bool use_tma, const RawBwdMaps& maps, const RawScanArgs& a, cudaStream_t s) {
   return use_tma ? launch_raw_bwd_t<3, true>(maps, a, s) : launch_raw_bwd_t<1, false>(maps, a, s);
+}
+
+int conv_tma_box_rows() { return 64 + 3; }
+int conv_tma_box_cols() { return 64; }
+
+template <typename IO>
+static cudaError_t conv_tma_fwd_t(const ConvMaps& maps, const ConvTmaArgs& a, cudaStream_t s) {
+  constexpr int ST = sizeof(IO) == 2 ? 4 : 3;
+  auto kern = conv_tma_fwd_kernel<IO, ST>;
+  constexpr int bytes = ConvFwdSmem<IO, ST>::BYTES;
+  cudaError_t e = set_smem(kern, bytes);
+  if (e != cudaSuccess) return e;
+  kern<<<dim3((a.D + 63) / 64, a.B), 288, bytes, s>>>(maps, a);
+  return cudaGetLastError();
+}
+cudaError_t launch_conv_tma_fwd(bool bf16, const ConvMaps& maps, const ConvTmaArgs& a, cudaStream_t s) {
+  return bf16 ? conv_tma_fwd_t<__nv_bfloat16>(maps, a, s) : conv_tma_fwd_t<float>(maps, a, s);
+}
+template <typename IO>
+static cudaError_t conv_tma_bwd_t(const ConvMaps& maps, const ConvTmaArgs& a, cudaStream_t s) {
+  constexpr int ST = sizeof(IO) == 2 ? 4 : 2;   // about 100 KB either way: two CTAs per SM
+  auto kern = conv_tma_bwd_kernel<IO, ST>;
+  constexpr int bytes = ConvBwdSmem<IO, ST>::BYTES;
+  static_assert(bytes <= 232448, "shared memory of one CTA");
+  cudaError_t e = set_smem(kern, bytes);
+  if (e != cudaSuccess) return e;
+  kern<<<dim3((a.D + 63) / 64, a.B), 288, bytes, s>>>(maps, a);
+  return cudaGetLastError();
+}
+cudaError_t launch_conv_tma_bwd(bool bf16, const ConvMaps& maps, const ConvTmaArgs& a, cudaStream_t s) {
+  return bf16 ? conv_tma_bwd_t<__nv_bfloat16>(maps, a, s) : conv_tma_bwd_t<float>(maps, a, s);
 }
 
 }  // namespace rglru

@@ -151,7 +151,8 @@ def test_block_forward_backward_all_gradients():
         assert orc.rel_l2(p.grad, case["g." + key]) <= FP32_REL, key
 
 
-@pytest.mark.parametrize("shape", [(2, 70, 64), (3, 37, 20), (1, 300, 136), (2, 5, 7)])
+# the last two shapes have enough (row, channel tile) pairs for the TMA-staged conv kernels
+@pytest.mark.parametrize("shape", [(2, 70, 64), (3, 37, 20), (1, 300, 136), (2, 5, 7), (10, 70, 960), (19, 133, 520)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_conv_forward_backward_against_oracle(shape, dtype):
     """Conv alone with a carried state, document boundaries, and gradients incl. the state's."""
@@ -212,6 +213,48 @@ def test_block_bf16_against_fp32_oracle():
     assert orc.rel_l2(xg.grad, xr.grad) <= BF16_REL
     for key, p in blk.named_parameters():
         assert orc.rel_l2(p.grad, params[key].grad) <= 3e-2, key
+
+
+@pytest.mark.parametrize("fold_merge", [False, True])
+def test_wide_batch_block_with_padding_and_cache_against_oracle(fold_merge):
+    """A batch wide enough for the TMA-staged conv kernels: right padding, ragged padding in one row, a carried
+    cache into a second chunk, and all gradients, against the oracle block (griffin/griffin.py:439-529)."""
+    from griffin_b200 import RecurrentBlock
+    torch.manual_seed(21)
+    B, T, DM, DR = 20, 70, 32, 512
+    blk = RecurrentBlock(DM, DR, gate_blocks=8, scan_mode="cuda", fold_merge=fold_merge)
+    with torch.no_grad():
+        blk.temporal_conv.weight.normal_(0.0, 0.5)
+        blk.temporal_conv.bias.normal_(0.0, 0.1)
+    params = {k: v.detach().clone().requires_grad_(True) for k, v in blk.state_dict().items()}
+    x, x2 = torch.randn(B, T, DM), torch.randn(B, 9, DM)
+    dout = torch.randn(B, T, DM)
+    active = torch.ones(B, T, dtype=torch.bool)
+    for r in range(B):
+        active[r, T - 3 * r:] = False if r else True        # row r ends 3 r tokens early (row 0 is full)
+    active[5, 10:14] = False                                  # a hole: not right padding
+    active2 = torch.ones(B, 9, dtype=torch.bool)
+    active2[3, 6:] = False
+    xr = x.clone().requires_grad_(True)
+    ref, c1 = orc.recurrent_block(xr, params, active=active)
+    (ref * dout).sum().backward()
+    with torch.no_grad():
+        ref2, c2 = orc.recurrent_block(x2, params, c1, active=active2)
+
+    blk = blk.to(DEV)
+    xg = x.to(DEV).requires_grad_(True)
+    out, g1 = blk(xg, active_mask=active.to(DEV), return_cache=True)
+    (out * dout.to(DEV)).sum().backward()
+    with torch.no_grad():
+        out2, g2 = blk(x2.to(DEV), g1, active_mask=active2.to(DEV), return_cache=True)
+    assert orc.rel_l2(out, ref) <= FP32_REL and orc.rel_l2(out2, ref2) <= FP32_REL
+    assert orc.rel_l2(xg.grad, xr.grad) <= FP32_REL
+    for key, p in blk.named_parameters():
+        assert orc.rel_l2(p.grad, params[key].grad) <= 2e-5, key
+    for got, want in ((g1, c1), (g2, c2)):
+        assert orc.rel_l2(got.rnn_state, want.rnn_state) <= FP32_REL
+        assert orc.rel_l2(got.conv_state, want.conv_state) <= FP32_REL
+        assert torch.equal(got.segment_position.cpu(), want.segment_position)
 
 
 # ---------------------------------------------------------------- conv folded into the scan's load stage
