@@ -405,11 +405,15 @@ def run_block(args) -> dict:
     xs = [torch.randn(B, T, DM, device=dev).to(torch.bfloat16).requires_grad_(True) for _ in range(3)]
     dout = torch.randn(B, T, DM, device=dev).to(torch.bfloat16)
     sampler = ClockSampler(dev.index or 0)
+    module = blk
+    if args.graph:   # forward and backward of the block replayed as two CUDA graphs (the step is launch-bound otherwise)
+        blk = torch.cuda.make_graphed_callables(module, (xs[0],))
 
     def step(i):
         x = xs[i % 3]
         x.grad = None
-        blk.zero_grad(set_to_none=True)
+        if not args.graph:
+            module.zero_grad(set_to_none=True)
         blk(x).backward(dout)
 
     sampler.start()
@@ -422,7 +426,8 @@ def run_block(args) -> dict:
         with torch.no_grad():
             x.copy_(host_x, non_blocking=True)
         x.grad = None
-        blk.zero_grad(set_to_none=True)
+        if not args.graph:
+            module.zero_grad(set_to_none=True)
         out = blk(x)
         out.backward(dout)
         host_loss.copy_(out.float().square().mean().reshape(1), non_blocking=True)
@@ -435,7 +440,7 @@ def run_block(args) -> dict:
            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 I/O, f32 state", "data": "synthetic",
            "config": {"workload": f"c2: RecurrentBlock fwd+bwd bf16 B={B}/GPU T={T} {DM}->{DR}->{DM}, conv k=4, 16 gate heads",
-                      "fold": args.fold,
+                      "fold": args.fold, "cuda_graph": bool(args.graph),
                       "l2": "three rotating inputs; 0.6 GB of activations per step"},
            "scan_conv_algorithmic_gbs": world * (22 + 10) * n / ms / 1e6,
            "e2e": {"value": world * n / e2e_ms * 1e3, "unit": "token-channels/s", "h2d_bytes_per_step": 2 * B * T * DM,
@@ -569,6 +574,7 @@ def main() -> None:
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["c2", "c3", "c4b"])
     ap.add_argument("--fold", default="merge", choices=["none", "conv", "merge"],
                     help="c2/c3: run conv (and the GeLU-branch product) inside the scan kernels")
+    ap.add_argument("--graph", action="store_true", help="c2: replay the block's forward and backward as CUDA graphs")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-kernel-timing", action="store_true", help="skip the per-kernel event pass (for profiler runs)")

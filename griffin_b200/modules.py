@@ -101,6 +101,28 @@ def token_flags(batch: int, steps: int, device, *, reset: Optional[Tensor] = Non
     return flags
 
 
+_PLAIN_FLAGS: dict = {}
+
+
+def _plain_flags(batch: int, steps: int, device) -> Tensor:
+    """Flag bytes of rows that are one fresh document each (positions 0..T-1): a reset at token 0 and the first
+    three tokens short of taps.  Built once per (batch, steps, device) with device-side fills only (no host
+    copy, so the block can be captured into a CUDA graph) and shared read-only between calls."""
+    key = (batch, steps, str(device))
+    flags = _PLAIN_FLAGS.get(key)
+    if flags is None:
+        flags = torch.zeros(batch, steps, device=device, dtype=torch.uint8)
+        flags[:, 0] = 3 | _lib.TOK_RESET
+        if steps > 1:
+            flags[:, 1] = 2
+        if steps > 2:
+            flags[:, 2] = 1
+        if len(_PLAIN_FLAGS) > 64:
+            _PLAIN_FLAGS.clear()
+        _PLAIN_FLAGS[key] = flags
+    return flags
+
+
 class RG_LRU(nn.Module):
     """Real-gated linear recurrent unit on the CUDA kernels (reference: griffin/griffin.py:157-306)."""
 
@@ -281,10 +303,7 @@ class RecurrentBlock(nn.Module):
 
         if plain:
             # contiguous positions 0..T-1: only the first three tokens lose taps, token 0 is a reset
-            flags = torch.zeros(batch, steps, device=x.device, dtype=torch.uint8)
-            head = min(3, steps)
-            flags[:, :head] = torch.tensor([3, 2, 1][:head], device=x.device, dtype=torch.uint8)
-            flags[:, 0] |= _lib.TOK_RESET
+            flags = _plain_flags(batch, steps, x.device)
         else:
             padded = None if kernel_active is None else ~kernel_active.all()
             flags = token_flags(batch, steps, x.device, reset=kernel_pos == 0, active=kernel_active,
