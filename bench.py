@@ -276,7 +276,7 @@ def run_ours(args) -> dict:
                      "algorithmic_bytes": bytes_bwd,
                      "fwd": {"achieved": bytes_fwd / fwd_ms / 1e6, "frac": bytes_fwd / fwd_ms / 1e6 / peak}},
         "e2e": e2e,
-        "gpu_launches": 3 * args.steps,
+        "gpu_launches": (2 if B <= 64 else 3) * args.steps,   # fwd + bwd (+ the dLambda fold kernel for B > 64)
         "clocks": clocks,
         "device_status": status,
     }
@@ -508,7 +508,7 @@ def run_lm(args) -> dict:
                       "fold": args.fold, "l2": "activations of one step far exceed L2"},
            "e2e": {"value": world * B * T / e2e_ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B * (T + 1),
                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
-           "gpu_launches": 8 * 9 * args.steps, "clocks": clocks, "device_status": _lib.device_status(),
+           "gpu_launches": 8 * 6 * args.steps,   # per recurrent layer: conv fwd + state, scan fwd, scan bwd, conv bwd + fold "clocks": clocks, "device_status": _lib.device_status(),
            "roofline": {"bound": "tensor", "note": "whole-model step: torch GEMMs and attention dominate; the library's kernels "
                         "are the conv, the RG-LRU scan and their backwards in 8 of 12 layers", "achieved": None, "peak": None,
                         "frac": None, "traffic": None, "unit": "TFLOP/s"}}
