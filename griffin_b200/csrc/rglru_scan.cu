@@ -228,11 +228,11 @@ __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, 
       float2 r, i;
       if (GROUPED) sigmoid_pair2_biased<sizeof(IO) == 2>(rv[cp], iv[cp], gb.r[cp], gb.i[cp], r, i);
       else sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
-      const float2 e = one_minus_exp_neg2<POLY>(mul2(r, K[cp]));   // 1 - a
+      const float2 e = one_minus_exp_neg2<POLY, sizeof(IO) == 2>(mul2(r, K[cp]));   // 1 - a
       float2 a = fma2(e, f2(-1.0f), f2(1.0f));
       const float2 gsq = mul2(e, fma2(e, f2(-1.0f), f2(2.0f)));     // 1 - a^2
-      // sqrt(gsq) as gsq * rsqrt(gsq): one MUFU operation; the floor keeps rsqrt finite (gamma error <= 1e-15)
-      const float2 gq = make_float2(fmaxf(gsq.x, 1e-30f), fmaxf(gsq.y, 1e-30f));
+      // sqrt(gsq) as gsq * rsqrt(gsq): one MUFU operation; the offset keeps rsqrt finite (gamma error <= 1e-15)
+      const float2 gq = add2(gsq, f2(1e-30f));
       float2 gam = mul2(gq, make_float2(rsqrt_approx(gq.x), rsqrt_approx(gq.y)));
       if (MASKED) {
         a = fma2(mul2(a, f2(m.keep)), f2(m.live), f2(1.0f - m.live));
@@ -507,18 +507,18 @@ __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8
       float2 r, i;
       if (GROUPED) sigmoid_pair2_biased<sizeof(IO) == 2>(rv[cp], iv[cp], gb.r[cp], gb.i[cp], r, i);
       else sigmoid_pair2<sizeof(IO) == 2>(rv[cp], iv[cp], r, i);
-      const float2 e = one_minus_exp_neg2<POLY>(mul2(r, K[cp]));       // 1 - a
+      const float2 e = one_minus_exp_neg2<POLY, sizeof(IO) == 2>(mul2(r, K[cp]));       // 1 - a
       const float2 a = fma2(e, f2(-1.0f), f2(1.0f));
       float2 gsq = mul2(e, fma2(e, f2(-1.0f), f2(2.0f)));               // 1 - a^2
-      // The floor keeps rsqrt finite; it changes gamma by at most 1e-15.
-      gsq = make_float2(fmaxf(gsq.x, 1e-30f), fmaxf(gsq.y, 1e-30f));
+      // The offset keeps rsqrt finite; it changes gamma by at most 1e-15.
+      gsq = add2(gsq, f2(1e-30f));
       const float2 rs = make_float2(rsqrt_approx(gsq.x), rsqrt_approx(gsq.y));
       float2 gam = mul2(gsq, rs);                                       // sqrt(gsq)
-      // 2 * slope, slope = 1 / sqrt(max(4 gsq, 1e-6)) = min(rs / 2, 1000)
-      const float2 rs2 = make_float2(fminf(rs.x, 2.0f * SLOPE_CAP), fminf(rs.y, 2.0f * SLOPE_CAP));
+      // -2 * slope, slope = 1 / sqrt(max(4 gsq, 1e-6)) = min(rs / 2, 1000); the sign rides on the min for free
+      const float2 nrs2 = make_float2(-fminf(rs.x, 2.0f * SLOPE_CAP), -fminf(rs.y, 2.0f * SLOPE_CAP));
       const float2 ix = mul2(i, xv[cp]);
       float2 am = a, ar = a;
-      float2 c3 = mul2(mul2(a, a), mul2(rs2, mul2(ix, f2(-1.0f))));   // stored negated
+      float2 c3 = mul2(mul2(a, a), mul2(nrs2, ix));   // stored negated
       if (MASKED) {
         const float kl = m.keep * m.live;
         am = fma2(mul2(a, f2(m.keep)), f2(m.live), f2(1.0f - m.live));
