@@ -29,6 +29,7 @@ SIGNATURES = {
     "rglru_last_cuda_error": (ctypes.c_char_p, []),
     "rglru_abi_version": (_i, []),
     "rglru_device_status": (_i, [ctypes.POINTER(_i)]),
+    "rglru_selftest_wait_timeout": (_i, [ctypes.c_uint, _vp, _vp]),
     "rglru_chunk_steps": (_i, [_i]),
     "rglru_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "rglru_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _f, _i, _vp]),

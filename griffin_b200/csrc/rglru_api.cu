@@ -142,6 +142,17 @@ int rglru_device_status(int* detail) {
   return RGLRU_OK;
 }
 
+int rglru_selftest_wait_timeout(unsigned limit_us, int* finished, void* stream) {
+  if (limit_us == 0 || limit_us > 100000u) return RGLRU_ERR_BAD_SHAPE;   // at most a tenth of a second
+  if (!aligned(finished, 4)) return RGLRU_ERR_MISALIGNED;
+  int* status = nullptr;
+  const int rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  const long long cycles = static_cast<long long>(limit_us) * 2000;         // SM clock is about 2 GHz
+  const cudaError_t e = launch_wait_selftest(status, finished, cycles, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
 int rglru_chunk_steps(int io_dtype) {
   (void)io_dtype;
   return SAVE_EVERY;

@@ -27,6 +27,8 @@ constexpr float POLY_RANGE = -0.25f;
 // Codes written to the device status word.
 constexpr int DEV_TIMEOUT_LOAD = 1;   // a tile load never completed
 constexpr int DEV_TIMEOUT_STORE = 2;  // the producer never saw a chunk's results
+constexpr int DEV_TIMEOUT_SELFTEST = 3;  // the wait self-test (a barrier nothing completes) gave up, as it must
+constexpr long long DEV_WAIT_CYCLES = 4000000000LL;   // about two seconds of SM clock
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -74,7 +76,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // executing the same barriers and the kernel runs to its end (producing garbage) with
 // the device status word set, instead of hanging or leaving barriers unmatched.
 __device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity, volatile int* dead, int* status,
-                                                  int code) {
+                                                  int code, long long limit = DEV_WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return;
   const long long start = clock64();
   for (;;) {
@@ -82,7 +84,7 @@ __device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity
     for (int spin = 0; spin < 128; ++spin)
       if (mbar_try_wait(bar, parity)) return;
     if (*dead) return;
-    if (clock64() - start > 4000000000LL) {
+    if (clock64() - start > limit) {
       *dead = 1;
       atomicExch(status, code);
       return;

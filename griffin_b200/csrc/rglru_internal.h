@@ -187,6 +187,8 @@ int scan_bwd_box_rows(int variant);
 int scan_bwd_box_cols(int variant);
 int raw_box_cols();
 
+cudaError_t launch_wait_selftest(int* status, int* finished, long long limit_cycles, cudaStream_t s);
+
 int* device_status_word();  // device address of the status word of the current device
 
 }  // namespace rglru

@@ -1449,6 +1449,30 @@ __global__ void __maxnreg__(96) conv_tma_bwd_kernel(const __grid_constant__ Conv
 }
 
 // ======================================================================
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever completes, with a limit of
+// `limit` SM cycles.  The wait must give up, set the device status word, and let every thread reach the
+// barrier and the final store below -- the behaviour the pipelined kernels rely on when a copy never lands.
+// ======================================================================
+__global__ void __launch_bounds__(64) wait_selftest_kernel(int* status, int* finished, long long limit) {
+  __shared__ uint64_t bar;
+  __shared__ int dead_flag;
+  volatile int* dead = &dead_flag;
+  if (threadIdx.x == 0) {
+    dead_flag = 0;
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  mbar_wait_or_flag(&bar, 0, dead, status, DEV_TIMEOUT_SELFTEST, limit);
+  __syncthreads();                       // every thread gets here: barriers stay matched after a timeout
+  if (threadIdx.x == 0 && finished) *finished = 1;
+}
+cudaError_t launch_wait_selftest(int* status, int* finished, long long limit_cycles, cudaStream_t s) {
+  wait_selftest_kernel<<<1, 64, 0, s>>>(status, finished, limit_cycles);
+  return cudaGetLastError();
+}
+
+// ======================================================================
 // Launchers
 // ======================================================================
 

@@ -59,6 +59,13 @@ int rglru_abi_version(void);
  * RGLRU_ERR_DEVICE_TIMEOUT; *detail receives a kernel-specific code. */
 int rglru_device_status(int* detail);
 
+/* Self-test of the bounded in-kernel wait (no reference counterpart; the reference's only runtime self-check is
+ * the Triton validation of griffin/triton_scan.py:180-204).  Launches one small CTA that waits, for at most
+ * `limit_us` microseconds (1 .. 100000), on a barrier that nothing completes.  The wait gives up, the kernel runs
+ * to its end (writing 1 to *finished when `finished`, a device int, is non-NULL) and the next
+ * rglru_device_status() reports RGLRU_ERR_DEVICE_TIMEOUT with detail 3.  The context stays usable. */
+int rglru_selftest_wait_timeout(unsigned limit_us, int* finished, void* stream);
+
 /* Time-steps between two saved recurrent states (the backward kernel rebuilds the
  * states inside one such chunk from its entry state). */
 int rglru_chunk_steps(int io_dtype);

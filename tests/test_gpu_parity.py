@@ -249,3 +249,30 @@ def test_raw_scan_tma_and_plain_paths(shape):
     assert orc.rel_l2(out, ref) <= FP32_REL
     for g, r in zip(grads, ref_g):
         assert orc.rel_l2(g, r) <= FP32_REL
+
+
+def test_bounded_wait_gives_up_and_reports_without_hanging():
+    """A wait on a barrier that nothing completes must expire (here after 300 us), set the status word, let the
+    kernel finish, and leave the context usable: the next scan call runs and the status word is clear again."""
+    from griffin_b200 import _lib, ops
+    lib = _lib.load()
+    assert _lib.device_status() == 0
+    finished = torch.zeros(1, device=DEV, dtype=torch.int32)
+    rc = lib.rglru_selftest_wait_timeout(300, finished.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.OK
+    detail = _lib._i(0)
+    import ctypes
+    assert lib.rglru_device_status(ctypes.byref(detail)) == _lib.ERR_DEVICE_TIMEOUT
+    assert detail.value == 3 and int(finished.item()) == 1
+    with pytest.raises(RuntimeError):
+        _lib.check(_lib.ERR_DEVICE_TIMEOUT, "self-test")
+    assert lib.rglru_selftest_wait_timeout(0, None, None) == _lib.ERR_BAD_SHAPE
+    assert lib.rglru_selftest_wait_timeout(200000, None, None) == _lib.ERR_BAD_SHAPE
+    # the context is intact: a regular call works and reports a clean status
+    case = orc.make_rglru_case(2, 70, 64, 4, seed=3)
+    u_r = orc.block_diagonal_linear(case["x"], case["recurrence_gate.weight"], case["recurrence_gate.bias"])
+    u_i = orc.block_diagonal_linear(case["x"], case["input_gate.weight"], case["input_gate.bias"])
+    y, _ = ops.rglru(case["x"].to(DEV), u_r.to(DEV), u_i.to(DEV), case["Lambda"].to(DEV))
+    ref, _ = orc.rglru_core(case["x"], u_r, u_i, case["Lambda"])
+    assert orc.rel_l2(y, ref) <= 1e-5
+    assert _lib.device_status() == 0
