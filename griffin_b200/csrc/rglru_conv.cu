@@ -536,33 +536,58 @@ __global__ void __launch_bounds__(256) decode_step_kernel(const IO* __restrict__
       }
     }
   }
-  float rate[VEC];   // c * logsigmoid(Lambda) <= 0
+  float rate[VEC];   // K = -c * logsigmoid(Lambda) >= 0
+  float kmax = 0.0f;
 #pragma unroll
   for (int v = 0; v < VEC; ++v) {
     const float lam = lambda[d + v];
-    rate[v] = c * (lam >= 0.0f ? -log1pf(__expf(-lam)) : lam - log1pf(__expf(lam)));
+    rate[v] = c * (lam >= 0.0f ? log1pf(__expf(-lam)) : log1pf(__expf(lam)) - lam);
+    kmax = fmaxf(kmax, rate[v]);
   }
+  const bool poly = kmax <= -POLY_RANGE;   // every r * K of this thread lies in the polynomial's range
 #pragma unroll
   for (int q = 0; q < DECODE_ROWS; ++q) {
     const int b = b0 + q;
     if (b >= B) break;
     const size_t at = static_cast<size_t>(b) * D + d;
     const uint32_t f = fl[q];
+    const float keep = (f & TOK_RESET) ? 0.0f : 1.0f;
+    const float live = (f & TOK_INACTIVE) ? 0.0f : 1.0f;
     float xv[VEC], rv[VEC], iv[VEC], yv[VEC];
     V::unpack(xr[q], xv);
     V::unpack(rr[q], rv);
     V::unpack(ir[q], iv);
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) {
+    if constexpr (VEC == 1) {
       float r, i;
-      sigmoid_pair(rv[v], iv[v], r, i);
-      const float em = expm1_nonpos<false>(r * rate[v]);
+      sigmoid_pair(rv[0], iv[0], r, i);
+      const float em = expm1_nonpos<false>(-r * rate[0]);
       float a = 1.0f + em;
-      float bdrive = sqrt_approx(fmaxf(-em * (2.0f + em), 0.0f)) * i * xv[v];
-      if (f & TOK_RESET) { a = 0.0f; bdrive = i * xv[v]; }
-      if (f & TOK_INACTIVE) { a = 1.0f; bdrive = 0.0f; }
-      hv[q][v] = fmaf(a, hv[q][v], bdrive);
-      yv[v] = hv[q][v];
+      float gam = sqrt_approx(fmaxf(-em * (2.0f + em), 0.0f));
+      a = a * keep * live + (1.0f - live);
+      gam = (gam * keep + (1.0f - keep)) * live;
+      hv[q][0] = fmaf(a, hv[q][0], gam * i * xv[0]);
+      yv[0] = hv[q][0];
+    } else {
+      // the arithmetic of the scan kernels' forward (same helpers, so prefill and decode agree to rounding)
+#pragma unroll
+      for (int v = 0; v < VEC; v += 2) {
+        const float2 x2 = make_float2(xv[v], xv[v + 1]);
+        const float2 K2 = make_float2(rate[v], rate[v + 1]);
+        float2 r, i;
+        sigmoid_pair2<sizeof(IO) == 2>(make_float2(rv[v], rv[v + 1]), make_float2(iv[v], iv[v + 1]), r, i);
+        const float2 y2 = mul2(r, K2);
+        const float2 e = poly ? one_minus_exp_neg2<true, sizeof(IO) == 2>(y2) : one_minus_exp_neg2<false, sizeof(IO) == 2>(y2);
+        float2 a = fma2(e, f2(-1.0f), f2(1.0f));
+        const float2 gq = add2(mul2(e, fma2(e, f2(-1.0f), f2(2.0f))), f2(1e-30f));
+        float2 gam = mul2(gq, make_float2(rsqrt_approx(gq.x), rsqrt_approx(gq.y)));
+        if (f) {
+          a = fma2(mul2(a, f2(keep)), f2(live), f2(1.0f - live));
+          gam = mul2(fma2(gam, f2(keep), f2(1.0f - keep)), f2(live));
+        }
+        const float2 h2 = fma2(a, make_float2(hv[q][v], hv[q][v + 1]), mul2(mul2(gam, i), x2));
+        hv[q][v] = h2.x; hv[q][v + 1] = h2.y;
+        yv[v] = h2.x; yv[v + 1] = h2.y;
+      }
     }
     V::store(y + at, yv);
     if constexpr (VEC == 1) {
