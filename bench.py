@@ -211,28 +211,48 @@ def run_ours(args) -> dict:
         host_dy = torch.randn(B, T, D).to(dtype).pin_memory()
         host_out = torch.empty(B, D, dtype=torch.float32).pin_memory()
         host_dlam = torch.empty(D, dtype=dtype).pin_memory()
-        xd = torch.empty(B, T, D, device=dev, dtype=dtype, requires_grad=True)
-        dyd = torch.empty(B, T, D, device=dev, dtype=dtype)
+        # Two device buffers per input: the copies of step k+1 (own stream) overlap the kernels of step k.
+        bufs = [(torch.empty(B, T, D, device=dev, dtype=dtype, requires_grad=True),
+                 torch.empty(B, T, D, device=dev, dtype=dtype)) for _ in range(2)]
+        copy_stream = torch.cuda.Stream(dev)
+        main_stream = torch.cuda.current_stream(dev)
+        loaded = [torch.cuda.Event() for _ in range(2)]
+        consumed = [torch.cuda.Event() for _ in range(2)]
 
-        def e2e_step():
-            with torch.no_grad():
+        def e2e_copy(k):
+            xd, dyd = bufs[k % 2]
+            with torch.cuda.stream(copy_stream), torch.no_grad():
+                copy_stream.wait_event(consumed[k % 2])          # the step that last used this buffer is done
                 xd.copy_(host_x, non_blocking=True)
                 dyd.copy_(host_dy, non_blocking=True)
+                loaded[k % 2].record(copy_stream)
+
+        def e2e_compute(k):
+            xd, dyd = bufs[k % 2]
+            main_stream.wait_event(loaded[k % 2])
             module.zero_grad(set_to_none=True)
             xd.grad = None
             yy, hh = module(xd, return_state=True)
             yy.backward(dyd)
+            consumed[k % 2].record(main_stream)
             host_out.copy_(hh, non_blocking=True)
             host_dlam.copy_(module.Lambda.grad, non_blocking=True)
 
+        def e2e_run(n):
+            e2e_copy(0)
+            for k in range(n):
+                if k + 1 < n:
+                    e2e_copy(k + 1)
+                e2e_compute(k)
+
         e2e_steps = max(3, min(args.steps, 50))
-        for _ in range(3):
-            e2e_step()
+        for ev in consumed:
+            ev.record(main_stream)
+        e2e_run(3)
         barrier()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a0.record()
-        for _ in range(e2e_steps):
-            e2e_step()
+        e2e_run(e2e_steps)
         a1.record()
         barrier()
         e2e_ms = a0.elapsed_time(a1) / e2e_steps
@@ -243,7 +263,8 @@ def run_ours(args) -> dict:
         e2e = {"value": world * bytes_step / e2e_ms / 1e6, "unit": "GB/s",
                "h2d_bytes_per_step": 2 * es * n_elem, "d2h_bytes_per_step": 4 * B * D + es * D,
                "ms_per_step": e2e_ms, "steps": e2e_steps,
-               "path": "griffin_b200.RG_LRU(scan_mode='cuda') forward+backward, gate GEMMs included"}
+               "path": "griffin_b200.RG_LRU(scan_mode='cuda') forward+backward, gate GEMMs included; every step's inputs "
+                       "copied from pinned host memory on a second stream (double-buffered), results read back"}
     clocks = sampler.stop()
     status = _lib.device_status()
 

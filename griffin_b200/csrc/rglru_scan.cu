@@ -20,6 +20,17 @@
 // The gate epilogue follows griffin/griffin.py:237-258 of the reference, the
 // scan :280-286, the backward is the closed form of autograd over those lines
 // with the capped sqrt slope of :59-65.  All arithmetic is fp32.
+//
+// Template switches of the two kernels (each a separate instantiation, so the
+// plain kernels pay nothing for them):
+//   CONV    the width-4 causal conv in front of the layer (:474-486) is applied
+//           while a chunk is loaded, from an x tile with a three-row halo;
+//   MERGE   the block's GeLU-branch product (:464, :520) is formed in the store
+//           stage and differentiated in the backward's load stage;
+//   GROUPED both gate pre-activations come from one [B, T, 2 D] tensor written
+//           by a single grouped GEMM, and the gate biases are added here.
+// The file also holds the raw affine scan operator (triton_scan.py:274-276), the
+// TMA-staged kernels of the conv alone, and the self-test of the bounded wait.
 
 #include <cstdlib>
 

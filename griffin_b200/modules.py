@@ -311,7 +311,24 @@ class RecurrentBlock(nn.Module):
 
         conv_w = self.temporal_conv.weight[:, 0, :]
         rnn_state = None if cache is None else cache.rnn_state
-        if self.fold_conv:
+        if steps == 1 and cache is not None and not torch.is_grad_enabled() and x_in.is_cuda:
+            # Cached single-token decode (inference): the two in-place decode kernels on copies of the cached
+            # states (the cache stays a value: the caller's old cache is not modified).
+            if rnn_state.shape != (batch, self.rnn_width):
+                raise ValueError(f"ht_minus_1 must have shape ({batch}, {self.rnn_width}), got {tuple(rnn_state.shape)}")
+            lru = self.rg_lru
+            tok = flags[:, 0].contiguous()
+            new_conv = conv_state.to(x_in.dtype).clone()
+            bias = self.temporal_conv.bias
+            x_conv = ops.decode_conv(x_in[:, 0].contiguous(), conv_w.float().contiguous(),
+                                     None if bias is None else bias.float().contiguous(), new_conv, tok)
+            u_r = lru.recurrence_gate(x_conv).to(x_conv.dtype)
+            u_i = lru.input_gate(x_conv).to(x_conv.dtype)
+            new_rnn = rnn_state.to(device=x_in.device, dtype=torch.float32).clone()
+            y = ops.decode_step(x_conv, u_r, u_i, lru.Lambda.float().contiguous(), new_rnn, tok, lru.c)[:, None, :]
+            if self.fold_merge:
+                y = y * F.gelu(y_branch, approximate="tanh")
+        elif self.fold_conv:
             if not x_in.is_cuda:
                 raise RuntimeError("scan_mode='cuda' requires CUDA tensors; there is no CPU fallback")
             if rnn_state is not None and rnn_state.shape != (batch, self.rnn_width):
