@@ -113,6 +113,15 @@ class LocalMQAAttention(nn.Module):
         return out
 
 
+def _autocast_once(h: Tensor) -> Tensor:
+    """Under CUDA autocast every projection that consumes ``h`` would cast it to the autocast dtype on its own
+    (autocast caches casts of parameters, not of activations); doing the same cast once here gives identical
+    values and saves the repeated passes."""
+    if h.is_cuda and h.dtype == torch.float32 and torch.is_autocast_enabled("cuda"):
+        return h.to(torch.get_autocast_dtype("cuda"))
+    return h
+
+
 class ResidualBlock(nn.Module):
     """Pre-norm temporal mixing + gated MLP (griffin/griffin.py:732-809)."""
 
@@ -136,8 +145,8 @@ class ResidualBlock(nn.Module):
         self.mlp = GatedMLPBlock(input_dim, input_dim * expansion_factor, final_w_init_variance_scale)
 
     def forward(self, x: Tensor, segment_pos: Optional[Tensor] = None, *, active_mask: Optional[Tensor] = None) -> Tensor:
-        x = x + self.temporal(self.norm1(x), None, segment_pos, active_mask=active_mask)
-        x = x + self.mlp(self.norm2(x))
+        x = x + self.temporal(_autocast_once(self.norm1(x)), None, segment_pos, active_mask=active_mask)
+        x = x + self.mlp(_autocast_once(self.norm2(x)))
         if active_mask is not None:
             x = torch.where(active_mask[..., None], x, torch.zeros_like(x))
         return x
