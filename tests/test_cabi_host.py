@@ -192,3 +192,11 @@ def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(RuntimeError, match="no CPU or Triton fallback"):
         _lib.load()
+
+
+def test_scan_self_check_says_no_without_a_cuda_device():
+    """tests/test_rglru.py:122-124 of the reference: the usability probe is False for the CPU."""
+    from griffin_b200 import cuda_scan_is_usable
+    assert cuda_scan_is_usable("cpu") is False
+    with pytest.raises(RuntimeError):
+        cuda_scan_is_usable("cpu", strict=True)

@@ -276,3 +276,10 @@ def test_bounded_wait_gives_up_and_reports_without_hanging():
     ref, _ = orc.rglru_core(case["x"], u_r, u_i, case["Lambda"])
     assert orc.rel_l2(y, ref) <= 1e-5
     assert _lib.device_status() == 0
+
+
+def test_scan_self_check_passes_on_this_device():
+    """The closed-form known-answer case of griffin/triton_scan.py:139-177 through the CUDA raw scan, fwd + grads."""
+    from griffin_b200 import cuda_scan_is_usable
+    assert cuda_scan_is_usable("cuda") is True
+    assert cuda_scan_is_usable(torch.device("cuda", 0), strict=True) is True
