@@ -365,8 +365,11 @@ def _model_cases(G):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("GRIFFIN_REFERENCE"),
+                    help="checkout of the unmodified reference project (or set GRIFFIN_REFERENCE)")
     args = ap.parse_args()
+    if not args.reference or not os.path.isdir(args.reference):
+        ap.error("pass --reference <checkout of the reference project>")
     sys.path.insert(0, args.reference)
     import griffin as G  # the unmodified reference
     from griffin import triton_scan as TS
