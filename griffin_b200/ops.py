@@ -14,6 +14,8 @@ CUDA stream; nothing here computes on the CPU.
 
 from __future__ import annotations
 
+import contextlib
+import os
 from typing import Optional
 
 import torch
@@ -36,6 +38,25 @@ def _require_cuda(*tensors: Optional[Tensor]) -> None:
             raise RuntimeError("CUDA RG-LRU kernels require CUDA tensors (scan_mode='cuda' has no CPU path)")
 
 
+_NVTX = os.environ.get("RGLRU_NVTX", "0") not in ("", "0")
+
+
+@contextlib.contextmanager
+def _on_traced(t: Tensor, name: str):
+    with torch.cuda.device(t.device):
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+
+
+def _on(t: Tensor, name: str):
+    """Context that makes ``t``'s device current for one library call; with RGLRU_NVTX=1 the call also sits in an
+    NVTX range named after the entry point, so a profiler's timeline or range filter shows the operators."""
+    return _on_traced(t, name) if _NVTX else torch.cuda.device(t.device)
+
+
 def _ptr(t: Optional[Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
@@ -56,7 +77,7 @@ def _rglru_fwd(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Te
     h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
     nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
     ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
-    with torch.cuda.device(x.device):
+    with _on(x, "rglru_fwd"):
         rc = lib.rglru_fwd(_ptr(x), _ptr(u_r), _ptr(u_i), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(y), _ptr(h_last),
                            _ptr(ws) if save else None, nbytes, B, T, D, c, dt, _stream(x))
     _lib.check(rc, "rglru_fwd")
@@ -81,7 +102,7 @@ def _rglru_bwd(dy: Tensor, dh_last: Optional[Tensor], x: Tensor, u_r: Tensor, u_
     du_i = torch.empty_like(x)
     dlam = torch.empty(D, device=x.device, dtype=torch.float32)
     dh0 = torch.empty((B, D) if want_dh0 else (0,), device=x.device, dtype=torch.float32)
-    with torch.cuda.device(x.device):
+    with _on(x, "rglru_bwd"):
         rc = lib.rglru_bwd(_ptr(dy), _ptr(dh_last), _ptr(x), _ptr(u_r), _ptr(u_i), _ptr(lam), _ptr(h0), _ptr(tok),
                            _ptr(ws), ws.numel(), _ptr(dx), _ptr(du_r), _ptr(du_i), _ptr(dlam),
                            _ptr(dh0) if want_dh0 else None, B, T, D, c, dt, _stream(x))
@@ -145,7 +166,7 @@ def _scan_fwd(decay: Tensor, drive: Tensor, h0: Tensor) -> Tensor:
     lib = _lib.load()
     B, T, D = decay.shape
     out = torch.empty_like(drive)
-    with torch.cuda.device(decay.device):
+    with _on(decay, "rglru_linear_scan_fwd"):
         rc = lib.rglru_linear_scan_fwd(_ptr(decay), _ptr(drive), _ptr(h0), _ptr(out), B, T, D, _stream(decay))
     _lib.check(rc, "rglru_linear_scan_fwd")
     return out
@@ -163,7 +184,7 @@ def _scan_bwd(d_out: Tensor, decay: Tensor, h0: Tensor, out: Tensor) -> tuple[Te
     d_decay = torch.empty_like(decay)
     d_drive = torch.empty_like(decay)
     d_h0 = torch.empty_like(h0)
-    with torch.cuda.device(decay.device):
+    with _on(decay, "rglru_linear_scan_bwd"):
         rc = lib.rglru_linear_scan_bwd(_ptr(d_out), _ptr(decay), _ptr(h0), _ptr(out), _ptr(d_decay), _ptr(d_drive),
                                        _ptr(d_h0), B, T, D, _stream(decay))
     _lib.check(rc, "rglru_linear_scan_bwd")
@@ -214,7 +235,7 @@ def _conv_fwd(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tens
     B, T, D = x_in.shape
     out = torch.empty_like(x_in)
     new_state = torch.empty(B, 3, D, device=x_in.device, dtype=x_in.dtype)
-    with torch.cuda.device(x_in.device):
+    with _on(x_in, "rglru_conv_fwd"):
         rc = lib.rglru_conv_fwd(_ptr(x_in), _ptr(w), _ptr(b), _ptr(state), _ptr(tok), _ptr(out), _ptr(new_state),
                                 B, T, D, dt, _stream(x_in))
     _lib.check(rc, "rglru_conv_fwd")
@@ -239,7 +260,7 @@ def _conv_bwd(d_conv: Tensor, x_in: Tensor, w: Tensor, state: Optional[Tensor], 
     d_state = torch.empty((B, 3, D) if want_state else (0,), device=x_in.device, dtype=x_in.dtype)
     nbytes = lib.rglru_conv_bwd_workspace_bytes(B, T, D)
     ws = torch.empty(nbytes, device=x_in.device, dtype=torch.uint8)
-    with torch.cuda.device(x_in.device):
+    with _on(x_in, "rglru_conv_bwd"):
         rc = lib.rglru_conv_bwd(_ptr(d_conv), _ptr(x_in), _ptr(w), _ptr(state), _ptr(tok), _ptr(dx), _ptr(d_w),
                                 _ptr(d_b), _ptr(d_state) if want_state else None, _ptr(ws), nbytes, B, T, D, dt,
                                 _stream(x_in))
@@ -301,7 +322,7 @@ def conv_scan_fwd(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_s
     h_last = torch.empty(B, D, device=x_in.device, dtype=torch.float32)
     nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
     ws = torch.empty(nbytes, device=x_in.device, dtype=torch.uint8)
-    with torch.cuda.device(x_in.device):
+    with _on(x_in, "rglru_conv_scan_fwd"):
         rc = lib.rglru_conv_scan_fwd(_ptr(x_in), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state), _ptr(u_r), _ptr(u_i),
                                      _ptr(lam), _ptr(h0), _ptr(tok), _ptr(y), _ptr(h_last),
                                      _ptr(ws) if save else None, nbytes, B, T, D, c, dt, _stream(x_in))
@@ -320,7 +341,7 @@ def conv_scan_bwd(dy: Tensor, dh_last: Optional[Tensor], x_in: Tensor, conv_w: T
     dxc, du_r, du_i = torch.empty_like(x_in), torch.empty_like(x_in), torch.empty_like(x_in)
     dlam = torch.empty(D, device=x_in.device, dtype=torch.float32)
     dh0 = torch.empty(B, D, device=x_in.device, dtype=torch.float32) if want_dh0 else None
-    with torch.cuda.device(x_in.device):
+    with _on(x_in, "rglru_conv_scan_bwd"):
         rc = lib.rglru_conv_scan_bwd(_ptr(dy), _ptr(dh_last), _ptr(x_in), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state),
                                      _ptr(u_r), _ptr(u_i), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(ws), ws.numel(),
                                      _ptr(dxc), _ptr(du_r), _ptr(du_i), _ptr(dlam), _ptr(dh0), B, T, D, c, dt,
@@ -343,7 +364,7 @@ def merge_scan_fwd(x: Tensor, conv_w: Optional[Tensor], conv_b: Optional[Tensor]
     h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
     nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
     ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
-    with torch.cuda.device(x.device):
+    with _on(x, "rglru_merge_fwd"):
         rc = lib.rglru_merge_fwd(_ptr(x), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state), _ptr(u_r), _ptr(u_i),
                                  _ptr(branch), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(out), _ptr(h_last),
                                  _ptr(ws) if save else None, nbytes, B, T, D, c, dt, _stream(x))
@@ -362,7 +383,7 @@ def merge_scan_bwd(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, conv_w: O
     dx, du_r, du_i, dbranch = (torch.empty_like(x) for _ in range(4))
     dlam = torch.empty(D, device=x.device, dtype=torch.float32)
     dh0 = torch.empty(B, D, device=x.device, dtype=torch.float32) if want_dh0 else None
-    with torch.cuda.device(x.device):
+    with _on(x, "rglru_merge_bwd"):
         rc = lib.rglru_merge_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state),
                                  _ptr(u_r), _ptr(u_i), _ptr(branch), _ptr(lam), _ptr(h0), _ptr(tok), _ptr(ws),
                                  ws.numel(), _ptr(dx), _ptr(du_r), _ptr(du_i), _ptr(dbranch), _ptr(dlam), _ptr(dh0),
@@ -452,7 +473,7 @@ class _GroupedRGLRU(torch.autograd.Function):
             h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
             nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
             ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
-            with torch.cuda.device(x.device):
+            with _on(x, "rglru_grouped_fwd"):
                 rc = lib.rglru_grouped_fwd(_ptr(x), _ptr(u), _ptr(bias), _ptr(branch), _ptr(lam32), _ptr(h032), _ptr(tok),
                                            _ptr(out), _ptr(h_last), _ptr(ws) if save else None, nbytes, B, T, D, bw,
                                            float(c), dt, _stream(x))
@@ -481,7 +502,7 @@ class _GroupedRGLRU(torch.autograd.Function):
             dbranch = None if branch is None else torch.empty_like(x)
             dlam = torch.empty(D, device=x.device, dtype=torch.float32)
             dh0 = torch.empty(B, D, device=x.device, dtype=torch.float32) if want_dh0 else None
-            with torch.cuda.device(x.device):
+            with _on(x, "rglru_grouped_bwd"):
                 rc = lib.rglru_grouped_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(u), _ptr(bias), _ptr(branch),
                                            _ptr(lam32), _ptr(h032), _ptr(tok), _ptr(ws), ws.numel(), _ptr(dx), _ptr(du),
                                            _ptr(dbranch), _ptr(dlam), _ptr(dh0), B, T, D, bw, ctx.c, dt, _stream(x))
@@ -621,7 +642,7 @@ def decode_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state
     if conv_state.shape != (B, 3, D) or conv_state.dtype != x_in.dtype or not conv_state.is_contiguous():
         raise ValueError("conv_state must be a contiguous [batch, 3, width] tensor of the activation dtype")
     out = torch.empty_like(x_in)
-    with torch.cuda.device(x_in.device):
+    with _on(x_in, "rglru_decode_conv"):
         rc = lib.rglru_decode_conv(_ptr(x_in.contiguous()), _ptr(weight), _ptr(bias), _ptr(conv_state), _ptr(tok),
                                    _ptr(out), B, D, dt, _stream(x_in))
     _lib.check(rc, "rglru_decode_conv")
@@ -638,7 +659,7 @@ def decode_step(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h: Tensor, tok
     if h.shape != (B, D) or h.dtype != torch.float32 or not h.is_contiguous():
         raise ValueError("h must be a contiguous fp32 [batch, width] tensor")
     y = torch.empty_like(x)
-    with torch.cuda.device(x.device):
+    with _on(x, "rglru_decode_step"):
         rc = lib.rglru_decode_step(_ptr(x.contiguous()), _ptr(u_r.contiguous()), _ptr(u_i.contiguous()), _ptr(lam),
                                    _ptr(h), _ptr(tok), _ptr(y), B, D, float(c), dt, _stream(x))
     _lib.check(rc, "rglru_decode_step")
