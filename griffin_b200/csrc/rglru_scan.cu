@@ -71,6 +71,16 @@ __device__ __forceinline__ void load_flags(const uint8_t* tok, int b, int T, int
   }
 }
 
+// Whether any of a thread's flag bytes is set.  Ordinary tokens have a zero byte, so a thread whose steps are
+// all ordinary takes the mask-free arithmetic even when the caller passed a flag tensor.
+template <int N>
+__device__ __forceinline__ bool any_flag(const uint32_t (&fl)[N]) {
+  uint32_t v = 0u;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v |= fl[i];
+  return v != 0u;
+}
+
 // Plain-load staging of one [rows, CH] tile (zero-filled outside the tensor).
 template <typename IO, int CH>
 __device__ __forceinline__ void tile_load_plain(uint8_t* tile, const void* src, int b, int t0, int d0, int rows, int T, int D) {
@@ -393,7 +403,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
       load_hist<IO>(p.conv_state, b, d0 + vec * CV, p.D, hist_v);
       hist = hist_v;
     }
-    if (masked) {
+    if (masked && any_flag(fl)) {
       if (poly) fwd_local<IO, TS, CH, true, true, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
       else fwd_local<IO, TS, CH, true, false, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
     } else {
@@ -721,7 +731,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         load_hist<IO>(p.conv_state, b, d0 + vec * CV, p.D, hist_v);
         hist = hist_v;
       }
-      if (masked) {
+      if (masked && any_flag(fl)) {
         if (poly) bwd_local<IO, TS, CH, true, true, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
         else bwd_local<IO, TS, CH, true, false, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
       } else {
@@ -1239,12 +1249,13 @@ __global__ void __launch_bounds__(288) conv_tma_fwd_kernel(const __grid_constant
     }
     mbar_wait_or_flag(&full[stage], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
     float2 xc[TS][2];
-    if (masked) conv_front<IO, TS, CH, true>(tiles, off0, ct, fl, hist, xc);
+    const bool flagged = masked && any_flag(fl);
+    if (flagged) conv_front<IO, TS, CH, true>(tiles, off0, ct, fl, hist, xc);
     else conv_front<IO, TS, CH, false>(tiles, off0, ct, fl, hist, xc);
     uint8_t* to = tiles + SM::TILEX;
 #pragma unroll
     for (int st = 0; st < TS; ++st) {
-      if (masked && ((fl[0] >> (8 * st)) & TOK_INACTIVE)) { xc[st][0] = f2(0.0f); xc[st][1] = f2(0.0f); }   // padding emits zero
+      if (flagged && ((fl[0] >> (8 * st)) & TOK_INACTIVE)) { xc[st][0] = f2(0.0f); xc[st][1] = f2(0.0f); }   // padding emits zero
       Pack<IO>::store2(to + off0 + st * ROWB, xc[st]);
     }
     fence_async_smem();
@@ -1433,7 +1444,7 @@ __global__ void __maxnreg__(96) conv_tma_bwd_kernel(const __grid_constant__ Conv
     if (k == 0 && lane_t == 0 && p.d_state)
       dstate = static_cast<IO*>(p.d_state) + static_cast<size_t>(b) * 3 * p.D + d0 + vec * CV;
     const float2 (*hist)[2] = use_hist ? hist_v : nullptr;
-    if (masked) conv_bwd_steps<IO, TS, CH, true>(tiles, tiles + SM::OFF_X, tiles + SM::OFF_DX, off0, ct, fb, hist, dstate,
+    if (masked && any_flag(fb)) conv_bwd_steps<IO, TS, CH, true>(tiles, tiles + SM::OFF_X, tiles + SM::OFF_DX, off0, ct, fb, hist, dstate,
                                                  p.D, p.D - (d0 + vec * CV), gw);
     else conv_bwd_steps<IO, TS, CH, false>(tiles, tiles + SM::OFF_X, tiles + SM::OFF_DX, off0, ct, fb, hist, dstate,
                                            p.D, p.D - (d0 + vec * CV), gw);
