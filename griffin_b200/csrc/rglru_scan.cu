@@ -60,6 +60,14 @@ __device__ __forceinline__ RowMask row_mask(uint32_t packed, int st) {
 // beyond T are padding.
 template <int TS>
 __device__ __forceinline__ void load_flags(const uint8_t* tok, int b, int T, int t_first, uint32_t (&fl)[(TS + 3) / 4]) {
+  if (TS == 4 && tok && t_first + 4 <= T) {
+    // four whole steps: one word when the bytes happen to be 4-byte aligned (the byte of step st sits at bits 8 st)
+    const uint8_t* p = tok + static_cast<size_t>(b) * T + t_first;
+    if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+      fl[0] = *reinterpret_cast<const uint32_t*>(p);
+      return;
+    }
+  }
 #pragma unroll
   for (int w = 0; w < (TS + 3) / 4; ++w) fl[w] = 0;
 #pragma unroll
@@ -1427,12 +1435,23 @@ __global__ void __maxnreg__(96) conv_tma_bwd_kernel(const __grid_constant__ Conv
     // flag bytes of the TS + 3 tokens whose gradient this thread reads (steps at or past T count as padding)
     uint32_t fb[TS + 3];
     const bool masked = (p.tok != nullptr) || (t0 + TC + 3 > p.T);
+    {
+      const int t_first = t0 + lane_t * TS;
+      const uint8_t* fp = p.tok ? p.tok + static_cast<size_t>(b) * p.T + t_first : nullptr;
+      if (masked && fp && t_first + 8 <= p.T && (reinterpret_cast<uintptr_t>(fp) & 3u) == 0) {
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(fp);       // two aligned words cover the seven tokens
+        const uint32_t w1 = *reinterpret_cast<const uint32_t*>(fp + 4);
 #pragma unroll
-    for (int j = 0; j < TS + 3; ++j) {
-      fb[j] = 0u;
-      if (masked) {
-        const int t = t0 + lane_t * TS + j;
-        fb[j] = t < p.T ? (p.tok ? p.tok[static_cast<size_t>(b) * p.T + t] : 0u) : TOK_INACTIVE;
+        for (int j = 0; j < TS + 3; ++j) fb[j] = ((j < 4 ? w0 : w1) >> (8 * (j & 3))) & 0xffu;
+      } else {
+#pragma unroll
+        for (int j = 0; j < TS + 3; ++j) {
+          fb[j] = 0u;
+          if (masked) {
+            const int t = t_first + j;
+            fb[j] = t < p.T ? (p.tok ? p.tok[static_cast<size_t>(b) * p.T + t] : 0u) : TOK_INACTIVE;
+          }
+        }
       }
     }
     float2 hist_v[3][2];
