@@ -60,14 +60,6 @@ __device__ __forceinline__ RowMask row_mask(uint32_t packed, int st) {
 // beyond T are padding.
 template <int TS>
 __device__ __forceinline__ void load_flags(const uint8_t* tok, int b, int T, int t_first, uint32_t (&fl)[(TS + 3) / 4]) {
-  if (TS == 4 && tok && t_first + 4 <= T) {
-    // four whole steps: one word when the bytes happen to be 4-byte aligned (the byte of step st sits at bits 8 st)
-    const uint8_t* p = tok + static_cast<size_t>(b) * T + t_first;
-    if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
-      fl[0] = *reinterpret_cast<const uint32_t*>(p);
-      return;
-    }
-  }
 #pragma unroll
   for (int w = 0; w < (TS + 3) / 4; ++w) fl[w] = 0;
 #pragma unroll
@@ -87,6 +79,20 @@ __device__ __forceinline__ bool any_flag(const uint32_t (&fl)[N]) {
 #pragma unroll
   for (int i = 0; i < N; ++i) v |= fl[i];
   return v != 0u;
+}
+
+// The same for four steps, as one word when the four bytes are whole and 4-byte aligned (the byte of step st sits
+// at bits 8 st).  Used by the conv kernels, whose per-element work is small enough for the byte loads to show;
+// the scan kernels keep the byte loads (the word path perturbed their register allocation: +9 % backward time).
+__device__ __forceinline__ void load_flags_word(const uint8_t* tok, int b, int T, int t_first, uint32_t (&fl)[1]) {
+  if (tok && t_first + 4 <= T) {
+    const uint8_t* p = tok + static_cast<size_t>(b) * T + t_first;
+    if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+      fl[0] = *reinterpret_cast<const uint32_t*>(p);
+      return;
+    }
+  }
+  load_flags<4>(tok, b, T, t_first, fl);
 }
 
 // Plain-load staging of one [rows, CH] tile (zero-filled outside the tensor).
@@ -295,8 +301,7 @@ struct FwdSmem {
 // MERGE: the kernel also reads the pre-activation of the block's GeLU branch and writes
 // h_t * gelu(branch_t) (griffin/griffin.py:464, 520 of the reference) instead of h_t.
 template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
-__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
-    rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
+__device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFwdArgs& p) {
   using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
@@ -473,6 +478,19 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     }
   }
   if (tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;
+}
+
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
+__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
+    rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
+  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED>(maps, p);
+}
+// The same kernel capped at 96 registers, which lets two 9-warp CTAs share an SM's register files (five warps
+// on one scheduler partition).  Used for the merged / grouped variants, which otherwise take about 112.
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
+__global__ void __maxnreg__(96)
+    rglru_fwd_kernel_capped(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
+  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED>(maps, p);
 }
 
 // ======================================================================
@@ -1248,7 +1266,7 @@ __global__ void __launch_bounds__(288) conv_tma_fwd_kernel(const __grid_constant
     const int t0 = k * TC;
     uint32_t fl[1];
     const bool masked = (p.tok != nullptr) || (t0 + TC > p.T);
-    if (masked) load_flags<TS>(p.tok, b, p.T, t0 + lane_t * TS, fl);
+    if (masked) load_flags_word(p.tok, b, p.T, t0 + lane_t * TS, fl);
     float2 hist_v[3][2];
     const float2 (*hist)[2] = nullptr;
     if (k == 0 && lane_t == 0 && p.state) {
@@ -1589,7 +1607,10 @@ static cudaError_t set_smem(Kern kern, int bytes) {
 template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
+  constexpr bool CAPPED = USE_TMA && !CONV && (MERGE || GROUPED);
+  void (*kern)(FwdMaps, ScanFwdArgs);
+  if constexpr (CAPPED) kern = rglru_fwd_kernel_capped<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
+  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
   constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
   cudaError_t e = set_smem(kern, bytes);
@@ -1668,7 +1689,7 @@ cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, c
 template <typename IO, bool CONV>
 static cudaError_t launch_merge_fwd_t(bool use_tma, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
-  return use_tma ? launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, CONV, true>(maps, a, s)
+  return use_tma ? launch_fwd_t<IO, Shape64x16x4, H ? (CONV ? 4 : 3) : 3, true, CONV, true>(maps, a, s)
                  : launch_fwd_t<IO, Shape64x16x4, 1, false, CONV, true>(maps, a, s);
 }
 template <typename IO, bool CONV>
@@ -1693,7 +1714,7 @@ cudaError_t launch_merge_bwd(bool bf16, bool use_tma, bool conv, const BwdMaps& 
 template <typename IO, bool MERGE>
 static cudaError_t launch_grouped_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
-  return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, MERGE, true>(maps, a, s);
+  return launch_fwd_t<IO, Shape64x16x4, H ? (MERGE ? 3 : 4) : 3, true, false, MERGE, true>(maps, a, s);
 }
 template <typename IO, bool MERGE>
 static cudaError_t launch_grouped_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
