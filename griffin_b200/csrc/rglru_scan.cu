@@ -615,8 +615,12 @@ struct BwdSmem {
   static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
-__global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
+// SELF_ISSUE: no producer warp; thread 0 of the compute warps issues the bulk copies at chunk boundaries (one
+// more CTA barrier per chunk).  Eight warps instead of nine put two warps on every scheduler partition, which
+// lifts the register limit of a thread from 168 to 255.
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED,
+          bool SELF_ISSUE = false>
+__global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), 1)
     rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
   using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
@@ -662,34 +666,40 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
   }
   const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
-  if (USE_TMA && tid >= NCOMP) {
+  auto issue = [&](int q) {  // q-th chunk in processing order == chunk nchunks-1-q in time
+    const int k = nchunks - 1 - q;
+    const int sidx = q % NSTAGE;
+    uint8_t* st = smem + sidx * SM::STAGE;
+    mbar_expect_tx(&full[sidx], SM::STAGE);
+    tma_load_3d(st, &maps.dy, d0, k * TC, b, &full[sidx]);
+    tma_load_3d(st + SM::OFF_X, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);
+    tma_load_3d(st + SM::OFF_UR, &maps.ur, rcol, k * TC, b, &full[sidx]);
+    tma_load_3d(st + SM::OFF_UI, &maps.ui, icol, k * TC, b, &full[sidx]);
+    if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
+  };
+  auto store = [&](int q) {
+    const int k = nchunks - 1 - q;
+    uint8_t* st = smem + (q % NSTAGE) * SM::STAGE;
+    tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
+    tma_store_3d(&maps.dur, st + SM::OFF_UR, rcol, k * TC, b);
+    tma_store_3d(&maps.dui, st + SM::OFF_UI, icol, k * TC, b);
+    if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
+    tma_commit();
+  };
+  if (USE_TMA && SELF_ISSUE && tid == 0)
+    for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
+
+  if (USE_TMA && !SELF_ISSUE && tid >= NCOMP) {
     // ---- producer warp (chunks are walked from the end of the sequence to its start)
     if (tid == NCOMP) {
       prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
       prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
       if (MERGE) { prefetch_map(&maps.g); prefetch_map(&maps.dg); }
-      auto issue = [&](int q) {  // q-th chunk in processing order == chunk nchunks-1-q in time
-        const int k = nchunks - 1 - q;
-        const int sidx = q % NSTAGE;
-        uint8_t* st = smem + sidx * SM::STAGE;
-        mbar_expect_tx(&full[sidx], SM::STAGE);
-        tma_load_3d(st, &maps.dy, d0, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::OFF_X, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);
-        tma_load_3d(st + SM::OFF_UR, &maps.ur, rcol, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::OFF_UI, &maps.ui, icol, k * TC, b, &full[sidx]);
-        if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
-      };
       for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
       for (int q = 0; q < nchunks; ++q) {
-        const int k = nchunks - 1 - q;
         const int sidx = q % NSTAGE;
-        uint8_t* st = smem + sidx * SM::STAGE;
         mbar_wait_or_flag(&ready[sidx], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
-        tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
-        tma_store_3d(&maps.dur, st + SM::OFF_UR, rcol, k * TC, b);
-        tma_store_3d(&maps.dui, st + SM::OFF_UI, icol, k * TC, b);
-        if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
-        tma_commit();
+        store(q);
         if (q + NSTAGE < nchunks) {
           tma_wait_read<0>();
           issue(q + NSTAGE);
@@ -848,7 +858,18 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
         Pack<IO>::store2(tdi + off, div);
       }
     }
-    if (USE_TMA) {
+    if (USE_TMA && SELF_ISSUE) {
+      fence_async_smem();
+      bar_compute(NCOMP);          // every thread's results are in the stage
+      if (tid == 0) {
+        store(q);
+        // the stage of the previous chunk is free once its store (the group before this one) has been read
+        if (q >= 1 && q - 1 + NSTAGE < nchunks) {
+          tma_wait_read<1>();
+          issue(q - 1 + NSTAGE);
+        }
+      }
+    } else if (USE_TMA) {
       fence_async_smem();
       __syncwarp();
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
@@ -862,6 +883,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0), 1)
     }
   }
 
+  if (USE_TMA && SELF_ISSUE && tid == 0) tma_wait_all<0>();
   if (rev_chain && dch < p.D && p.dh0) p.dh0[static_cast<size_t>(b) * p.D + dch] = carry_rev;
 
   // Per-row partial of sum_t dl * r: fold the time-lanes in a fixed order.
@@ -1549,7 +1571,7 @@ constexpr int NUM_VARIANTS = 4;
 static const int kFwdRows[NUM_VARIANTS] = {64, 64, 128, 64};
 static const int kFwdCols[NUM_VARIANTS] = {64, 64, 32, 32};
 static const int kBwdRows[NUM_VARIANTS] = {64, 64, 64, 64};
-static const int kBwdCols[NUM_VARIANTS] = {64, 64, 32, 32};
+static const int kBwdCols[NUM_VARIANTS] = {64, 64, 32, 64};
 
 int scan_fwd_box_rows(int v) { return kFwdRows[v]; }
 int scan_fwd_box_cols(int v) { return kFwdCols[v]; }
@@ -1561,7 +1583,8 @@ static int env_override(const char* name) {
   return (v && v[0] >= '0' && v[0] < '0' + NUM_VARIANTS) ? (v[0] - '0') : -1;
 }
 
-// RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT force a shape (for tuning runs).
+// RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT force a shape (for tuning runs).  Backward variant 3 is the 64 x 64
+// shape without the producer warp (SELF_ISSUE); measured on B200 it is as fast as variant 0, not faster.
 // Measured on B200: half-width forward tiles pay off for bf16 when 64-channel tiles cannot put two
 // CTAs on every SM (e.g. B=8, D=1024: 35 us against 43 us); for fp32 and for the backward kernel
 // (one CTA per SM by registers either way) the 64-channel shape is faster.
@@ -1636,16 +1659,17 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
   return bf16 ? launch_fwd_io<__nv_bfloat16>(use_tma, variant, maps, a, s) : launch_fwd_io<float>(use_tma, variant, maps, a, s);
 }
 
-template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false,
+          bool SELF_ISSUE = false>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE>;
   constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
   cudaError_t e = set_smem(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
-  e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s, maps, a);
+  e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), bytes, s, maps, a);
   if (e != cudaSuccess || a.ticket) return e;
   rglru_dlambda_kernel<<<(a.D + 255) / 256, 256, 0, s>>>(a.dlam_part, a.lambda, a.dlambda, a.B, a.D, a.c);
   return cudaGetLastError();
@@ -1658,7 +1682,7 @@ static cudaError_t launch_bwd_io(bool use_tma, int variant, const BwdMaps& maps,
   switch (variant) {
     case 1: return launch_bwd_t<IO, Shape64x16x4, H ? 6 : 3, true>(maps, a, s);
     case 2: return launch_bwd_t<IO, Shape32x16x4, H ? 4 : 3, true>(maps, a, s);
-    case 3: return launch_bwd_t<IO, Shape32x16x4, 3, true>(maps, a, s);
+    case 3: return launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
     default: return launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
   }
 }
