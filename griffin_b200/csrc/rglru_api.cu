@@ -65,7 +65,7 @@ static EncodeTiledFn encode_fn() {
 
 // 3-D map over a dense [B, T, D] tensor with a [1, rows, cols] box; out-of-range parts
 // of a box read as zero and are dropped on store.
-static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols) {
+static bool encode_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const size_t es = bf16 ? 2 : 4;
@@ -78,6 +78,43 @@ static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T
                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+// A tensor map is a pure function of (base address, element type, shape, box), and a training loop calls with
+// the same handful of buffers step after step (the caching allocator hands the same blocks back), so encoded
+// maps are kept in a small per-thread table: a hit costs a compare and a 128-byte copy instead of a driver call
+// per map (seven to nine of them per backward call).
+struct MapKey {
+  const void* base;
+  int B, T, D, rows, cols, bf16;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && B == o.B && T == o.T && D == o.D && rows == o.rows && cols == o.cols && bf16 == o.bf16;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int MAP_CACHE_SLOTS = 256;   // direct-mapped
+
+static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols) {
+  static thread_local MapSlot table[MAP_CACHE_SLOTS] = {};
+  const MapKey key{base, B, T, D, rows, cols, bf16 ? 1 : 0};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 8;
+  h ^= (static_cast<uint64_t>(rows) << 3) ^ (static_cast<uint64_t>(cols) << 11) ^ (static_cast<uint64_t>(D) << 17) ^
+       (static_cast<uint64_t>(T) << 29) ^ (static_cast<uint64_t>(B) << 41);
+  h ^= h >> 29;
+  MapSlot& slot = table[(h * 0x9E3779B97F4A7C15ull) >> 56];
+  if (slot.used && slot.key == key) {
+    *map = slot.map;
+    return true;
+  }
+  if (!encode_map(map, base, bf16, B, T, D, rows, cols)) return false;
+  slot.key = key;
+  slot.map = *map;
+  slot.used = true;
+  return true;
 }
 
 static bool aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) % n) == 0; }

@@ -95,6 +95,21 @@ __device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ void bar_compute(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
+// The same barrier with an AND vote over its `nthreads` participants.
+__device__ __forceinline__ bool bar_compute_and(int nthreads, bool pred) {
+  uint32_t all;
+  asm volatile(
+      "{\n"
+      " .reg .pred pin, pout;\n"
+      " setp.ne.u32 pin, %2, 0;\n"
+      " bar.red.and.pred pout, 1, %1, pin;\n"
+      " selp.u32 %0, 1, 0, pout;\n"
+      "}\n"
+      : "=r"(all)
+      : "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return all != 0;
+}
 // Named barrier 2: compute warps and the producer warp together (nthreads counts all of them).
 __device__ __forceinline__ void bar_all(int nthreads) {
   __syncwarp();

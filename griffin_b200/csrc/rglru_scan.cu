@@ -32,6 +32,7 @@
 // The file also holds the raw affine scan operator (triton_scan.py:274-276), the
 // TMA-staged kernels of the conv alone, and the self-test of the bounded wait.
 
+#include <atomic>
 #include <cstdlib>
 
 #include "rglru_device.cuh"
@@ -300,7 +301,7 @@ struct FwdSmem {
 // no compute warp ever waits on the copy engine's instruction latency.
 // MERGE: the kernel also reads the pre-activation of the block's GeLU branch and writes
 // h_t * gelu(branch_t) (griffin/griffin.py:464, 520 of the reference) instead of h_t.
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false>
 __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFwdArgs& p) {
   using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
@@ -326,39 +327,40 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   const int rcol = GROUPED ? grouped_col(d0, p.gate_bw) : d0;   // first column of this tile's u_r / u_i
   const int icol = GROUPED ? rcol + p.gate_bw : d0;
 
+  auto issue = [&](int k) {
+    const int sidx = k % NSTAGE;
+    uint8_t* st = smem + sidx * SM::STAGE;
+    mbar_expect_tx(&full[sidx], SM::STAGE);
+    tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
+    tma_load_3d(st + SM::TILEX, &maps.ur, rcol, k * TC, b, &full[sidx]);
+    tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, icol, k * TC, b, &full[sidx]);
+    if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
+  };
+  // Set-up by the thread that will issue the bulk copies, published by one early CTA barrier; after it the
+  // producer warp and the compute warps go their own ways (the compute warps vote among themselves), so the
+  // first loads are issued while the per-channel rates are worked out and nobody waits for the issuing thread.
   pdl_launch_dependents();
-  if (tid == 0) {
+  if (USE_TMA ? (tid == NCOMP) : (tid == 0)) {
     *dead = 0;
     if (USE_TMA) {
       for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
       mbar_fence_init();
+      prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
+      if (MERGE) prefetch_map(&maps.g);
     }
   }
+  __syncthreads();
   pdl_wait();   // nothing above touches global memory; everything below may depend on the previous kernel
-  float2 K[2];
-  {
-    const int d = d0 + vec * CV;
-    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
-    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
-  }
-  const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
   if (USE_TMA && tid >= NCOMP) {
     // ---- producer warp: loads run NSTAGE-1 chunks ahead; a stage is refilled as soon as the
     // store of the results written into it has drained from shared memory.
     if (tid == NCOMP) {
-      prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
-      if (MERGE) prefetch_map(&maps.g);
-      auto issue = [&](int k) {
-        const int sidx = k % NSTAGE;
-        uint8_t* st = smem + sidx * SM::STAGE;
-        mbar_expect_tx(&full[sidx], SM::STAGE);
-        tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
-        tma_load_3d(st + SM::TILEX, &maps.ur, rcol, k * TC, b, &full[sidx]);
-        tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, icol, k * TC, b, &full[sidx]);
-        if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
-      };
-      for (int k = 0; k < NSTAGE && k < nchunks; ++k) issue(k);
+      // Every CTA of the grid starts at once and asks for NSTAGE chunks; the first chunk is asked for alone and
+      // the rest once it has landed, so that no CTA's first chunk queues behind other CTAs' later ones.
+      issue(0);
+      mbar_wait_or_flag(&full[0], 0, dead, p.status, DEV_TIMEOUT_LOAD);
+      for (int k = 1; k < NSTAGE && k < nchunks; ++k) issue(k);
       for (int k = 0; k < nchunks; ++k) {
         const int sidx = k % NSTAGE;
         mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
@@ -373,6 +375,14 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
     }
     return;
   }
+
+  float2 K[2];
+  {
+    const int d = d0 + vec * CV;
+    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
+    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
+  }
+  const bool poly = bar_compute_and(NCOMP, fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
   if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && p.ticket) *p.ticket = 0u;   // consumed by the backward kernel
 
@@ -393,7 +403,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
     uint8_t* tiles = smem + stage * SM::STAGE;
     const int t0 = k * TC;
     uint32_t fl[(TS + 3) / 4];
-    const bool masked = (p.tok != nullptr) || (t0 + TC > p.T);
+    const bool masked = !PLAIN && ((p.tok != nullptr) || (t0 + TC > p.T));
     if (masked) load_flags<TS>(p.tok, b, p.T, t0 + lane_t * TS, fl);
 
     if (USE_TMA) {
@@ -480,10 +490,11 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   if (tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;
 }
 
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED>
+// PLAIN: no token flags and a whole number of chunks, so the masked arithmetic is not compiled in.
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
-  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED>(maps, p);
+  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED, PLAIN>(maps, p);
 }
 // The same kernel capped at 96 registers, which lets two 9-warp CTAs share an SM's register files (five warps
 // on one scheduler partition).  Used for the merged / grouped variants, which otherwise take about 112.
@@ -510,7 +521,7 @@ struct BwdRegs {
 };
 
 // Level one of the backward chunk: gate math, coefficients for the second pass, and the
-// lane aggregates.  aggF = (prod a, local state), aggR = (prod a, local reverse carry),
+// lane aggregates: prod a, the local state, and the local reverse carry,
 // where the reverse carry is a_t g_t flowing from step t to step t-1.
 // MERGE: the incoming gradient is that of h * gelu(branch).  This pass turns it into the gradient of h
 // (kept, rounded to the I/O type, where the incoming gradient was) and leaves d_out * gelu'(branch) in the
@@ -565,7 +576,9 @@ __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8
       const float2 nrs2 = make_float2(-fminf(rs.x, 2.0f * SLOPE_CAP), -fminf(rs.y, 2.0f * SLOPE_CAP));
       const float2 ix = mul2(i, xv[cp]);
       float2 am = a, ar = a;
-      float2 c3 = mul2(mul2(a, a), mul2(nrs2, ix));   // stored negated
+      // slope term of d log a, stored negated: -2 a^2 slope i x.  Unmasked, one factor a is left to the second
+      // pass, which has a g at hand as the reverse carry.
+      float2 c3 = MASKED ? mul2(mul2(a, a), mul2(nrs2, ix)) : mul2(a, mul2(nrs2, ix));
       if (MASKED) {
         const float kl = m.keep * m.live;
         am = fma2(mul2(a, f2(m.keep)), f2(m.live), f2(1.0f - m.live));
@@ -576,7 +589,7 @@ __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8
       const float2 c1 = mul2(gam, i);
       const float2 bb = mul2(gam, ix);
       R.am[st][cp] = am;
-      R.ar[st][cp] = ar;
+      if (MASKED) R.ar[st][cp] = ar;
       R.c1[st][cp] = c1;
       R.c2[st][cp] = mul2(bb, fma2(i, f2(-1.0f), f2(1.0f)));
       R.c3[st][cp] = c3;
@@ -598,6 +611,66 @@ __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8
   for (int cp = 0; cp < 2; ++cp) { prod[cp] = p[cp]; sfwd[cp] = s[cp]; crev[cp] = c[cp]; }
 }
 
+// Second pass of the backward chunk: with the state `hin` entering the thread's first step and the reverse
+// carry `cin` entering its last, rebuild the states, run the reverse recurrence and write dx, du_r, du_i (and,
+// merged, the branch gradient) over the input tiles.  MASKED = false is the path of a thread whose tokens are
+// all ordinary: the decay that takes the gradient is the decay itself, so R.ar is not read.  The incoming
+// gradient is read back from its tile unless the merged variant replaced it in registers.
+template <typename IO, int TS, int CH, bool MASKED, bool CONV, bool MERGE>
+__device__ __forceinline__ void bwd_apply(uint8_t* tiles, int off_dx, int off_dr, int off_di, int off_g, int off0,
+                                          const float2 (&K)[2], const float2 (&hin)[2], const float2 (&cin)[2],
+                                          BwdRegs<IO, TS>& R, float2 (&dlam)[2]) {
+  constexpr int ROWB = CH * sizeof(IO);
+  float2 h[2] = {hin[0], hin[1]};
+  float2 c[2] = {cin[0], cin[1]};
+  // States entering each step, rebuilt forward in time.
+#pragma unroll
+  for (int st = 0; st < TS; ++st) {
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {
+      const float2 hprev = h[cp];
+      h[cp] = fma2(R.am[st][cp], hprev, R.hb[st][cp]);
+      R.hb[st][cp] = hprev;
+    }
+    if (MERGE) {   // d branch_t = d_out_t * gelu'(branch_t) * h_t, the first two factors left by the first pass
+      uint8_t* tq = tiles + off_g + off0 + st * ROWB;
+      float2 q[2];
+      Pack<IO>::unpack2(Pack<IO>::load(tq), q);
+      q[0] = mul2(q[0], h[0]);
+      q[1] = mul2(q[1], h[1]);
+      Pack<IO>::store2(tq, q);
+    }
+  }
+  uint8_t* tdx = tiles + off_dx;   // over x (past its halo rows)
+  uint8_t* tdr = tiles + off_dr;   // over u_r
+  uint8_t* tdi = tiles + off_di;   // over u_i
+  const float2 nK[2] = {mul2(K[0], f2(-1.0f)), mul2(K[1], f2(-1.0f))};
+#pragma unroll
+  for (int st = TS - 1; st >= 0; --st) {
+    const int off = off0 + st * ROWB;
+    float2 dyv[2], dxv[2], drv[2], div[2];
+    if (MERGE) Pack<IO>::unpack2(R.dy[st], dyv);
+    else Pack<IO>::unpack2(Pack<IO>::load(tiles + off), dyv);
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp) {
+      const float2 g = add2(dyv[cp], c[cp]);
+      c[cp] = mul2(R.am[st][cp], g);
+      dxv[cp] = mul2(g, R.c1[st][cp]);
+      div[cp] = mul2(g, R.c2[st][cp]);
+      // d log a = g a (h_prev + c3 / a); unmasked, g a is the reverse carry just formed and c3 came divided by a
+      const float2 dl = MASKED ? mul2(g, fma2(R.hb[st][cp], R.ar[st][cp], R.c3[st][cp]))
+                               : mul2(c[cp], add2(R.hb[st][cp], R.c3[st][cp]));
+      const float2 w = mul2(dl, R.rr[st][cp]);
+      dlam[cp] = add2(dlam[cp], w);
+      // d u_r = dl * d(log a)/d u_r = dl * (-K) r (1 - r) with K = -c logsigmoid(Lambda) >= 0
+      drv[cp] = mul2(w, fma2(K[cp], R.rr[st][cp], nK[cp]));
+    }
+    Pack<IO>::store2(tdx + off, dxv);
+    Pack<IO>::store2(tdr + off, drv);
+    Pack<IO>::store2(tdi + off, div);
+  }
+}
+
 template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool CONV = false, bool MERGE = false>
 struct BwdSmem {
   static constexpr int TC = LANES * TS;
@@ -607,31 +680,41 @@ struct BwdSmem {
   static constexpr int OFF_X = TILE, OFF_UR = TILE + TILEX, OFF_UI = 2 * TILE + TILEX;   // after the dy tile
   static constexpr int OFF_G = 3 * TILE + TILEX;                // GeLU-branch tile of the merged variant
   static constexpr int STAGE = 3 * TILE + TILEX + (MERGE ? TILE : 0);
-  static constexpr int OFF_AGGF = NSTAGE * STAGE;
-  static constexpr int OFF_AGGR = OFF_AGGF + ChainSmem<LANES, CH>::AGG;
-  static constexpr int OFF_EINF = OFF_AGGR + ChainSmem<LANES, CH>::AGG;
-  static constexpr int OFF_EINR = OFF_EINF + ChainSmem<LANES, CH>::EIN;
-  static constexpr int OFF_BAR = OFF_EINR + ChainSmem<LANES, CH>::EIN;   // full[NSTAGE], ready[NSTAGE], dead flag
+  // Lane aggregates as three float planes [LANES][CH]: decay product, local state, local reverse carry.
+  static constexpr int PLANE = LANES * CH * 4;
+  static constexpr int OFF_AGGP = NSTAGE * STAGE;
+  static constexpr int OFF_AGGS = OFF_AGGP + PLANE;
+  static constexpr int OFF_AGGC = OFF_AGGS + PLANE;
+  static constexpr int OFF_EINF = OFF_AGGC + PLANE;
+  static constexpr int OFF_EINR = OFF_EINF + PLANE;
+  static constexpr int OFF_BAR = OFF_EINR + PLANE;   // full[NSTAGE], ready[NSTAGE], dead flag
   static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
-// SELF_ISSUE: no producer warp; thread 0 of the compute warps issues the bulk copies at chunk boundaries (one
-// more CTA barrier per chunk).  Eight warps instead of nine put two warps on every scheduler partition, which
-// lifts the register limit of a thread from 168 to 255.
+// SELF_ISSUE: no producer warp.  One thread of the last compute warp (not a chain thread) issues the bulk
+// copies right after the first barrier of a chunk: by then every thread has finished, and fenced, the results
+// of the chunk before, so that chunk's tiles can leave and the stage of the chunk before it, whose store has
+// been read out of shared memory by now, can be refilled.  No barrier is added; loads run NSTAGE - 2 chunks
+// ahead.  A whole number of warps per scheduler partition leaves every thread 128 registers at 512 threads.
+// PLAIN: the caller passed no token flags and the sequence is a whole number of chunks, so no step is ever
+// masked; the masked arithmetic is not compiled in (half the code, and registers allotted for this path alone).
 template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED,
-          bool SELF_ISSUE = false>
-__global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), 1)
+          bool SELF_ISSUE = false, bool PLAIN = false>
+__global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0),
+                                  (SELF_ISSUE && CH == 32) ? 2 : 1)
     rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
   using SM = BwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
   static_assert(TC % SAVE_EVERY == 0, "backward chunks must start on a saved state");
+  static_assert(!SELF_ISSUE || !USE_TMA || NSTAGE >= 3, "without a producer warp a stage is refilled two chunks after its use");
   constexpr int ROWB = CH * sizeof(IO);
   constexpr int NCOMP = LANES * NCV;
   extern __shared__ __align__(128) uint8_t smem[];
-  float2* aggF = reinterpret_cast<float2*>(smem + SM::OFF_AGGF);
-  float2* aggR = reinterpret_cast<float2*>(smem + SM::OFF_AGGR);
+  float* aggP = reinterpret_cast<float*>(smem + SM::OFF_AGGP);
+  float* aggS = reinterpret_cast<float*>(smem + SM::OFF_AGGS);
+  float* aggC = reinterpret_cast<float*>(smem + SM::OFF_AGGC);
   float* einF = reinterpret_cast<float*>(smem + SM::OFF_EINF);
   float* einR = reinterpret_cast<float*>(smem + SM::OFF_EINR);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::OFF_BAR);
@@ -648,23 +731,6 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   static_assert(!GROUPED || USE_TMA, "the grouped gate layout is staged by TMA only");
   const int rcol = GROUPED ? grouped_col(d0, p.gate_bw) : d0;   // first column of this tile's u_r / u_i (and du_r / du_i)
   const int icol = GROUPED ? rcol + p.gate_bw : d0;
-
-  pdl_launch_dependents();
-  if (tid == 0) {
-    *dead = 0;
-    if (USE_TMA) {
-      for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
-      mbar_fence_init();
-    }
-  }
-  pdl_wait();   // nothing above touches global memory; everything below may depend on the previous kernel
-  float2 K[2];
-  {
-    const int d = d0 + vec * CV;
-    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
-    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
-  }
-  const bool poly = __syncthreads_and(fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
   auto issue = [&](int q) {  // q-th chunk in processing order == chunk nchunks-1-q in time
     const int k = nchunks - 1 - q;
@@ -686,16 +752,33 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
     tma_commit();
   };
-  if (USE_TMA && SELF_ISSUE && tid == 0)
-    for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
+  // Set-up by the thread that will issue the bulk copies (the producer warp's first lane, or with SELF_ISSUE
+  // the first lane of the last compute warp), published by one early CTA barrier; after it the producer warp
+  // and the compute warps go their own ways (the compute warps vote among themselves), so the first loads are
+  // issued while the per-channel rates are worked out.
+  const bool issuer = USE_TMA && tid == (SELF_ISSUE ? NCOMP - 32 : NCOMP);
+  const bool self_issuer = SELF_ISSUE && issuer;
+  pdl_launch_dependents();
+  if (USE_TMA ? issuer : (tid == 0)) {
+    *dead = 0;
+    if (USE_TMA) {
+      for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full[s], 1); mbar_init(&ready[s], NCOMP / 32); }
+      mbar_fence_init();
+      prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
+      prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
+      if (MERGE) { prefetch_map(&maps.g); prefetch_map(&maps.dg); }
+    }
+  }
+  __syncthreads();
+  pdl_wait();   // nothing above touches global memory; everything below may depend on the previous kernel
 
   if (USE_TMA && !SELF_ISSUE && tid >= NCOMP) {
     // ---- producer warp (chunks are walked from the end of the sequence to its start)
     if (tid == NCOMP) {
-      prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
-      prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
-      if (MERGE) { prefetch_map(&maps.g); prefetch_map(&maps.dg); }
-      for (int q = 0; q < NSTAGE && q < nchunks; ++q) issue(q);
+      // the first chunk is asked for alone, the rest once it has landed (see the forward kernel)
+      issue(0);
+      mbar_wait_or_flag(&full[0], 0, dead, p.status, DEV_TIMEOUT_LOAD);
+      for (int q = 1; q < NSTAGE && q < nchunks; ++q) issue(q);
       for (int q = 0; q < nchunks; ++q) {
         const int sidx = q % NSTAGE;
         mbar_wait_or_flag(&ready[sidx], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
@@ -709,6 +792,15 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     }
     return;
   }
+
+  if (self_issuer) issue(0);    // the first chunk before this thread's share of the prologue, the rest after it
+  float2 K[2];
+  {
+    const int d = d0 + vec * CV;
+    K[0] = make_float2(decay_rate(p.lambda, d, p.D, p.c), decay_rate(p.lambda, d + 1, p.D, p.c));
+    K[1] = make_float2(decay_rate(p.lambda, d + 2, p.D, p.c), decay_rate(p.lambda, d + 3, p.D, p.c));
+  }
+  const bool poly = bar_compute_and(NCOMP, fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
   // Threads 0..63 chain the forward lane aggregates, threads 64..127 the reverse ones.
   const int cch = tid & (CH - 1);
@@ -732,7 +824,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     uint8_t* tiles = smem + stage * SM::STAGE;
     const int t0 = k * TC;
     uint32_t fl[(TS + 3) / 4];
-    const bool masked = (p.tok != nullptr) || (t0 + TC > p.T);
+    const bool masked = !PLAIN && ((p.tok != nullptr) || (t0 + TC > p.T));
     if (masked) load_flags<TS>(p.tok, b, p.T, t0 + lane_t * TS, fl);
 
     // State entering this chunk (saved by the forward kernel; chunk 0 starts from h0).
@@ -744,6 +836,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
 
     if (USE_TMA) {
       mbar_wait_or_flag(&full[stage], (q / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_LOAD);
+      if (self_issuer && q == 0)      // the first chunk was asked for alone; now that it has landed, the rest
+        for (int qq = 1; qq < NSTAGE && qq < nchunks; ++qq) issue(qq);
     } else {
       tile_load_plain<IO, CH>(tiles, p.dy, b, t0, d0, TC, p.T, p.D);
       tile_load_plain<IO, CH>(tiles + SM::OFF_X, p.x, b, t0 - (CONV ? 3 : 0), d0, TC + (CONV ? 3 : 0), p.T, p.D);
@@ -755,6 +849,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
 
     BwdRegs<IO, TS> R;
     float2 prod[2], sfwd[2], crev[2];
+    const bool flagged = masked && any_flag(fl);
     {
       uint8_t* tdy = tiles;
       uint8_t* tg = tiles + SM::OFF_G;
@@ -767,7 +862,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
         load_hist<IO>(p.conv_state, b, d0 + vec * CV, p.D, hist_v);
         hist = hist_v;
       }
-      if (masked && any_flag(fl)) {
+      if (flagged) {
         if (poly) bwd_local<IO, TS, CH, true, true, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
         else bwd_local<IO, TS, CH, true, false, CONV, MERGE, GROUPED>(tdy, tg, tx, tr, ti, off0, K, fl, ct, hist, gb, R, prod, sfwd, crev);
       } else {
@@ -776,99 +871,55 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
       }
     }
     {
-      float4* df = reinterpret_cast<float4*>(aggF + lane_t * CH + vec * CV);
-      df[0] = make_float4(prod[0].x, sfwd[0].x, prod[0].y, sfwd[0].y);
-      df[1] = make_float4(prod[1].x, sfwd[1].x, prod[1].y, sfwd[1].y);
-      float4* dr = reinterpret_cast<float4*>(aggR + lane_t * CH + vec * CV);
-      dr[0] = make_float4(prod[0].x, crev[0].x, prod[0].y, crev[0].y);
-      dr[1] = make_float4(prod[1].x, crev[1].x, prod[1].y, crev[1].y);
+      const int ao = lane_t * CH + vec * CV;
+      *reinterpret_cast<float4*>(aggP + ao) = make_float4(prod[0].x, prod[0].y, prod[1].x, prod[1].y);
+      *reinterpret_cast<float4*>(aggS + ao) = make_float4(sfwd[0].x, sfwd[0].y, sfwd[1].x, sfwd[1].y);
+      *reinterpret_cast<float4*>(aggC + ao) = make_float4(crev[0].x, crev[0].y, crev[1].x, crev[1].y);
     }
     bar_compute(NCOMP);
+    if (self_issuer && q >= 1) {
+      store(q - 1);
+      if (q >= 2 && q - 2 + NSTAGE < nchunks) {
+        tma_wait_read<1>();      // all but the store just committed have been read out: the stage of chunk q-2 is free
+        issue(q - 2 + NSTAGE);
+      }
+    }
 
-    if (fwd_chain) {
-      float2 ag[LANES];
+    if (fwd_chain || rev_chain) {
+      const float* plane = fwd_chain ? aggS : aggC;
+      float* ein = fwd_chain ? einF : einR;
+      float ap[LANES], as[LANES];
 #pragma unroll
-      for (int j = 0; j < LANES; ++j) ag[j] = aggF[j * CH + cch];
-      float e = enter;
+      for (int j = 0; j < LANES; ++j) { ap[j] = aggP[j * CH + cch]; as[j] = plane[j * CH + cch]; }
+      if (fwd_chain) {
+        float e = enter;
 #pragma unroll
-      for (int j = 0; j < LANES; ++j) {
-        einF[j * CH + cch] = e;
-        e = fmaf(ag[j].x, e, ag[j].y);
+        for (int j = 0; j < LANES; ++j) {
+          ein[j * CH + cch] = e;
+          e = fmaf(ap[j], e, as[j]);
+        }
+      } else {
+        float e = carry_rev;
+#pragma unroll
+        for (int j = LANES - 1; j >= 0; --j) {
+          ein[j * CH + cch] = e;
+          e = fmaf(ap[j], e, as[j]);
+        }
+        carry_rev = e;
       }
-    } else if (rev_chain) {
-      float2 ag[LANES];
-#pragma unroll
-      for (int j = 0; j < LANES; ++j) ag[j] = aggR[j * CH + cch];
-      float e = carry_rev;
-#pragma unroll
-      for (int j = LANES - 1; j >= 0; --j) {
-        einR[j * CH + cch] = e;
-        e = fmaf(ag[j].x, e, ag[j].y);
-      }
-      carry_rev = e;
     }
     bar_compute(NCOMP);
 
     {
       const float4 f4 = *reinterpret_cast<const float4*>(einF + lane_t * CH + vec * CV);
       const float4 r4 = *reinterpret_cast<const float4*>(einR + lane_t * CH + vec * CV);
-      float2 h[2] = {make_float2(f4.x, f4.y), make_float2(f4.z, f4.w)};
-      float2 c[2] = {make_float2(r4.x, r4.y), make_float2(r4.z, r4.w)};
-      // States entering each step, rebuilt forward in time.
-#pragma unroll
-      for (int st = 0; st < TS; ++st) {
-#pragma unroll
-        for (int cp = 0; cp < 2; ++cp) {
-          const float2 hin = h[cp];
-          h[cp] = fma2(R.am[st][cp], hin, R.hb[st][cp]);
-          R.hb[st][cp] = hin;
-        }
-        if (MERGE) {   // d branch_t = d_out_t * gelu'(branch_t) * h_t, the first two factors left by the first pass
-          uint8_t* tq = tiles + SM::OFF_G + off0 + st * ROWB;
-          float2 q[2];
-          Pack<IO>::unpack2(Pack<IO>::load(tq), q);
-          q[0] = mul2(q[0], h[0]);
-          q[1] = mul2(q[1], h[1]);
-          Pack<IO>::store2(tq, q);
-        }
-      }
-      uint8_t* tdx = tiles + SM::OFF_X + SM::HALO;   // over x (past its halo rows)
-      uint8_t* tdr = tiles + SM::OFF_UR;             // over u_r
-      uint8_t* tdi = tiles + SM::OFF_UI;             // over u_i
-      const float2 nK[2] = {mul2(K[0], f2(-1.0f)), mul2(K[1], f2(-1.0f))};
-#pragma unroll
-      for (int st = TS - 1; st >= 0; --st) {
-        float2 dyv[2], dxv[2], drv[2], div[2];
-        Pack<IO>::unpack2(R.dy[st], dyv);
-#pragma unroll
-        for (int cp = 0; cp < 2; ++cp) {
-          const float2 g = add2(dyv[cp], c[cp]);
-          c[cp] = mul2(R.am[st][cp], g);
-          dxv[cp] = mul2(g, R.c1[st][cp]);
-          div[cp] = mul2(g, R.c2[st][cp]);
-          const float2 dl = mul2(g, fma2(R.hb[st][cp], R.ar[st][cp], R.c3[st][cp]));   // c3 is stored negated
-          const float2 w = mul2(dl, R.rr[st][cp]);
-          dlam[cp] = add2(dlam[cp], w);
-          // d u_r = dl * d(log a)/d u_r = dl * (-K) r (1 - r) with K = -c logsigmoid(Lambda) >= 0
-          drv[cp] = mul2(w, fma2(K[cp], R.rr[st][cp], nK[cp]));
-        }
-        const int off = off0 + st * ROWB;
-        Pack<IO>::store2(tdx + off, dxv);
-        Pack<IO>::store2(tdr + off, drv);
-        Pack<IO>::store2(tdi + off, div);
-      }
+      const float2 hin[2] = {make_float2(f4.x, f4.y), make_float2(f4.z, f4.w)};
+      const float2 cin[2] = {make_float2(r4.x, r4.y), make_float2(r4.z, r4.w)};
+      if (flagged) bwd_apply<IO, TS, CH, true, CONV, MERGE>(tiles, SM::OFF_X + SM::HALO, SM::OFF_UR, SM::OFF_UI, SM::OFF_G, off0, K, hin, cin, R, dlam);
+      else bwd_apply<IO, TS, CH, false, CONV, MERGE>(tiles, SM::OFF_X + SM::HALO, SM::OFF_UR, SM::OFF_UI, SM::OFF_G, off0, K, hin, cin, R, dlam);
     }
     if (USE_TMA && SELF_ISSUE) {
-      fence_async_smem();
-      bar_compute(NCOMP);          // every thread's results are in the stage
-      if (tid == 0) {
-        store(q);
-        // the stage of the previous chunk is free once its store (the group before this one) has been read
-        if (q >= 1 && q - 1 + NSTAGE < nchunks) {
-          tma_wait_read<1>();
-          issue(q - 1 + NSTAGE);
-        }
-      }
+      fence_async_smem();          // the stage leaves after the next barrier all threads pass
     } else if (USE_TMA) {
       fence_async_smem();
       __syncwarp();
@@ -883,11 +934,14 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     }
   }
 
-  if (USE_TMA && SELF_ISSUE && tid == 0) tma_wait_all<0>();
   if (rev_chain && dch < p.D && p.dh0) p.dh0[static_cast<size_t>(b) * p.D + dch] = carry_rev;
 
   // Per-row partial of sum_t dl * r: fold the time-lanes in a fixed order.
   bar_compute(NCOMP);
+  if (self_issuer) {             // the last chunk's results
+    store(nchunks - 1);
+    tma_wait_all<0>();
+  }
   *reinterpret_cast<float4*>(einF + lane_t * CH + vec * CV) = make_float4(dlam[0].x, dlam[0].y, dlam[1].x, dlam[1].y);
   bar_compute(NCOMP);
   if (tid < CH && dch < p.D) {
@@ -910,11 +964,35 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   bar_compute(NCOMP);
   if (!s_last) return;
   __threadfence();
-  for (int d = tid; d < p.D; d += NCOMP) {
-    float acc = 0.0f;
-    for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + d);
-    const float lam = p.lambda[d];
-    p.dlambda[d] = (1.0f / (1.0f + expf(lam))) * p.c * acc;
+  // Rows are added in index order whatever the load order; loads go out eight rows at a time so that the
+  // fold costs a few round trips to L2, not one per row.
+  if ((p.D & 3) == 0) {
+    for (int d = tid * 4; d < p.D; d += NCOMP * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; r0 < p.B; r0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(p.dlam_part + static_cast<size_t>(r0 + j) * p.D + d))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+      }
+      const float4 lam = *reinterpret_cast<const float4*>(p.lambda + d);
+      float4 out;
+      out.x = (1.0f / (1.0f + expf(lam.x))) * p.c * acc.x;
+      out.y = (1.0f / (1.0f + expf(lam.y))) * p.c * acc.y;
+      out.z = (1.0f / (1.0f + expf(lam.z))) * p.c * acc.z;
+      out.w = (1.0f / (1.0f + expf(lam.w))) * p.c * acc.w;
+      *reinterpret_cast<float4*>(p.dlambda + d) = out;
+    }
+  } else {
+    for (int d = tid; d < p.D; d += NCOMP) {
+      float acc = 0.0f;
+      for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + d);
+      const float lam = p.lambda[d];
+      p.dlambda[d] = (1.0f / (1.0f + expf(lam))) * p.c * acc;
+    }
   }
   if (tid == 0) *p.ticket = 0u;
 }
@@ -1558,47 +1636,44 @@ cudaError_t launch_wait_selftest(int* status, int* finished, long long limit_cyc
 // ======================================================================
 
 // CTA shapes.  CH channels x (LANES * TS) time-steps per chunk, LANES * CH / 4 compute threads.
-//   64 x 64 : the default; grids large enough to put two or more CTAs on every SM.
-//   32 x .. : half-width tiles double the number of CTAs for small grids, so that two CTAs
-//             (two independent barrier domains) still share an SM and overlap their phases.
+//   64 x 64  : the default; grids large enough to put two or more forward CTAs on every SM.
+//   32 x 128 : half-width forward tiles double the number of CTAs for small grids, so that two CTAs
+//              (two independent barrier domains) still share an SM and overlap their phases.
 struct Shape64x16x4 { static constexpr int CH = 64, LANES = 16, TS = 4; };
-struct Shape64x32x4 { static constexpr int CH = 64, LANES = 32, TS = 4; };
 struct Shape32x32x4 { static constexpr int CH = 32, LANES = 32, TS = 4; };
-struct Shape32x16x4 { static constexpr int CH = 32, LANES = 16, TS = 4; };
-struct Shape64x32x2 { static constexpr int CH = 64, LANES = 32, TS = 2; };
 
-constexpr int NUM_VARIANTS = 4;
-static const int kFwdRows[NUM_VARIANTS] = {64, 64, 128, 64};
-static const int kFwdCols[NUM_VARIANTS] = {64, 64, 32, 32};
-static const int kBwdRows[NUM_VARIANTS] = {64, 64, 64, 64};
-static const int kBwdCols[NUM_VARIANTS] = {64, 64, 32, 64};
+// Kernel variants.  Forward: 0 = 64 x 64 tiles, 2 = 32 x 128 tiles.  Backward: 0 = 64 x 64 tiles with a
+// producer warp, 3 = the same tiles with the bulk copies issued by a compute thread (SELF_ISSUE).  The numbers
+// are what RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT accept (they force one variant for a whole process; the
+// test-suite uses them to run every variant over the parity cases); anything else means "choose by shape".
+static bool fwd_variant_exists(int v) { return v == 0 || v == 2; }
+static bool bwd_variant_exists(int v) { return v == 0 || v == 3; }
 
-int scan_fwd_box_rows(int v) { return kFwdRows[v]; }
-int scan_fwd_box_cols(int v) { return kFwdCols[v]; }
-int scan_bwd_box_rows(int v) { return kBwdRows[v]; }
-int scan_bwd_box_cols(int v) { return kBwdCols[v]; }
+int scan_fwd_box_rows(int v) { return v == 2 ? 128 : 64; }
+int scan_fwd_box_cols(int v) { return v == 2 ? 32 : 64; }
+int scan_bwd_box_rows(int) { return 64; }
+int scan_bwd_box_cols(int) { return 64; }
 
 static int env_override(const char* name) {
   const char* v = getenv(name);
-  return (v && v[0] >= '0' && v[0] < '0' + NUM_VARIANTS) ? (v[0] - '0') : -1;
+  return (v && v[0] >= '0' && v[0] <= '9' && v[1] == 0) ? (v[0] - '0') : -1;
 }
 
-// RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT force a shape (for tuning runs).  Backward variant 3 is the 64 x 64
-// shape without the producer warp (SELF_ISSUE); measured on B200 it is as fast as variant 0, not faster.
-// Measured on B200: half-width forward tiles pay off for bf16 when 64-channel tiles cannot put two
-// CTAs on every SM (e.g. B=8, D=1024: 35 us against 43 us); for fp32 and for the backward kernel
-// (one CTA per SM by registers either way) the 64-channel shape is faster.
+// Measured on B200 (bf16, T = 2048, D = 1024): half-width forward tiles win while 64-channel tiles cannot fill
+// the 148 SMs (B = 8, 128 tiles: 31 us against 50 us) and lose once they can (B = 16: 58 us against 52 us); for
+// fp32 the 64-channel shape is faster throughout.  The backward runs one CTA per SM either way; without the
+// producer warp it is 1 to 2 % faster for bf16 tensors (eight warps leave every thread its registers).
 int scan_fwd_variant(int B, int T, int D, bool bf16) {
   static const int forced = env_override("RGLRU_FWD_VARIANT");
-  if (forced >= 0) return forced;
-  const long long ctas = static_cast<long long>(B) * ((D + 63) / 64);
-  return (bf16 && ctas < 2 * 148 && T >= 256) ? 2 : 0;
+  if (fwd_variant_exists(forced)) return forced;
+  const long long tiles = static_cast<long long>(B) * ((D + 63) / 64);
+  return (bf16 && tiles <= 160 && T >= 256) ? 2 : 0;
 }
 int scan_bwd_variant(int B, int T, int D, bool bf16) {
   static const int forced = env_override("RGLRU_BWD_VARIANT");
-  if (forced >= 0) return forced;
-  (void)B; (void)T; (void)D; (void)bf16;
-  return 0;
+  if (bwd_variant_exists(forced)) return forced;
+  (void)B; (void)T; (void)D;
+  return bf16 ? 3 : 0;
 }
 
 // Launch with programmatic stream serialization, so that this kernel's launch and prologue may overlap
@@ -1618,25 +1693,37 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, int threads, int bytes, cuda
   return cudaLaunchKernelEx(&cfg, kern, maps, a);
 }
 
-template <typename Kern>
+// Shared-memory attributes of one kernel: the largest carveout, so that occupancy is set by the kernel's own
+// footprint and not by the default L1 / shared split, and the dynamic size.  They are per device and do not
+// change, so each call site (one per kernel instantiation, told apart by TAG) sets them once per device.
+template <typename TAG, typename Kern>
 static cudaError_t set_smem(Kern kern, int bytes) {
-  // Ask for the largest shared-memory carveout so that occupancy is set by the kernel's own
-  // footprint, not by the default L1 / shared split.
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  static std::atomic<unsigned long long> done{0ull};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  const unsigned long long bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0ull;
+  if (bit && (done.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && bit) done.fetch_or(bit, std::memory_order_release);
+  return e;
 }
+template <typename... Ts> struct KernelTag {};
+template <int... Vs> struct IntTag {};
 
-template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false>
+template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false,
+          bool PLAIN = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
   constexpr bool CAPPED = USE_TMA && !CONV && (MERGE || GROUPED);
   void (*kern)(FwdMaps, ScanFwdArgs);
   if constexpr (CAPPED) kern = rglru_fwd_kernel_capped<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
-  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
+  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN>;
   constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
-  cudaError_t e = set_smem(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<FwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
   return launch_pdl(kern, grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s, maps, a);
@@ -1646,12 +1733,11 @@ template <typename IO>
 static cudaError_t launch_fwd_io(bool use_tma, int variant, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
   if (!use_tma) return launch_fwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
-  switch (variant) {
-    case 1: return launch_fwd_t<IO, Shape64x16x4, H ? 8 : 4, true>(maps, a, s);
-    case 2: return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true>(maps, a, s);
-    case 3: return launch_fwd_t<IO, Shape32x16x4, 4, true>(maps, a, s);
-    default: return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
-  }
+  const bool plain = a.tok == nullptr && a.T % 128 == 0;   // no step of any chunk is masked
+  if (plain && variant == 0) return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
+  if (plain && variant == 2) return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
+  if (variant == 2) return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true>(maps, a, s);
+  return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
 }
 
 cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps& maps, const ScanFwdArgs& a,
@@ -1660,13 +1746,13 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
 }
 
 template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false,
-          bool SELF_ISSUE = false>
+          bool SELF_ISSUE = false, bool PLAIN = false>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE>;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE, PLAIN>;
   constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
-  cudaError_t e = set_smem(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<BwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE, PLAIN>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
   e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), bytes, s, maps, a);
@@ -1679,12 +1765,13 @@ template <typename IO>
 static cudaError_t launch_bwd_io(bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
   if (!use_tma) return launch_bwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
-  switch (variant) {
-    case 1: return launch_bwd_t<IO, Shape64x16x4, H ? 6 : 3, true>(maps, a, s);
-    case 2: return launch_bwd_t<IO, Shape32x16x4, H ? 4 : 3, true>(maps, a, s);
-    case 3: return launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
-    default: return launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
+  const bool plain = a.tok == nullptr && a.T % 64 == 0;   // no step of any chunk is masked
+  if (variant == 3) {   // bulk copies issued by a compute thread: loads run NSTAGE - 2 chunks ahead, so one more stage
+    if (plain) return launch_bwd_t<IO, Shape64x16x4, H ? 5 : 3, true, false, false, false, true, true>(maps, a, s);
+    return launch_bwd_t<IO, Shape64x16x4, H ? 5 : 3, true, false, false, false, true>(maps, a, s);
   }
+  if (plain) return launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, false, true>(maps, a, s);
+  return launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
 }
 
 cudaError_t launch_scan_bwd(bool bf16, bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& a,
@@ -1702,7 +1789,7 @@ cudaError_t launch_conv_scan_fwd(bool bf16, bool use_tma, const FwdMaps& maps, c
 }
 cudaError_t launch_conv_scan_bwd(bool bf16, bool use_tma, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   if (bf16)
-    return use_tma ? launch_bwd_t<__nv_bfloat16, Shape64x16x4, 4, true, true>(maps, a, s)
+    return use_tma ? launch_bwd_t<__nv_bfloat16, Shape64x16x4, 4, true, true, false, false, true>(maps, a, s)
                    : launch_bwd_t<__nv_bfloat16, Shape64x16x4, 1, false, true>(maps, a, s);
   return use_tma ? launch_bwd_t<float, Shape64x16x4, 3, true, true>(maps, a, s)
                  : launch_bwd_t<float, Shape64x16x4, 1, false, true>(maps, a, s);
@@ -1719,8 +1806,11 @@ static cudaError_t launch_merge_fwd_t(bool use_tma, const FwdMaps& maps, const S
 template <typename IO, bool CONV>
 static cudaError_t launch_merge_bwd_t(bool use_tma, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
-  return use_tma ? launch_bwd_t<IO, Shape64x16x4, H ? 4 : 2, true, CONV, true>(maps, a, s)
-                 : launch_bwd_t<IO, Shape64x16x4, 1, false, CONV, true>(maps, a, s);
+  if (!use_tma) return launch_bwd_t<IO, Shape64x16x4, 1, false, CONV, true>(maps, a, s);
+  // bf16: four stages without a producer warp (eight warps leave these variants the registers they need);
+  // fp32 fits two stages only, which the producer warp needs to keep a load ahead
+  if constexpr (H) return launch_bwd_t<IO, Shape64x16x4, 4, true, CONV, true, false, true>(maps, a, s);
+  else return launch_bwd_t<IO, Shape64x16x4, 2, true, CONV, true>(maps, a, s);
 }
 cudaError_t launch_merge_fwd(bool bf16, bool use_tma, bool conv, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   if (bf16) return conv ? launch_merge_fwd_t<__nv_bfloat16, true>(use_tma, maps, a, s)
@@ -1743,7 +1833,8 @@ static cudaError_t launch_grouped_fwd_t(const FwdMaps& maps, const ScanFwdArgs& 
 template <typename IO, bool MERGE>
 static cudaError_t launch_grouped_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
-  return launch_bwd_t<IO, Shape64x16x4, H ? 4 : (MERGE ? 2 : 3), true, false, MERGE, true>(maps, a, s);
+  if constexpr (H) return launch_bwd_t<IO, Shape64x16x4, MERGE ? 4 : 5, true, false, MERGE, true, true>(maps, a, s);
+  else return launch_bwd_t<IO, Shape64x16x4, MERGE ? 2 : 3, true, false, MERGE, true>(maps, a, s);
 }
 cudaError_t launch_grouped_fwd(bool bf16, bool merge, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   if (bf16) return merge ? launch_grouped_fwd_t<__nv_bfloat16, true>(maps, a, s) : launch_grouped_fwd_t<__nv_bfloat16, false>(maps, a, s);
@@ -1762,7 +1853,7 @@ template <int NSTAGE, bool USE_TMA>
 static cudaError_t launch_raw_fwd_t(const RawFwdMaps& maps, const RawScanArgs& a, cudaStream_t s) {
   auto kern = rawscan_fwd_kernel<NSTAGE, USE_TMA>;
   constexpr int bytes = RawSmem<NSTAGE>::BYTES;
-  cudaError_t e = set_smem(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<RawFwdMaps, IntTag<NSTAGE, USE_TMA>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + CH - 1) / CH, a.B);
   kern<<<grid, RAW_NT, bytes, s>>>(maps, a);
@@ -1775,7 +1866,7 @@ template <int NSTAGE, bool USE_TMA>
 static cudaError_t launch_raw_bwd_t(const RawBwdMaps& maps, const RawScanArgs& a, cudaStream_t s) {
   auto kern = rawscan_bwd_kernel<NSTAGE, USE_TMA>;
   constexpr int bytes = RawSmem<NSTAGE>::BYTES;
-  cudaError_t e = set_smem(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<RawBwdMaps, IntTag<NSTAGE, USE_TMA>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + CH - 1) / CH, a.B);
   kern<<<grid, RAW_NT, bytes, s>>>(maps, a);
@@ -1793,7 +1884,7 @@ static cudaError_t conv_tma_fwd_t(const ConvMaps& maps, const ConvTmaArgs& a, cu
   constexpr int ST = sizeof(IO) == 2 ? 4 : 3;
   auto kern = conv_tma_fwd_kernel<IO, ST>;
   constexpr int bytes = ConvFwdSmem<IO, ST>::BYTES;
-  cudaError_t e = set_smem(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<ConvFwdSmem<IO, ST>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   kern<<<dim3((a.D + 63) / 64, a.B), 288, bytes, s>>>(maps, a);
   return cudaGetLastError();
@@ -1807,7 +1898,7 @@ static cudaError_t conv_tma_bwd_t(const ConvMaps& maps, const ConvTmaArgs& a, cu
   auto kern = conv_tma_bwd_kernel<IO, ST>;
   constexpr int bytes = ConvBwdSmem<IO, ST>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
-  cudaError_t e = set_smem(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<ConvBwdSmem<IO, ST>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   kern<<<dim3((a.D + 63) / 64, a.B), 288, bytes, s>>>(maps, a);
   return cudaGetLastError();

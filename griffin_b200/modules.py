@@ -104,19 +104,37 @@ def token_flags(batch: int, steps: int, device, *, reset: Optional[Tensor] = Non
 _PLAIN_FLAGS: dict = {}
 
 
+def _build_plain_flags(batch: int, steps: int, device) -> Tensor:
+    flags = torch.zeros(batch, steps, device=device, dtype=torch.uint8)
+    flags[:, 0] = 3 | _lib.TOK_RESET
+    if steps > 1:
+        flags[:, 1] = 2
+    if steps > 2:
+        flags[:, 2] = 1
+    return flags
+
+
 def _plain_flags(batch: int, steps: int, device) -> Tensor:
     """Flag bytes of rows that are one fresh document each (positions 0..T-1): a reset at token 0 and the first
-    three tokens short of taps.  Built once per (batch, steps, device) with device-side fills only (no host
-    copy, so the block can be captured into a CUDA graph) and shared read-only between calls."""
+    three tokens short of taps.  Built with device-side fills only (no host copy, so the block can be captured
+    into a CUDA graph), once per (batch, steps, device), and shared read-only between calls.
+
+    The shared tensor must be usable from any later context, so it is created as an ordinary tensor even when
+    the first caller runs under ``torch.inference_mode`` (an inference tensor could not be saved for a later
+    backward), the creating stream is drained once so that other streams may read it, and nothing is cached
+    while a CUDA graph is being captured (a tensor born in a capture belongs to the graph's memory pool and
+    holds data only after a replay): such calls get a tensor of their own."""
+    device = torch.device(device)
+    capturing = device.type == "cuda" and torch.cuda.is_current_stream_capturing()
     key = (batch, steps, str(device))
-    flags = _PLAIN_FLAGS.get(key)
+    flags = None if capturing else _PLAIN_FLAGS.get(key)
     if flags is None:
-        flags = torch.zeros(batch, steps, device=device, dtype=torch.uint8)
-        flags[:, 0] = 3 | _lib.TOK_RESET
-        if steps > 1:
-            flags[:, 1] = 2
-        if steps > 2:
-            flags[:, 2] = 1
+        with torch.inference_mode(False):
+            flags = _build_plain_flags(batch, steps, device)
+        if capturing:
+            return flags
+        if device.type == "cuda":
+            torch.cuda.current_stream(device).synchronize()
         if len(_PLAIN_FLAGS) > 64:
             _PLAIN_FLAGS.clear()
         _PLAIN_FLAGS[key] = flags

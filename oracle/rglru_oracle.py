@@ -263,6 +263,47 @@ def rglru_backward_linear(
     }
 
 
+class _CoreLinearBackward(torch.autograd.Function):
+    """``rglru_core`` as one autograd node whose backward is ``rglru_backward_linear``.
+
+    Same forward values as the sequential loop of griffin/griffin.py:280-286 (fp32 state for half-precision
+    I/O); the gradient is the hand-derived O(T) reverse pass instead of autograd's O(T^2) one, so that whole
+    blocks can be differentiated at sequence lengths in the thousands.  The closed form is itself held to
+    the reference's autograd results by tests/test_oracle_golden.py.
+    """
+
+    @staticmethod
+    def forward(ctx, x, u_r, u_i, lam, h0, reset, active, c):
+        with torch.no_grad():
+            y, h_last = rglru_core(x, u_r, u_i, lam, h0, reset, active, c)
+        ctx.save_for_backward(x, u_r, u_i, lam, h0, reset, active)
+        ctx.c = c
+        return y, h_last
+
+    @staticmethod
+    def backward(ctx, dy, dh_last):
+        x, u_r, u_i, lam, h0, reset, active = ctx.saved_tensors
+        got = rglru_backward_linear(x, u_r, u_i, lam, dy, h0=h0, dh_last=dh_last, reset=reset, active=active, c=ctx.c)
+        dh0 = None if h0 is None else got["dh0"].to(h0.dtype)
+        return (got["dx"].to(x.dtype), got["du_r"].to(u_r.dtype), got["du_i"].to(u_i.dtype), got["dLambda"].to(lam.dtype),
+                dh0, None, None, None)
+
+
+def rglru_layer_linear_backward(
+    x: Tensor,
+    params: dict[str, Tensor],
+    h0: Tensor | None = None,
+    reset: Tensor | None = None,
+    active: Tensor | None = None,
+    c: float = 8.0,
+) -> tuple[Tensor, Tensor]:
+    """``rglru_layer`` with the O(T) closed-form backward through the gate epilogue and the scan (the gate
+    projections stay ordinary autograd)."""
+    u_r = block_diagonal_linear(x, params["recurrence_gate.weight"], params["recurrence_gate.bias"])
+    u_i = block_diagonal_linear(x, params["input_gate.weight"], params["input_gate.bias"])
+    return _CoreLinearBackward.apply(x, u_r, u_i, params["Lambda"], h0, reset, active, c)
+
+
 def linear_scan(decay: Tensor, drive: Tensor, h0: Tensor) -> Tensor:
     """The raw affine scan operator (griffin/triton_scan.py:130-137, 274-276)."""
     return sequential_scan(decay, drive, h0)[0]
@@ -395,11 +436,13 @@ def recurrent_block(
     segment_pos: Tensor | None = None,
     active: Tensor | None = None,
     c: float = 8.0,
+    linear_backward: bool = False,
 ) -> tuple[Tensor, BlockCache]:
     """``RecurrentBlock.forward`` (griffin/griffin.py:439-529).
 
     ``params`` uses the reference's state-dict names (``linear_x.weight`` ...,
-    ``temporal_conv.weight`` [D,1,K], ``rg_lru.Lambda`` ...).
+    ``temporal_conv.weight`` [D,1,K], ``rg_lru.Lambda`` ...).  ``linear_backward``
+    swaps autograd's O(T^2) backward of the scan for the O(T) closed form (same values).
     """
     batch, steps = x.shape[:2]
     everyone = active is None
@@ -422,7 +465,8 @@ def recurrent_block(
 
     rnn_params = {k[len("rg_lru.") :]: v for k, v in params.items() if k.startswith("rg_lru.")}
     h0 = None if cache is None else cache.rnn_state
-    y, h_last = rglru_layer(xc, rnn_params, h0, reset=pos == 0, active=active, c=c)
+    layer = rglru_layer_linear_backward if linear_backward else rglru_layer
+    y, h_last = layer(xc, rnn_params, h0, reset=pos == 0, active=active, c=c)
     out = F.linear(y * gate_branch, params["linear_out.weight"], params["linear_out.bias"])
     out = torch.where(active[..., None], out, torch.zeros_like(out))
     return out, BlockCache(h_last, new_conv, last_position(pos, active, previous))

@@ -116,7 +116,7 @@ def _rglru_case(G, name, batch, steps, width, blocks, *, dtype=torch.float32, se
 
 
 def _config0(G):
-    """BASELINE config 0 at full shape; inputs come from oracle.make_rglru_case(seed=0)."""
+    """B=2, T=256, D=256, 4 gate heads, fp32 at full shape; inputs come from oracle.make_rglru_case(seed=0)."""
     case = orc.make_rglru_case(2, 256, 256, 4, seed=0)
     module = G.RG_LRU(256, gate_blocks=4, scan_mode="sequential")
     with torch.no_grad():
@@ -363,10 +363,36 @@ def _model_cases(G):
     _save("attention_block", out)
 
 
+def _model_autocast_case(G):
+    """A small hybrid LM run the way the reference trains (train.py:254-267): bf16 autocast around the model,
+    cross-entropy on the logits, fp32 parameters and gradients.  Gate heads are 64 wide like the 100M model's, the
+    vocabulary is odd, and the sequence spans more than one 64-step chunk."""
+    torch.manual_seed(9)
+    vocab = 131
+    model = G.GriffinModel(vocab_size=vocab, input_dim=16, mlp_expansion_factor=2, rnn_width=128, depth=3,
+                           attention_heads=2, attention_window_size=16, gate_blocks=2, scan_mode="sequential")
+    tokens = torch.randint(0, vocab, (2, 97))
+    out = {"tokens": tokens}
+    for key, p_ in model.state_dict().items():
+        out["p." + key] = p_
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        logits = model(tokens[:, :-1])
+    loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, vocab), tokens[:, 1:].reshape(-1))
+    loss.backward()
+    out["logits"] = logits.float()
+    out["loss"] = loss.detach().reshape(1)
+    keep = ("embd.weight", "final_norm.g", "layers.2.attention.query.weight", "layers.2.mlp.linear3.weight")
+    for name, p_ in model.named_parameters():
+        if name.startswith("layers.0.recurrent.") or name.startswith("layers.1.recurrent.rg_lru.") or name in keep:
+            out["g." + name] = p_.grad
+    _save("model_autocast_bf16", out)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("GRIFFIN_REFERENCE"),
                     help="checkout of the unmodified reference project (or set GRIFFIN_REFERENCE)")
+    ap.add_argument("--only", default=None, help="write just this case (e.g. model_autocast_bf16)")
     args = ap.parse_args()
     if not args.reference or not os.path.isdir(args.reference):
         ap.error("pass --reference <checkout of the reference project>")
@@ -375,6 +401,9 @@ def main() -> None:
     from griffin import triton_scan as TS
 
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+    if args.only == "model_autocast_bf16":
+        _model_autocast_case(G)
+        return
     _rglru_case(G, "rglru_masks_f32", 2, 29, 32, 4, seed=0, reset_at=[(0, 17), (1, 17)], inactive_tail=4)
     _rglru_case(G, "rglru_state_f32", 3, 19, 24, 4, seed=1, use_h0=True, use_dh=True,
                 reset_at=[(1, 7)], inactive_tail=5, extreme=True)
@@ -385,6 +414,7 @@ def main() -> None:
     _scan_selftest(TS)
     _block_cases(G)
     _model_cases(G)
+    _model_autocast_case(G)
 
 
 if __name__ == "__main__":

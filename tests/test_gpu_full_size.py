@@ -44,8 +44,8 @@ def _oracle_slab(x, u_r, u_i, dy, lam, sl, rows):
     return orc.rglru_backward_linear(cut(x), cut(u_r), cut(u_i), lam[sl].double().cpu(), cut(dy))
 
 
-def test_config1_full_shape_bf16_against_oracle():
-    """BASELINE config 1: bf16 I/O, B=8, T=2048, D=1024 -- every output and gradient, all channels."""
+def test_layer_full_shape_bf16_against_oracle():
+    """bf16 I/O, B=8, T=2048, D=1024 (the benchmark's headline shape) -- every output and gradient, all channels."""
     x, u_r, u_i, dy, lam = _inputs(8, 2048, 1024, torch.bfloat16, 1)
     got = _run(x, u_r, u_i, dy, lam)
     want = _oracle_slab(x, u_r, u_i, dy, lam, slice(None), slice(None))
@@ -54,7 +54,7 @@ def test_config1_full_shape_bf16_against_oracle():
         assert err <= BF16_REL, (key, err)
 
 
-def test_config3_layer_shape_fp32_against_oracle():
+def test_layer_full_shape_fp32_against_oracle():
     """The same shape with fp32 I/O (what the RG-LRU sees inside the 100M model): 1e-5 on everything,
     including dLambda, a 16384-term reduction per channel."""
     x, u_r, u_i, dy, lam = _inputs(8, 2048, 1024, torch.float32, 2)
@@ -65,8 +65,43 @@ def test_config3_layer_shape_fp32_against_oracle():
         assert err <= FP32_REL, (key, err)
 
 
-def test_config4_long_wide_slab_and_properties():
-    """Config 4 geometry (T=8192, D=5632, bf16) at B=2: a 256-channel slab against the oracle, plus
+@pytest.mark.parametrize("fold_merge", [False, True])
+def test_recurrent_block_full_shape_bf16_against_oracle(fold_merge):
+    """The whole recurrent block at B=16, T=2048, 768 -> 1024 -> 768 in bf16 (conv weights ~ N(0, 1/4), input
+    ~ N(0, 1)), with and without the GeLU-branch product folded into the scan kernels: output, input gradient and
+    every parameter gradient of all 16 rows against the oracle block (griffin/griffin.py:439-529 of the
+    reference) evaluated in fp32 on the bf16-rounded parameters.  The oracle differentiates the scan with its
+    O(T) closed form, which tests/test_oracle_golden.py holds to the reference's autograd."""
+    from griffin_b200 import RecurrentBlock
+    torch.manual_seed(5)
+    B, T, DM, DR = 16, 2048, 768, 1024
+    blk = RecurrentBlock(DM, DR, gate_blocks=16, scan_mode="cuda", fold_merge=fold_merge)
+    with torch.no_grad():
+        blk.temporal_conv.weight.normal_(0.0, 0.5)
+    blk = blk.to(torch.bfloat16)
+    params = {k: v.detach().float().clone().requires_grad_(True) for k, v in blk.state_dict().items()}
+    x = torch.randn(B, T, DM).to(torch.bfloat16)
+    dout = torch.randn(B, T, DM).to(torch.bfloat16)
+    xr = x.float().requires_grad_(True)
+    ref, ref_cache = orc.recurrent_block(xr, params, linear_backward=True)
+    (ref * dout.float()).sum().backward()
+
+    blk = blk.to(DEV)
+    xg = x.to(DEV).requires_grad_(True)
+    out, cache = blk(xg, return_cache=True)
+    (out.float() * dout.to(DEV).float()).sum().backward()
+    errs = {"out": orc.rel_l2(out, ref), "dx": orc.rel_l2(xg.grad, xr.grad),
+            "rnn_state": orc.rel_l2(cache.rnn_state, ref_cache.rnn_state),
+            "conv_state": orc.rel_l2(cache.conv_state, ref_cache.conv_state)}
+    for key, p in blk.named_parameters():
+        errs["g." + key] = orc.rel_l2(p.grad, params[key].grad)
+    bad = {k: v for k, v in errs.items() if not v <= BF16_REL}
+    assert not bad, (bad, errs)
+    assert torch.equal(cache.segment_position.cpu(), ref_cache.segment_position)
+
+
+def test_long_wide_slab_and_properties():
+    """Long and wide geometry (T=8192, D=5632, bf16) at B=2: a 256-channel slab against the oracle, plus
     properties that need no oracle: time-chunked == whole, backward is linear in the upstream gradient,
     rows are independent, repeated runs are bit-identical."""
     from griffin_b200 import ops
@@ -99,8 +134,8 @@ def test_config4_long_wide_slab_and_properties():
         assert orc.rel_l2(doubled[key].float(), 2 * got[key].float()) <= 4e-3, key
 
 
-def test_decode_steps_at_config4_batch_against_sequence_kernel():
-    """Config 4 part two geometry (B=512, D=5632, bf16, fp32 carried state): 16 single-token updates equal
+def test_decode_steps_at_batch_512_against_sequence_kernel():
+    """Decode geometry (B=512, D=5632, bf16, fp32 carried state): 16 single-token updates equal
     one 16-step sequence call, and the first step equals the oracle."""
     from griffin_b200 import ops
     B, D, S = 512, 5632, 16

@@ -100,7 +100,7 @@ def test_module_matches_reference_golden_fp32(name, width, blocks):
 
 
 def test_config0_full_shape_fp32():
-    """BASELINE config 0 (B=2, T=256, D=256, 4 gate heads, fp32) against the reference's stored results."""
+    """B=2, T=256, D=256, 4 gate heads, fp32 (the reference's CPU-runnable benchmark shape) against the reference's stored results."""
     from griffin_b200 import RG_LRU
     case = load_golden("rglru_config0_f32")
     inp = orc.make_rglru_case(2, 256, 256, 4, seed=0)

@@ -1,6 +1,7 @@
-"""The scan kernels exist in several CTA shapes picked by a size heuristic (64 or 32 channels, 16 or 32
-time-lanes, different ring depths).  The environment variables RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT force one
-shape for a whole process, so each forced shape runs the odd-shape parity cases in a child interpreter."""
+"""The scan kernels exist in two variants each, picked by shape and dtype: the forward with 64- or 32-channel
+tiles (variants 0 and 2), the backward with a producer warp or with the bulk copies issued by a compute thread
+(variants 0 and 3).  The environment variables RGLRU_FWD_VARIANT / RGLRU_BWD_VARIANT force one variant for a
+whole process, so each combination runs the parity cases in a child interpreter."""
 
 from __future__ import annotations
 
@@ -15,9 +16,9 @@ from conftest import ROOT
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("variant", ["1", "2", "3"])
-def test_forced_kernel_shape_passes_the_parity_cases(variant):
-    env = dict(os.environ, RGLRU_FWD_VARIANT=variant, RGLRU_BWD_VARIANT=variant)
+@pytest.mark.parametrize("fwd,bwd", [("0", "0"), ("2", "3"), ("0", "3"), ("2", "0")])
+def test_forced_kernel_variant_passes_the_parity_cases(fwd, bwd):
+    env = dict(os.environ, RGLRU_FWD_VARIANT=fwd, RGLRU_BWD_VARIANT=bwd)
     cmd = [sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_parity.py"), "-m", "gpu", "-q", "-x",
            "-k", "odd_shapes or config0 or bf16_io or golden", "-p", "no:cacheprovider"]
     res = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=600)

@@ -84,3 +84,38 @@ def test_padded_vocabulary_head_matches_plain_linear_gpu():
     assert torch.isfinite(gw).all() and rel_l2(gw, gp) <= 1e-5
     exact = model._logits(h)                       # no autocast: the plain fp32 path
     assert exact.dtype == torch.float32 and rel_l2(padded.float(), exact) <= 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fold_merge", [False, True])
+def test_autocast_model_against_reference_autocast_gpu(fold_merge):
+    """The harness the way the training benchmark runs it -- CUDA bf16 autocast, the GeLU-branch product folded
+    into the scan kernels, the vocabulary padded for the head -- against the reference's own autocast step
+    (train.py:254-267 of the reference, run on CPU by tests/golden/make_golden.py): logits, loss and gradients.
+    Both sides round to bf16 at different points of the graph, so the comparison is norm-wise at 2e-2
+    (the loss, a mean over 192 tokens, at 2e-3)."""
+    from griffin_b200.lm import GriffinModel
+    case = load_golden("model_autocast_bf16")
+    vocab = 131
+    model = GriffinModel(vocab, 16, 2, 128, 3, attention_heads=2, attention_window_size=16, gate_blocks=2)
+    model.load_state_dict(params_of(case), strict=True)
+    for layer in model.layers:
+        if hasattr(layer, "recurrent"):
+            layer.recurrent.fold_merge = fold_merge
+    model = model.cuda()
+    tokens = case["tokens"].cuda()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        logits = model(tokens[:, :-1], pad_vocab=True)
+    assert logits.shape[-1] == 136 and torch.isinf(logits[..., vocab:]).all()
+    loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.size(-1)), tokens[:, 1:].reshape(-1))
+    loss.backward()
+    assert rel_l2(logits[..., :vocab].float(), case["logits"]) <= 2e-2
+    torch.testing.assert_close(loss.detach().cpu().reshape(1), case["loss"], atol=0.0, rtol=2e-3)
+    grads = dict(model.named_parameters())
+    worst = {}
+    for key in case:
+        if key.startswith("g."):
+            err = rel_l2(grads[key[2:]].grad, case[key])
+            if not err <= 2e-2:
+                worst[key] = err
+    assert not worst, worst

@@ -197,11 +197,28 @@ def test_block_with_padding_that_is_not_right_padding():
             torch.testing.assert_close(p[key[2:]].grad, case[key], **TIGHT)
 
 
-def test_block_gradients():
+def test_ragged_block_gradients_through_the_linear_backward():
+    """The O(T) backward with padding that is not right padding and a carried cache (stored reference gradients)."""
+    case = load_golden("block_ragged")
+    p = {k: v.clone().requires_grad_(True) for k, v in params_of(case).items()}
+    x = case["x"].clone().requires_grad_(True)
+    first, _ = orc.recurrent_block(x, p, active=case["active"], linear_backward=True)
+    (first * case["dout"]).sum().backward()
+    torch.testing.assert_close(first.detach(), case["first"], **TIGHT)
+    torch.testing.assert_close(x.grad, case["dx"], **TIGHT)
+    for key in case:
+        if key.startswith("g."):
+            torch.testing.assert_close(p[key[2:]].grad, case[key], **TIGHT)
+
+
+@pytest.mark.parametrize("linear_backward", [False, True])
+def test_block_gradients(linear_backward):
+    """The reference's stored block gradients, through autograd over the sequential loop and through the
+    oracle's O(T) closed-form backward of the scan (the route the full-size GPU tests check against)."""
     case = load_golden("block_grads")
     p = {k: v.clone().requires_grad_(True) for k, v in params_of(case).items()}
     x = case["x"].clone().requires_grad_(True)
-    out, _ = orc.recurrent_block(x, p)
+    out, _ = orc.recurrent_block(x, p, linear_backward=linear_backward)
     (out * case["dout"]).sum().backward()
     torch.testing.assert_close(out, case["out"], **TIGHT)
     torch.testing.assert_close(x.grad, case["dx"], atol=1e-5, rtol=1e-5)
