@@ -95,7 +95,11 @@ __device__ __forceinline__ void mbar_wait_or_flag(uint64_t* bar, uint32_t parity
 __device__ __forceinline__ void bar_compute(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
-// The same barrier with an AND vote over its `nthreads` participants.
+// Named barrier 3: the threads that share the level-two chain of a chunk.
+__device__ __forceinline__ void bar_chain(int nthreads) {
+  asm volatile("bar.sync 3, %0;" ::"r"(nthreads) : "memory");
+}
+// Barrier 1 with an AND vote over its `nthreads` participants.
 __device__ __forceinline__ bool bar_compute_and(int nthreads, bool pred) {
   uint32_t all;
   asm volatile(

@@ -293,7 +293,10 @@ struct FwdSmem {
   static constexpr int STAGE = TILEX + 2 * TILE + (MERGE ? TILE : 0);
   static constexpr int OFF_AGG = NSTAGE * STAGE;
   static constexpr int OFF_EIN = OFF_AGG + ChainSmem<LANES, CH>::AGG;
-  static constexpr int OFF_BAR = OFF_EIN + ChainSmem<LANES, CH>::EIN;   // full[NSTAGE], ready[NSTAGE], dead flag
+  // The 32-lane shape splits a channel's chain over SEGS threads (segment totals: one float2 per segment and channel).
+  static constexpr int SEGS = (LANES == 32 && CH == 32) ? 4 : 1;
+  static constexpr int OFF_SEG = OFF_EIN + ChainSmem<LANES, CH>::EIN;
+  static constexpr int OFF_BAR = OFF_SEG + SEGS * CH * 8;   // full[NSTAGE], ready[NSTAGE], dead flag
   static constexpr int BYTES = OFF_BAR + 2 * NSTAGE * 8 + 16;
 };
 
@@ -391,10 +394,16 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   GateBias gb;
   if (GROUPED) load_gate_bias<sizeof(IO) == 2>(p.gate_bias, rcol + vec * CV, icol + vec * CV, gb);
 
-  // Level-two chain state: thread `tid` < CH carries channel d0 + tid across chunks.
+  // Level-two chain: SEGS threads per channel (thread tid: channel d0 + tid % CH, lane segment tid / CH), each
+  // of which carries the channel's state across chunks (identical copies).
+  constexpr int SEGS = SM::SEGS, SEGL = LANES / SEGS;
+  static_assert(SEGS * CH <= NCOMP && (SEGS * CH) % 32 == 0, "chain threads are whole warps of the compute group");
+  float2* segtot = reinterpret_cast<float2*>(smem + SM::OFF_SEG);
+  const bool chain_thread = tid < SEGS * CH;
+  const int cch = tid % CH, seg = tid / CH;
   float carry = 0.0f;
-  const int dch = d0 + tid;
-  if (tid < CH && dch < p.D && p.h0) carry = p.h0[static_cast<size_t>(b) * p.D + dch];
+  const int dch = d0 + cch;
+  if (chain_thread && dch < p.D && p.h0) carry = p.h0[static_cast<size_t>(b) * p.D + dch];
 
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
 
@@ -440,22 +449,52 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
     }
     bar_compute(NCOMP);
 
-    if (tid < CH) {
-      float2 ag[LANES];
+    if (chain_thread) {
+      float2 ag[SEGL];
 #pragma unroll
-      for (int j = 0; j < LANES; ++j) ag[j] = agg[j * CH + tid];
-      float e = carry;
-#pragma unroll
-      for (int j = 0; j < LANES; ++j) {
-        if (((j * TS) % SAVE_EVERY) == 0) {
-          const int t = t0 + j * TS;
+      for (int j = 0; j < SEGL; ++j) ag[j] = agg[(seg * SEGL + j) * CH + cch];
+      auto emit = [&](int lane, float e) {       // state entering a lane; every SAVE_EVERY steps also kept for the backward
+        if (((lane * TS) % SAVE_EVERY) == 0) {
+          const int t = t0 + lane * TS;
           if (p.states && t < p.T && dch < p.D)
             p.states[(static_cast<size_t>(b) * nsave + t / SAVE_EVERY) * p.D + dch] = e;
         }
-        ein[j * CH + tid] = e;
-        e = fmaf(ag[j].x, e, ag[j].y);
+        ein[lane * CH + cch] = e;
+      };
+      if (SEGS == 1) {
+        float e = carry;
+#pragma unroll
+        for (int j = 0; j < LANES; ++j) {
+          emit(j, e);
+          e = fmaf(ag[j].x, e, ag[j].y);
+        }
+        carry = e;
+      } else {
+        // Each thread composes its segment from the identity, keeping the map (pp, sp) that takes the state
+        // entering the segment to the state entering each of its lanes; the segment totals are exchanged through
+        // shared memory and every thread chains the few totals in front of it.
+        float pp[SEGL], sp[SEGL];
+        float pa = 1.0f, sa = 0.0f;
+#pragma unroll
+        for (int j = 0; j < SEGL; ++j) {
+          pp[j] = pa;
+          sp[j] = sa;
+          sa = fmaf(ag[j].x, sa, ag[j].y);
+          pa *= ag[j].x;
+        }
+        segtot[seg * CH + cch] = make_float2(pa, sa);
+        bar_chain(SEGS * CH);
+        float e = carry, enter = carry;
+#pragma unroll
+        for (int sgm = 0; sgm < SEGS; ++sgm) {
+          const float2 tot = segtot[sgm * CH + cch];
+          if (sgm == seg) enter = e;
+          e = fmaf(tot.x, e, tot.y);
+        }
+        carry = e;
+#pragma unroll
+        for (int j = 0; j < SEGL; ++j) emit(seg * SEGL + j, fmaf(pp[j], enter, sp[j]));
       }
-      carry = e;
     }
     bar_compute(NCOMP);
 
@@ -487,7 +526,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       bar_compute(NCOMP);
     }
   }
-  if (tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;
+  if (tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;   // segment 0's copy
 }
 
 // PLAIN: no token flags and a whole number of chunks, so the masked arithmetic is not compiled in.

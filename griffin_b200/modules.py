@@ -124,6 +124,8 @@ def _plain_flags(batch: int, steps: int, device) -> Tensor:
     backward), the creating stream is drained once so that other streams may read it, and nothing is cached
     while a CUDA graph is being captured (a tensor born in a capture belongs to the graph's memory pool and
     holds data only after a replay): such calls get a tensor of their own."""
+    if ops._library_ops_active():      # being traced (torch.compile, fake tensors): plain ops, no cache, no CUDA runtime calls
+        return _build_plain_flags(batch, steps, device)
     device = torch.device(device)
     capturing = device.type == "cuda" and torch.cuda.is_current_stream_capturing()
     key = (batch, steps, str(device))

@@ -1,8 +1,9 @@
 """Differentiable torch operators over the C ABI.
 
-Each operator is registered with ``torch.library`` (namespace ``griffin_b200``)
-with an explicit backward, so autograd, DDP and ``torch.compile`` see ordinary
-ops.  Tensors are passed to the library as raw device pointers on the current
+Every differentiable operator here -- the plain, merged, grouped and conv-folded scans, the raw
+affine scan and the conv -- is a ``torch.library`` custom op (namespace ``griffin_b200``) with an
+explicit backward op and a fake (shape-only) implementation, so autograd, DDP and ``torch.compile``
+see ordinary ops.  Tensors are passed to the library as raw device pointers on the current
 CUDA stream; nothing here computes on the CPU.
 
 * ``rglru``        -- gate epilogue + scan (griffin/griffin.py:237-286 of the reference)
@@ -65,9 +66,50 @@ def _stream(t: Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+# Every differentiable operator exists in two forms over the same implementation functions: a ``torch.library``
+# custom op (with fake implementation and registered backward), which is what ``torch.compile`` and other
+# tracers see, and a plain ``torch.autograd.Function``, which is what eager calls use because it costs a
+# fraction of the dispatcher round trip per call (the block is launch-bound on the host at these sizes).
+_FORCE_LIBRARY_OPS = False
+
+
+@contextlib.contextmanager
+def library_ops(enabled: bool = True):
+    """Route eager calls through the ``torch.library`` custom ops as well (tracing with fake tensors, opcheck)."""
+    global _FORCE_LIBRARY_OPS
+    previous, _FORCE_LIBRARY_OPS = _FORCE_LIBRARY_OPS, enabled
+    try:
+        yield
+    finally:
+        _FORCE_LIBRARY_OPS = previous
+
+
+def _library_ops_active() -> bool:
+    return _FORCE_LIBRARY_OPS or torch.compiler.is_compiling()
+
+
+def _eager_node(name: str, fwd_impl, setup, backward_rule, bwd_impl):
+    """The autograd.Function twin of a custom op: same forward implementation, same set-up and backward rule."""
+
+    class Node(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, *args):
+            ctx.set_materialize_grads(False)     # results nobody differentiates (workspace, gate tensor) stay None
+            out = fwd_impl(*args)
+            setup(ctx, args, out)
+            return out
+
+        @staticmethod
+        @torch.autograd.function.once_differentiable
+        def backward(ctx, *grads):
+            return backward_rule(ctx, *grads, _bwd=bwd_impl)
+
+    Node.__name__ = Node.__qualname__ = name
+    return Node
+
+
 # ----------------------------------------------------------------------------- rglru
-@torch.library.custom_op("griffin_b200::rglru_fwd", mutates_args=())
-def _rglru_fwd(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
+def _rglru_fwd_impl(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
                c: float, save: bool) -> tuple[Tensor, Tensor, Tensor]:
     lib = _lib.load()
     _require_cuda(x, u_r, u_i, lam, h0, tok)
@@ -84,14 +126,23 @@ def _rglru_fwd(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Te
     return y, h_last, ws
 
 
+def workspace_bytes(B, T, D):
+    """Bytes of the scan workspace (``rglru_workspace_bytes``) as plain arithmetic, for shape inference: the
+    states entering every 64-step chunk, one row of dLambda partial sums per batch row, and a 256-byte tail."""
+    return (B * ((T + 63) // 64) * D + B * D) * 4 + 256
+
+
+_rglru_fwd = torch.library.custom_op("griffin_b200::rglru_fwd", _rglru_fwd_impl, mutates_args=())
+
+
 @_rglru_fwd.register_fake
 def _(x, u_r, u_i, lam, h0, tok, c, save):
     B, T, D = x.shape
-    return (torch.empty_like(x), x.new_empty((B, D), dtype=torch.float32), x.new_empty((0,), dtype=torch.uint8))
+    return (torch.empty_like(x), x.new_empty((B, D), dtype=torch.float32),
+            x.new_empty((workspace_bytes(B, T, D) if save else 0,), dtype=torch.uint8))
 
 
-@torch.library.custom_op("griffin_b200::rglru_bwd", mutates_args=())
-def _rglru_bwd(dy: Tensor, dh_last: Optional[Tensor], x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor,
+def _rglru_bwd_impl(dy: Tensor, dh_last: Optional[Tensor], x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor,
                h0: Optional[Tensor], tok: Optional[Tensor], ws: Tensor, c: float, want_dh0: bool
                ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
     lib = _lib.load()
@@ -110,6 +161,9 @@ def _rglru_bwd(dy: Tensor, dh_last: Optional[Tensor], x: Tensor, u_r: Tensor, u_
     return dx, du_r, du_i, dlam, dh0
 
 
+_rglru_bwd = torch.library.custom_op("griffin_b200::rglru_bwd", _rglru_bwd_impl, mutates_args=())
+
+
 @_rglru_bwd.register_fake
 def _(dy, dh_last, x, u_r, u_i, lam, h0, tok, ws, c, want_dh0):
     B, T, D = x.shape
@@ -126,7 +180,7 @@ def _rglru_setup(ctx, inputs, output):
     ctx.want_dh0 = h0 is not None and ctx.needs_input_grad[4]
 
 
-def _rglru_backward(ctx, dy, dh_last, _dws):
+def _rglru_backward(ctx, dy, dh_last, _dws, _bwd=None):
     if not ctx.saved:
         raise RuntimeError("rglru was run with save=False (inference); its backward is unavailable")
     x, u_r, u_i, lam, h0, tok, ws = ctx.saved_tensors
@@ -135,11 +189,12 @@ def _rglru_backward(ctx, dy, dh_last, _dws):
     dy = dy.contiguous()
     if dh_last is not None:
         dh_last = dh_last.to(torch.float32).contiguous()
-    dx, du_r, du_i, dlam, dh0 = _rglru_bwd(dy, dh_last, x, u_r, u_i, lam, h0, tok, ws, ctx.c, ctx.want_dh0)
+    dx, du_r, du_i, dlam, dh0 = (_bwd or _rglru_bwd)(dy, dh_last, x, u_r, u_i, lam, h0, tok, ws, ctx.c, ctx.want_dh0)
     return dx, du_r, du_i, dlam, (dh0 if ctx.want_dh0 else None), None, None, None
 
 
 _rglru_fwd.register_autograd(_rglru_backward, setup_context=_rglru_setup)
+_RglruNode = _eager_node("RglruScan", _rglru_fwd_impl, _rglru_setup, _rglru_backward, _rglru_bwd_impl)
 
 
 def rglru(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor] = None,
@@ -153,7 +208,8 @@ def rglru(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor]
         raise ValueError("Lambda must have shape [width]")
     save = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (x, u_r, u_i, lam, h0))
-    y, h_last, _ = _rglru_fwd(x.contiguous(), u_r.contiguous(), u_i.contiguous(),
+    y, h_last, _ = (_rglru_fwd if _library_ops_active() else _RglruNode.apply)(
+        x.contiguous(), u_r.contiguous(), u_i.contiguous(),
                               lam.to(torch.float32).contiguous(),
                               None if h0 is None else h0.to(torch.float32).contiguous(),
                               None if tok is None else tok.contiguous(), float(c), save)
@@ -161,8 +217,7 @@ def rglru(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor]
 
 
 # ----------------------------------------------------------------------------- raw affine scan
-@torch.library.custom_op("griffin_b200::linear_scan_fwd", mutates_args=())
-def _scan_fwd(decay: Tensor, drive: Tensor, h0: Tensor) -> Tensor:
+def _scan_fwd_impl(decay: Tensor, drive: Tensor, h0: Tensor) -> Tensor:
     lib = _lib.load()
     B, T, D = decay.shape
     out = torch.empty_like(drive)
@@ -172,13 +227,15 @@ def _scan_fwd(decay: Tensor, drive: Tensor, h0: Tensor) -> Tensor:
     return out
 
 
+_scan_fwd = torch.library.custom_op("griffin_b200::linear_scan_fwd", _scan_fwd_impl, mutates_args=())
+
+
 @_scan_fwd.register_fake
 def _(decay, drive, h0):
     return torch.empty_like(drive)
 
 
-@torch.library.custom_op("griffin_b200::linear_scan_bwd", mutates_args=())
-def _scan_bwd(d_out: Tensor, decay: Tensor, h0: Tensor, out: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+def _scan_bwd_impl(d_out: Tensor, decay: Tensor, h0: Tensor, out: Tensor) -> tuple[Tensor, Tensor, Tensor]:
     lib = _lib.load()
     B, T, D = decay.shape
     d_decay = torch.empty_like(decay)
@@ -191,6 +248,9 @@ def _scan_bwd(d_out: Tensor, decay: Tensor, h0: Tensor, out: Tensor) -> tuple[Te
     return d_decay, d_drive, d_h0
 
 
+_scan_bwd = torch.library.custom_op("griffin_b200::linear_scan_bwd", _scan_bwd_impl, mutates_args=())
+
+
 @_scan_bwd.register_fake
 def _(d_out, decay, h0, out):
     return torch.empty_like(decay), torch.empty_like(decay), torch.empty_like(h0)
@@ -201,12 +261,15 @@ def _scan_setup(ctx, inputs, output):
     ctx.save_for_backward(decay, h0, output)
 
 
-def _scan_backward(ctx, d_out):
+def _scan_backward(ctx, d_out, _bwd=None):
     decay, h0, out = ctx.saved_tensors
-    return _scan_bwd(d_out.contiguous(), decay, h0, out)
+    if d_out is None:
+        d_out = torch.zeros_like(out)
+    return (_bwd or _scan_bwd)(d_out.contiguous(), decay, h0, out)
 
 
 _scan_fwd.register_autograd(_scan_backward, setup_context=_scan_setup)
+_ScanNode = _eager_node("LinearScan", _scan_fwd_impl, _scan_setup, _scan_backward, _scan_bwd_impl)
 
 
 def linear_scan(decay: Tensor, current_input: Tensor, initial_state: Tensor) -> Tensor:
@@ -222,12 +285,12 @@ def linear_scan(decay: Tensor, current_input: Tensor, initial_state: Tensor) -> 
         raise TypeError("CUDA linear scan expects fp32 decay and normalized input")
     if initial_state.dtype != torch.float32:
         raise TypeError("CUDA linear scan expects fp32 recurrent state")
-    return _scan_fwd(decay.contiguous(), current_input.contiguous(), initial_state.contiguous())
+    return (_scan_fwd if _library_ops_active() else _ScanNode.apply)(
+        decay.contiguous(), current_input.contiguous(), initial_state.contiguous())
 
 
 # ----------------------------------------------------------------------------- causal conv
-@torch.library.custom_op("griffin_b200::conv_fwd", mutates_args=())
-def _conv_fwd(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tensor], tok: Optional[Tensor]
+def _conv_fwd_impl(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tensor], tok: Optional[Tensor]
               ) -> tuple[Tensor, Tensor]:
     lib = _lib.load()
     _require_cuda(x_in, w, b, state, tok)
@@ -242,14 +305,16 @@ def _conv_fwd(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tens
     return out, new_state
 
 
+_conv_fwd = torch.library.custom_op("griffin_b200::conv_fwd", _conv_fwd_impl, mutates_args=())
+
+
 @_conv_fwd.register_fake
 def _(x_in, w, b, state, tok):
     B, T, D = x_in.shape
     return torch.empty_like(x_in), x_in.new_empty((B, 3, D))
 
 
-@torch.library.custom_op("griffin_b200::conv_bwd", mutates_args=())
-def _conv_bwd(d_conv: Tensor, x_in: Tensor, w: Tensor, state: Optional[Tensor], tok: Optional[Tensor],
+def _conv_bwd_impl(d_conv: Tensor, x_in: Tensor, w: Tensor, state: Optional[Tensor], tok: Optional[Tensor],
               want_state: bool) -> tuple[Tensor, Tensor, Tensor, Tensor]:
     lib = _lib.load()
     dt = _io_dtype(x_in, "conv backward")
@@ -268,6 +333,9 @@ def _conv_bwd(d_conv: Tensor, x_in: Tensor, w: Tensor, state: Optional[Tensor], 
     return dx, d_w, d_b, d_state
 
 
+_conv_bwd = torch.library.custom_op("griffin_b200::conv_bwd", _conv_bwd_impl, mutates_args=())
+
+
 @_conv_bwd.register_fake
 def _(d_conv, x_in, w, state, tok, want_state):
     B, T, D = x_in.shape
@@ -282,13 +350,16 @@ def _conv_setup(ctx, inputs, output):
     ctx.want_state = state is not None and ctx.needs_input_grad[3]
 
 
-def _conv_backward(ctx, d_out, _d_new_state):
+def _conv_backward(ctx, d_out, _d_new_state, _bwd=None):
     x_in, w, state, tok = ctx.saved_tensors
-    dx, d_w, d_b, d_state = _conv_bwd(d_out.contiguous(), x_in, w, state, tok, ctx.want_state)
+    if d_out is None:
+        d_out = torch.zeros_like(x_in)
+    dx, d_w, d_b, d_state = (_bwd or _conv_bwd)(d_out.contiguous(), x_in, w, state, tok, ctx.want_state)
     return dx, d_w, (d_b if ctx.has_bias else None), (d_state if ctx.want_state else None), None
 
 
 _conv_fwd.register_autograd(_conv_backward, setup_context=_conv_setup)
+_ConvNode = _eager_node("CausalConv", _conv_fwd_impl, _conv_setup, _conv_backward, _conv_bwd_impl)
 
 
 def causal_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state: Optional[Tensor] = None,
@@ -305,7 +376,8 @@ def causal_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state
     w = weight.to(torch.float32).contiguous()
     b = None if bias is None else bias.to(torch.float32).contiguous()
     st = None if conv_state is None else conv_state.to(x_in.dtype).contiguous()
-    return _conv_fwd(x_in.contiguous(), w, b, st, None if tok is None else tok.contiguous())
+    return (_conv_fwd if _library_ops_active() else _ConvNode.apply)(
+        x_in.contiguous(), w, b, st, None if tok is None else tok.contiguous())
 
 
 # ----------------------------------------------------------------------------- conv folded into the scan
@@ -392,31 +464,59 @@ def merge_scan_bwd(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, conv_w: O
     return dx, du_r, du_i, dbranch, dlam, dh0
 
 
-class _MergedScan(torch.autograd.Function):
-    """RG-LRU whose output is multiplied by gelu_tanh(branch) inside the scan kernels (no conv fold)."""
+def _merged_fwd_impl(x: Tensor, u_r: Tensor, u_i: Tensor, branch: Tensor, lam: Tensor, h0: Optional[Tensor],
+                tok: Optional[Tensor], c: float, save: bool) -> tuple[Tensor, Tensor, Tensor]:
+    return merge_scan_fwd(x, None, None, None, u_r, u_i, branch, lam, h0, tok, c, save)
 
-    @staticmethod
-    def forward(ctx, x, u_r, u_i, branch, lam, h0, tok, c):
-        lam32 = lam.to(torch.float32).contiguous()
-        h032 = None if h0 is None else h0.to(torch.float32).contiguous()
-        x, u_r, u_i, branch = x.contiguous(), u_r.contiguous(), u_i.contiguous(), branch.to(x.dtype).contiguous()
-        save = any(ctx.needs_input_grad)
-        out, h_last, ws = merge_scan_fwd(x, None, None, None, u_r, u_i, branch, lam32, h032, tok, float(c), save)
-        ctx.save_for_backward(x, u_r, u_i, branch, lam32, h032, tok, ws)
-        ctx.c, ctx.lam_dtype = float(c), lam.dtype
-        return out, h_last
 
-    @staticmethod
-    @torch.autograd.function.once_differentiable
-    def backward(ctx, dout, dh_last):
-        x, u_r, u_i, branch, lam32, h032, tok, ws = ctx.saved_tensors
-        if ws.numel() == 0:
-            raise RuntimeError("merged scan was run without saving its workspace; backward is unavailable")
-        dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
-        want_dh0 = h032 is not None and ctx.needs_input_grad[5]
-        dx, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dout.contiguous(), dh_last, x, None, None, None, u_r, u_i,
-                                                            branch, lam32, h032, tok, ws, ctx.c, want_dh0)
-        return dx, du_r, du_i, dbranch, dlam.to(ctx.lam_dtype), dh0, None, None
+_merged_fwd = torch.library.custom_op("griffin_b200::merged_fwd", _merged_fwd_impl, mutates_args=())
+
+
+@_merged_fwd.register_fake
+def _(x, u_r, u_i, branch, lam, h0, tok, c, save):
+    B, T, D = x.shape
+    return (torch.empty_like(x), x.new_empty((B, D), dtype=torch.float32),
+            x.new_empty((workspace_bytes(B, T, D) if save else 0,), dtype=torch.uint8))
+
+
+def _merged_bwd_impl(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, u_r: Tensor, u_i: Tensor, branch: Tensor,
+                lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor], ws: Tensor, c: float, want_dh0: bool
+                ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    dx, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dout, dh_last, x, None, None, None, u_r, u_i, branch, lam, h0,
+                                                        tok, ws, c, want_dh0)
+    return dx, du_r, du_i, dbranch, dlam, (dh0 if want_dh0 else x.new_empty((0,), dtype=torch.float32))
+
+
+_merged_bwd = torch.library.custom_op("griffin_b200::merged_bwd", _merged_bwd_impl, mutates_args=())
+
+
+@_merged_bwd.register_fake
+def _(dout, dh_last, x, u_r, u_i, branch, lam, h0, tok, ws, c, want_dh0):
+    B, T, D = x.shape
+    return (torch.empty_like(x), torch.empty_like(x), torch.empty_like(x), torch.empty_like(x),
+            x.new_empty((D,), dtype=torch.float32), x.new_empty((B, D) if want_dh0 else (0,), dtype=torch.float32))
+
+
+def _merged_setup(ctx, inputs, output):
+    x, u_r, u_i, branch, lam, h0, tok, c, save = inputs
+    ctx.save_for_backward(x, u_r, u_i, branch, lam, h0, tok, output[2])
+    ctx.c, ctx.saved = c, save
+    ctx.want_dh0 = h0 is not None and ctx.needs_input_grad[5]
+
+
+def _merged_backward(ctx, dout, dh_last, _dws, _bwd=None):
+    if not ctx.saved:
+        raise RuntimeError("merged scan was run without saving its workspace; backward is unavailable")
+    x, u_r, u_i, branch, lam, h0, tok, ws = ctx.saved_tensors
+    dout = torch.zeros_like(x) if dout is None else dout.to(x.dtype).contiguous()
+    dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
+    dx, du_r, du_i, dbranch, dlam, dh0 = (_bwd or _merged_bwd)(dout, dh_last, x, u_r, u_i, branch, lam, h0, tok, ws,
+                                                               ctx.c, ctx.want_dh0)
+    return dx, du_r, du_i, dbranch, dlam, (dh0 if ctx.want_dh0 else None), None, None, None
+
+
+_merged_fwd.register_autograd(_merged_backward, setup_context=_merged_setup)
+_MergedNode = _eager_node("MergedScan", _merged_fwd_impl, _merged_setup, _merged_backward, _merged_bwd_impl)
 
 
 def rglru_merged(x: Tensor, u_r: Tensor, u_i: Tensor, branch: Tensor, lam: Tensor, h0: Optional[Tensor] = None,
@@ -429,7 +529,12 @@ def rglru_merged(x: Tensor, u_r: Tensor, u_i: Tensor, branch: Tensor, lam: Tenso
         raise TypeError("x, u_r and u_i must share one dtype")
     if lam.shape != (x.shape[2],):
         raise ValueError("Lambda must have shape [width]")
-    return _MergedScan.apply(x, u_r, u_i, branch, lam, h0, None if tok is None else tok.contiguous(), c)
+    save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, u_r, u_i, branch, lam, h0))
+    out, h_last, _ = (_merged_fwd if _library_ops_active() else _MergedNode.apply)(
+        x.contiguous(), u_r.contiguous(), u_i.contiguous(), branch.to(x.dtype).contiguous(),
+        lam.to(torch.float32).contiguous(), None if h0 is None else h0.to(torch.float32).contiguous(),
+        None if tok is None else tok.contiguous(), float(c), save)
+    return out, h_last
 
 
 # ----------------------------------------------------------------------------- both gates from one grouped GEMM
@@ -443,78 +548,128 @@ def _aligned16(t: Optional[Tensor]) -> Optional[Tensor]:
     return t if t is None or t.data_ptr() % 16 == 0 else t.clone()
 
 
-class _GroupedRGLRU(torch.autograd.Function):
-    """Gate projections + RG-LRU (+ optional GeLU-branch product) as one node around ONE grouped GEMM.
+def _stacked_gates(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor) -> tuple[Tensor, Tensor]:
+    """The two [G, bw, bw] gate weights stacked per head in the activation dtype, and the biases [2 D] fp32 in the
+    same column layout."""
+    wcat = torch.cat([w_r, w_i], dim=1).to(x.dtype)                                   # [G, 2 bw, bw]
+    bias = torch.cat([b_r, b_i], dim=1).to(torch.float32).reshape(-1).contiguous()    # [2 D]
+    return wcat, bias
+
+
+def _grouped_fwd_impl(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor, h0: Optional[Tensor],
+                 tok: Optional[Tensor], c: float, branch: Optional[Tensor], save: bool
+                 ) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """Gate projections + RG-LRU (+ optional GeLU-branch product) around ONE grouped GEMM.
 
     The two [G, bw, bw] gate weights are stacked per head and a single batched GEMM writes both gate
     pre-activations straight into a [B, T, G, 2 bw] tensor (cuBLAS takes the strided output, so there is no
     re-layout pass); the kernels read that layout, add the biases themselves and return the gradient in the
     same layout, from which two more batched GEMMs give the input and weight gradients.
-    Reference: BlockDiagonalLinear griffin/griffin.py:129-154 called twice at :237-238."""
+    Reference: BlockDiagonalLinear griffin/griffin.py:129-154 called twice at :237-238.
+    Returns (out, h_last, the gate tensor u, the workspace)."""
+    lib = _lib.load()
+    with torch.autocast("cuda", enabled=False):
+        x = _aligned16(x)
+        B, T, D = x.shape
+        G, bw, _ = w_r.shape
+        dt = _io_dtype(x, "grouped forward")
+        wcat, bias = _stacked_gates(x, w_r, b_r, w_i, b_i)
+        rows = x.view(B * T, G, bw).transpose(0, 1)                                       # [G, N, bw] view
+        u = torch.empty(B, T, 2 * D, device=x.device, dtype=x.dtype)
+        torch.bmm(rows, wcat.transpose(1, 2), out=u.view(B * T, G, 2 * bw).transpose(0, 1))
+        branch = _aligned16(branch)
+        out = torch.empty_like(x)
+        h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
+        nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
+        ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
+        with _on(x, "rglru_grouped_fwd"):
+            rc = lib.rglru_grouped_fwd(_ptr(x), _ptr(u), _ptr(bias), _ptr(branch), _ptr(lam), _ptr(h0), _ptr(tok),
+                                       _ptr(out), _ptr(h_last), _ptr(ws) if save else None, nbytes, B, T, D, bw,
+                                       c, dt, _stream(x))
+        _lib.check(rc, "rglru_grouped_fwd")
+    return out, h_last, u, ws
 
-    @staticmethod
-    def forward(ctx, x, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch):
-        lib = _lib.load()
-        with torch.autocast("cuda", enabled=False):
-            x = _aligned16(x.contiguous())
-            B, T, D = x.shape
-            G, bw, _ = w_r.shape
-            dt = _io_dtype(x, "grouped forward")
-            wcat = torch.cat([w_r, w_i], dim=1).to(x.dtype)                                   # [G, 2 bw, bw]
-            bias = torch.cat([b_r, b_i], dim=1).to(torch.float32).reshape(-1).contiguous()    # [2 D]
-            rows = x.view(B * T, G, bw).transpose(0, 1)                                       # [G, N, bw] view
-            u = torch.empty(B, T, 2 * D, device=x.device, dtype=x.dtype)
-            torch.bmm(rows, wcat.transpose(1, 2), out=u.view(B * T, G, 2 * bw).transpose(0, 1))
-            lam32 = lam.to(torch.float32).contiguous()
-            h032 = None if h0 is None else h0.to(torch.float32).contiguous()
-            branch = None if branch is None else _aligned16(branch.to(x.dtype).contiguous())
-            save = any(ctx.needs_input_grad)
-            out = torch.empty_like(x)
-            h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
-            nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
-            ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
-            with _on(x, "rglru_grouped_fwd"):
-                rc = lib.rglru_grouped_fwd(_ptr(x), _ptr(u), _ptr(bias), _ptr(branch), _ptr(lam32), _ptr(h032), _ptr(tok),
-                                           _ptr(out), _ptr(h_last), _ptr(ws) if save else None, nbytes, B, T, D, bw,
-                                           float(c), dt, _stream(x))
-            _lib.check(rc, "rglru_grouped_fwd")
-        ctx.save_for_backward(x, u, wcat, bias, lam32, h032, tok, ws, branch)
-        ctx.c = float(c)
-        ctx.meta = (w_r.dtype, b_r.dtype, w_i.dtype, b_i.dtype, lam.dtype)
-        return out, h_last
 
-    @staticmethod
-    @torch.autograd.function.once_differentiable
-    def backward(ctx, dout, dh_last):
-        lib = _lib.load()
-        x, u, wcat, bias, lam32, h032, tok, ws, branch = ctx.saved_tensors
-        if ws.numel() == 0:
-            raise RuntimeError("grouped RG-LRU was run without saving its workspace; backward is unavailable")
-        with torch.autocast("cuda", enabled=False):
-            B, T, D = x.shape
-            G, bw2, bw = wcat.shape
-            dt = _io_dtype(x, "grouped backward")
-            dout = _aligned16(dout.to(x.dtype).contiguous())
-            dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
-            want_dh0 = h032 is not None and ctx.needs_input_grad[6]
-            dx = torch.empty_like(x)
-            du = torch.empty_like(u)
-            dbranch = None if branch is None else torch.empty_like(x)
-            dlam = torch.empty(D, device=x.device, dtype=torch.float32)
-            dh0 = torch.empty(B, D, device=x.device, dtype=torch.float32) if want_dh0 else None
-            with _on(x, "rglru_grouped_bwd"):
-                rc = lib.rglru_grouped_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(u), _ptr(bias), _ptr(branch),
-                                           _ptr(lam32), _ptr(h032), _ptr(tok), _ptr(ws), ws.numel(), _ptr(dx), _ptr(du),
-                                           _ptr(dbranch), _ptr(dlam), _ptr(dh0), B, T, D, bw, ctx.c, dt, _stream(x))
-            _lib.check(rc, "rglru_grouped_bwd")
-            dg = du.view(B * T, G, bw2).transpose(0, 1)                    # [G, N, 2 bw] view
-            rows = x.view(B * T, G, bw).transpose(0, 1)                    # [G, N, bw] view
-            dx.view(B * T, G, bw).transpose(0, 1).baddbmm_(dg, wcat)       # gate path added onto the direct path
-            dwcat = torch.bmm(dg.transpose(1, 2), rows)                    # [G, 2 bw, bw]
-            dbias = du.view(B * T, G, bw2).sum(dim=0, dtype=torch.float32)  # [G, 2 bw]
-        wr_dt, br_dt, wi_dt, bi_dt, lam_dt = ctx.meta
-        return (dx, dwcat[:, :bw].to(wr_dt), dbias[:, :bw].to(br_dt), dwcat[:, bw:].to(wi_dt), dbias[:, bw:].to(bi_dt),
-                dlam.to(lam_dt), dh0, None, None, dbranch)
+_grouped_fwd = torch.library.custom_op("griffin_b200::grouped_fwd", _grouped_fwd_impl, mutates_args=())
+
+
+@_grouped_fwd.register_fake
+def _(x, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch, save):
+    B, T, D = x.shape
+    return (torch.empty_like(x), x.new_empty((B, D), dtype=torch.float32), x.new_empty((B, T, 2 * D)),
+            x.new_empty((workspace_bytes(B, T, D) if save else 0,), dtype=torch.uint8))
+
+
+def _grouped_bwd_impl(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, u: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor,
+                 b_i: Tensor, branch: Optional[Tensor], lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
+                 ws: Tensor, c: float, want_dh0: bool
+                 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """(dx, dw_r, db_r, dw_i, db_i, dLambda, dh0, dbranch); absent results are empty tensors."""
+    lib = _lib.load()
+    with torch.autocast("cuda", enabled=False):
+        x = _aligned16(x)
+        B, T, D = x.shape
+        G, bw, _ = w_r.shape
+        bw2 = 2 * bw
+        dt = _io_dtype(x, "grouped backward")
+        wcat, bias = _stacked_gates(x, w_r, b_r, w_i, b_i)
+        dout = _aligned16(dout)
+        branch = _aligned16(branch)
+        dx = torch.empty_like(x)
+        du = torch.empty_like(u)
+        dbranch = torch.empty_like(x) if branch is not None else x.new_empty((0,))
+        dlam = torch.empty(D, device=x.device, dtype=torch.float32)
+        dh0 = torch.empty((B, D) if want_dh0 else (0,), device=x.device, dtype=torch.float32)
+        with _on(x, "rglru_grouped_bwd"):
+            rc = lib.rglru_grouped_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(u), _ptr(bias), _ptr(branch),
+                                       _ptr(lam), _ptr(h0), _ptr(tok), _ptr(ws), ws.numel(), _ptr(dx), _ptr(du),
+                                       _ptr(dbranch) if branch is not None else None, _ptr(dlam),
+                                       _ptr(dh0) if want_dh0 else None, B, T, D, bw, c, dt, _stream(x))
+        _lib.check(rc, "rglru_grouped_bwd")
+        dg = du.view(B * T, G, bw2).transpose(0, 1)                    # [G, N, 2 bw] view
+        rows = x.view(B * T, G, bw).transpose(0, 1)                    # [G, N, bw] view
+        dx.view(B * T, G, bw).transpose(0, 1).baddbmm_(dg, wcat)       # gate path added onto the direct path
+        dwcat = torch.bmm(dg.transpose(1, 2), rows)                    # [G, 2 bw, bw]
+        dbias = du.view(B * T, G, bw2).sum(dim=0, dtype=torch.float32)  # [G, 2 bw]
+    # (copies, not views: results of an operator may not share storage)
+    return (dx, dwcat[:, :bw].to(w_r.dtype).contiguous(), dbias[:, :bw].to(b_r.dtype).contiguous(),
+            dwcat[:, bw:].to(w_i.dtype).contiguous(), dbias[:, bw:].to(b_i.dtype).contiguous(), dlam, dh0, dbranch)
+
+
+_grouped_bwd = torch.library.custom_op("griffin_b200::grouped_bwd", _grouped_bwd_impl, mutates_args=())
+
+
+@_grouped_bwd.register_fake
+def _(dout, dh_last, x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws, c, want_dh0):
+    B, T, D = x.shape
+    return (torch.empty_like(x), torch.empty_like(w_r), torch.empty_like(b_r), torch.empty_like(w_i),
+            torch.empty_like(b_i), x.new_empty((D,), dtype=torch.float32),
+            x.new_empty((B, D) if want_dh0 else (0,), dtype=torch.float32),
+            torch.empty_like(x) if branch is not None else x.new_empty((0,)))
+
+
+def _grouped_setup(ctx, inputs, output):
+    x, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch, save = inputs
+    _, _, u, ws = output
+    ctx.save_for_backward(x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws)
+    ctx.c, ctx.saved = c, save
+    ctx.want_dh0 = h0 is not None and ctx.needs_input_grad[6]
+
+
+def _grouped_backward(ctx, dout, dh_last, _du, _dws, _bwd=None):
+    if not ctx.saved:
+        raise RuntimeError("grouped RG-LRU was run without saving its workspace; backward is unavailable")
+    x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws = ctx.saved_tensors
+    dout = torch.zeros_like(x) if dout is None else dout.to(x.dtype).contiguous()
+    dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
+    dx, dw_r, db_r, dw_i, db_i, dlam, dh0, dbranch = (_bwd or _grouped_bwd)(
+        dout, dh_last, x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws, ctx.c, ctx.want_dh0)
+    return (dx, dw_r, db_r, dw_i, db_i, dlam, (dh0 if ctx.want_dh0 else None), None, None,
+            (dbranch if branch is not None else None), None)
+
+
+_grouped_fwd.register_autograd(_grouped_backward, setup_context=_grouped_setup)
+_GroupedNode = _eager_node("GroupedRGLRU", _grouped_fwd_impl, _grouped_setup, _grouped_backward, _grouped_bwd_impl)
 
 
 def rglru_grouped(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor,
@@ -534,7 +689,13 @@ def rglru_grouped(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor,
     if not grouped_gates_supported(x, bw):
         raise ValueError("the grouped gate layout needs CUDA tensors, gate heads of a multiple of 64 channels and "
                          "rows that are a multiple of 16 bytes")
-    return _GroupedRGLRU.apply(x, w_r, b_r, w_i, b_i, lam, h0, None if tok is None else tok.contiguous(), c, branch)
+    save = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (x, w_r, b_r, w_i, b_i, lam, h0, branch))
+    out, h_last, _, _ = (_grouped_fwd if _library_ops_active() else _GroupedNode.apply)(
+        x.contiguous(), w_r, b_r, w_i, b_i, lam.to(torch.float32).contiguous(),
+        None if h0 is None else h0.to(torch.float32).contiguous(), None if tok is None else tok.contiguous(), float(c),
+        None if branch is None else branch.to(x.dtype).contiguous(), save)
+    return out, h_last
 
 
 def _gate(x: Tensor, weight: Tensor, bias: Tensor) -> Tensor:
@@ -556,63 +717,106 @@ def _gate_backward(du: Tensor, x: Tensor, weight: Tensor) -> tuple[Tensor, Tenso
     return dx, dw, db
 
 
-class _RecurrentCore(torch.autograd.Function):
-    """conv -> gate projections -> RG-LRU as one autograd node that keeps only the conv INPUT.
+def _core_fwd_impl(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_state: Optional[Tensor], w_r: Tensor,
+              b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor], c: float,
+              branch: Optional[Tensor], save: bool) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """conv -> gate projections -> RG-LRU as one operator that keeps only the conv INPUT for its backward.
 
-    Forward materialises the conv output once for the two gate GEMMs and drops it; the scan kernels read the
-    conv input and redo the four taps in their load stage.  Backward recomputes the conv output (one streaming
-    pass) for the gate-weight gradients, sums the direct and gate paths and runs a single conv backward.
-    """
-
-    @staticmethod
-    def forward(ctx, x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch):
-        x_in = x_in.contiguous()
-        cw = conv_w.to(torch.float32).contiguous()
-        cb = None if conv_b is None else conv_b.to(torch.float32).contiguous()
-        cs = None if conv_state is None else conv_state.to(x_in.dtype).contiguous()
-        lam32 = lam.to(torch.float32).contiguous()
-        h032 = None if h0 is None else h0.to(torch.float32).contiguous()
-        x_conv, new_state = _conv_fwd(x_in, cw, cb, cs, tok)
+    The conv output is materialised once for the two gate GEMMs and dropped; the scan kernels read the conv
+    input and redo the four taps in their load stage.  ``conv_w`` [D,4], ``conv_b``, ``lam``, ``h0`` fp32.
+    Returns (y, h_last, next conv state, u_r, u_i, workspace)."""
+    with torch.autocast("cuda", enabled=False):
+        x_conv, new_state = _conv_fwd_impl(x_in, conv_w, conv_b, conv_state, tok)
         u_r = _gate(x_conv, w_r, b_r)
         u_i = _gate(x_conv, w_i, b_i)
         del x_conv
-        save = any(ctx.needs_input_grad)
         if branch is None:
-            y, h_last, ws = conv_scan_fwd(x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, float(c), save)
+            y, h_last, ws = conv_scan_fwd(x_in, conv_w, conv_b, conv_state, u_r, u_i, lam, h0, tok, c, save)
         else:
-            branch = branch.to(x_in.dtype).contiguous()
-            y, h_last, ws = merge_scan_fwd(x_in, cw, cb, cs, u_r, u_i, branch, lam32, h032, tok, float(c), save)
-        ctx.save_for_backward(x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws, branch)
-        ctx.c = float(c)
-        ctx.meta = (conv_w.dtype, None if conv_b is None else conv_b.dtype, b_r.dtype, b_i.dtype, lam.dtype)
-        ctx.mark_non_differentiable(new_state)
-        return y, h_last, new_state
+            y, h_last, ws = merge_scan_fwd(x_in, conv_w, conv_b, conv_state, u_r, u_i, branch, lam, h0, tok, c, save)
+    return y, h_last, new_state, u_r, u_i, ws
 
-    @staticmethod
-    @torch.autograd.function.once_differentiable
-    def backward(ctx, dy, dh_last, _d_state):
-        x_in, cw, cb, cs, w_r, w_i, lam32, h032, tok, u_r, u_i, ws, branch = ctx.saved_tensors
-        if ws.numel() == 0:
-            raise RuntimeError("recurrent core was run without saving its workspace; backward is unavailable")
-        dy = dy.contiguous()
-        dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
-        want_dh0 = h032 is not None and ctx.needs_input_grad[9]
-        dbranch = None
+
+_core_fwd = torch.library.custom_op("griffin_b200::core_fwd", _core_fwd_impl, mutates_args=())
+
+
+@_core_fwd.register_fake
+def _(x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch, save):
+    B, T, D = x_in.shape
+    return (torch.empty_like(x_in), x_in.new_empty((B, D), dtype=torch.float32), x_in.new_empty((B, 3, D)),
+            torch.empty_like(x_in), torch.empty_like(x_in),
+            x_in.new_empty((workspace_bytes(B, T, D) if save else 0,), dtype=torch.uint8))
+
+
+def _core_bwd_impl(dy: Tensor, dh_last: Optional[Tensor], x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor],
+              conv_state: Optional[Tensor], w_r: Tensor, w_i: Tensor, lam: Tensor, h0: Optional[Tensor],
+              tok: Optional[Tensor], u_r: Tensor, u_i: Tensor, ws: Tensor, branch: Optional[Tensor], c: float,
+              want_dh0: bool, want_state: bool
+              ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Backward of ``core_fwd``: recomputes the conv output (one streaming pass) for the gate-weight gradients,
+    sums the direct and gate paths and runs a single conv backward.  Returns (dx_in, d conv_w, d conv_b,
+    d conv_state, dw_r, db_r, dw_i, db_i, dLambda, dh0, dbranch); absent results are empty tensors."""
+    with torch.autocast("cuda", enabled=False):
+        empty = x_in.new_empty((0,))
+        dbranch = empty
         if branch is None:
-            dxc, du_r, du_i, dlam, dh0 = conv_scan_bwd(dy, dh_last, x_in, cw, cb, cs, u_r, u_i, lam32, h032, tok, ws,
-                                                       ctx.c, want_dh0)
+            dxc, du_r, du_i, dlam, dh0 = conv_scan_bwd(dy, dh_last, x_in, conv_w, conv_b, conv_state, u_r, u_i, lam, h0,
+                                                       tok, ws, c, want_dh0)
         else:
-            dxc, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dy, dh_last, x_in, cw, cb, cs, u_r, u_i, branch, lam32,
-                                                                 h032, tok, ws, ctx.c, want_dh0)
-        x_conv, _ = _conv_fwd(x_in, cw, cb, cs, tok)          # recomputed, not saved
+            dxc, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dy, dh_last, x_in, conv_w, conv_b, conv_state, u_r, u_i,
+                                                                 branch, lam, h0, tok, ws, c, want_dh0)
+        x_conv, _ = _conv_fwd_impl(x_in, conv_w, conv_b, conv_state, tok)     # recomputed, not saved
         dx_r, dw_r, db_r = _gate_backward(du_r, x_conv, w_r)
         dx_i, dw_i, db_i = _gate_backward(du_i, x_conv, w_i)
         total = (dxc + dx_r + dx_i).contiguous()
-        want_state = cs is not None and ctx.needs_input_grad[3]
-        dx_in, d_w, d_b, d_state = _conv_bwd(total, x_in, cw, cs, tok, want_state)
-        wdt, bdt, brdt, bidt, ldt = ctx.meta
-        return (dx_in, d_w.to(wdt), None if cb is None else d_b.to(bdt), d_state if want_state else None,
-                dw_r, db_r.to(brdt), dw_i, db_i.to(bidt), dlam.to(ldt), dh0, None, None, dbranch)
+        dx_in, d_w, d_b, d_state = _conv_bwd_impl(total, x_in, conv_w, conv_state, tok, want_state)
+    return (dx_in, d_w, d_b, d_state, dw_r, db_r, dw_i, db_i, dlam,
+            dh0 if want_dh0 else x_in.new_empty((0,), dtype=torch.float32), dbranch)
+
+
+_core_bwd = torch.library.custom_op("griffin_b200::core_bwd", _core_bwd_impl, mutates_args=())
+
+
+@_core_bwd.register_fake
+def _(dy, dh_last, x_in, conv_w, conv_b, conv_state, w_r, w_i, lam, h0, tok, u_r, u_i, ws, branch, c, want_dh0, want_state):
+    B, T, D = x_in.shape
+    g, wo, _ = w_r.shape
+    f32 = torch.float32
+    return (torch.empty_like(x_in), x_in.new_empty((D, 4), dtype=f32), x_in.new_empty((D,), dtype=f32),
+            x_in.new_empty((B, 3, D) if want_state else (0,)), torch.empty_like(w_r), x_in.new_empty((g, wo), dtype=f32),
+            torch.empty_like(w_i), x_in.new_empty((g, wo), dtype=f32), x_in.new_empty((D,), dtype=f32),
+            x_in.new_empty((B, D) if want_dh0 else (0,), dtype=f32),
+            torch.empty_like(x_in) if branch is not None else x_in.new_empty((0,)))
+
+
+def _core_setup(ctx, inputs, output):
+    x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch, save = inputs
+    _, _, new_state, u_r, u_i, ws = output
+    ctx.save_for_backward(x_in, conv_w, conv_b, conv_state, w_r, w_i, lam, h0, tok, u_r, u_i, ws, branch)
+    ctx.c, ctx.saved = c, save
+    ctx.bias_dtypes = (b_r.dtype, b_i.dtype)
+    ctx.want_dh0 = h0 is not None and ctx.needs_input_grad[9]
+    ctx.want_state = conv_state is not None and ctx.needs_input_grad[3]
+    ctx.mark_non_differentiable(new_state)
+
+
+def _core_backward(ctx, dy, dh_last, _d_state, _du_r, _du_i, _dws, _bwd=None):
+    if not ctx.saved:
+        raise RuntimeError("recurrent core was run without saving its workspace; backward is unavailable")
+    x_in, conv_w, conv_b, conv_state, w_r, w_i, lam, h0, tok, u_r, u_i, ws, branch = ctx.saved_tensors
+    dy = torch.zeros_like(x_in) if dy is None else dy.to(x_in.dtype).contiguous()
+    dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
+    (dx_in, d_w, d_b, d_state, dw_r, db_r, dw_i, db_i, dlam, dh0, dbranch) = (_bwd or _core_bwd)(
+        dy, dh_last, x_in, conv_w, conv_b, conv_state, w_r, w_i, lam, h0, tok, u_r, u_i, ws, branch, ctx.c,
+        ctx.want_dh0, ctx.want_state)
+    brdt, bidt = ctx.bias_dtypes
+    return (dx_in, d_w, None if conv_b is None else d_b, d_state if ctx.want_state else None,
+            dw_r, db_r.to(brdt), dw_i, db_i.to(bidt), dlam, (dh0 if ctx.want_dh0 else None), None, None,
+            (dbranch if branch is not None else None), None)
+
+
+_core_fwd.register_autograd(_core_backward, setup_context=_core_setup)
+_CoreNode = _eager_node("RecurrentCore", _core_fwd_impl, _core_setup, _core_backward, _core_bwd_impl)
 
 
 def recurrent_core(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_state: Optional[Tensor],
@@ -627,8 +831,16 @@ def recurrent_core(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_
         raise ValueError("branch must have the shape of x_in")
     if x_in.dim() != 3 or conv_w.shape != (x_in.shape[2], 4):
         raise ValueError("x_in must be [batch, sequence, width] and conv_w [width, 4]")
-    return _RecurrentCore.apply(x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0,
-                                None if tok is None else tok.contiguous(), c, branch)
+    save = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (x_in, conv_w, conv_b, conv_state, w_r, b_r, w_i, b_i, lam, h0, branch))
+    y, h_last, new_state, _, _, _ = (_core_fwd if _library_ops_active() else _CoreNode.apply)(
+        x_in.contiguous(), conv_w.to(torch.float32).contiguous(),
+        None if conv_b is None else conv_b.to(torch.float32).contiguous(),
+        None if conv_state is None else conv_state.to(x_in.dtype).contiguous(), w_r, b_r, w_i, b_i,
+        lam.to(torch.float32).contiguous(), None if h0 is None else h0.to(torch.float32).contiguous(),
+        None if tok is None else tok.contiguous(), float(c),
+        None if branch is None else branch.to(x_in.dtype).contiguous(), save)
+    return y, h_last, new_state
 
 
 # ----------------------------------------------------------------------------- decode (in-place state, no autograd)

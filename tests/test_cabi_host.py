@@ -57,6 +57,10 @@ def test_workspace_size_and_chunk(lib):
     assert lib.rglru_workspace_bytes(B, T, D, _lib.F32) == 4 * (B * nsave * D + B * D) + 256
     assert lib.rglru_workspace_bytes(0, T, D, _lib.F32) == 0
     assert lib.rglru_conv_bwd_workspace_bytes(B, T, D) >= 4 * 5 * D * B
+    # the arithmetic that shape inference (the ops' fake implementations) uses is the library's own
+    from griffin_b200.ops import workspace_bytes
+    for shape in ((3, 130, 40), (8, 2048, 1024), (1, 1, 1), (64, 8192, 5632)):
+        assert workspace_bytes(*shape) == lib.rglru_workspace_bytes(*shape, _lib.BF16)
 
 
 def test_argument_validation_codes(lib):

@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from oracle import rglru_oracle as orc
+from oracle.rglru_oracle import rel_l2 as rel_l2_
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -122,9 +123,12 @@ def test_long_wide_slab_and_properties():
         yb, hb = ops.rglru(x[:, cutp:].contiguous(), u_r[:, cutp:].contiguous(), u_i[:, cutp:].contiguous(), lam, ha)
         assert orc.rel_l2(torch.cat([ya, yb], 1), got["y"]) <= 4e-3      # bf16 outputs, fp32 state
         assert orc.rel_l2(hb, got["h_last"]) <= 1e-5
-        # batch rows are independent: row 1 alone gives the same bits
+        # batch rows are independent: with the two rows swapped, each row's results are the same bits
+        ys, hs = ops.rglru(x.flip(0).contiguous(), u_r.flip(0).contiguous(), u_i.flip(0).contiguous(), lam)
+        assert torch.equal(ys.flip(0), got["y"]) and torch.equal(hs.flip(0), got["h_last"])
+        # and a row on its own (which may run a different kernel shape) agrees to rounding
         y1, h1 = ops.rglru(x[1:2].contiguous(), u_r[1:2].contiguous(), u_i[1:2].contiguous(), lam)
-        assert torch.equal(y1, got["y"][1:2]) and torch.equal(h1, got["h_last"][1:2])
+        assert rel_l2_(y1, got["y"][1:2]) <= 2e-3 and rel_l2_(h1, got["h_last"][1:2]) <= 1e-5
     # determinism and linearity of the backward in dy
     again = _run(x, u_r, u_i, dy, lam)
     for key in got:
