@@ -39,7 +39,7 @@ SIGNATURES = {
     "rglru_merge_fwd": (_i, [_vp] * 12 + [_vp, _sz, _i, _i, _i, _f, _i, _vp]),
     "rglru_merge_bwd": (_i, [_vp] * 12 + [_vp, _sz] + [_vp] * 6 + [_i, _i, _i, _f, _i, _vp]),
     "rglru_grouped_fwd": (_i, [_vp] * 9 + [_vp, _sz, _i, _i, _i, _i, _f, _i, _vp]),
-    "rglru_grouped_bwd": (_i, [_vp] * 9 + [_vp, _sz] + [_vp] * 5 + [_i, _i, _i, _i, _f, _i, _vp]),
+    "rglru_grouped_bwd": (_i, [_vp] * 9 + [_vp, _sz] + [_vp] * 6 + [_i, _i, _i, _i, _f, _i, _vp]),
     "rglru_linear_scan_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rglru_linear_scan_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rglru_conv_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -159,7 +159,7 @@ const char* rglru_status_string(int status) {
 
 const char* rglru_last_cuda_error(void) { return cudaGetErrorString(t_last_cuda); }
 
-int rglru_abi_version(void) { return 1; }
+int rglru_abi_version(void) { return 2; }
 
 int rglru_device_status(int* detail) {
   int* status = nullptr;
@@ -199,7 +199,9 @@ size_t rglru_workspace_bytes(int B, int T, int D, int io_dtype) {
   (void)io_dtype;
   if (B <= 0 || T <= 0 || D <= 0) return 0;
   const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
-  return (static_cast<size_t>(B) * nsave * D + static_cast<size_t>(B) * D) * sizeof(float) + WS_TAIL_BYTES;
+  // chunk-entry states [B, nsave, D] | dLambda partial rows [B, D] | tail (completion ticket) | gate-sum partial rows [B, 2 D]
+  return (static_cast<size_t>(B) * nsave * D + static_cast<size_t>(B) * D) * sizeof(float) + WS_TAIL_BYTES +
+         static_cast<size_t>(B) * 2 * D * sizeof(float);
 }
 
 int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
@@ -524,8 +526,8 @@ int rglru_grouped_fwd(const void* x, const void* u, const float* gate_bias, cons
 
 int rglru_grouped_bwd(const void* dout, const float* dh_last, const void* x, const void* u, const float* gate_bias,
                       const void* branch, const float* lambda, const float* h0, const uint8_t* tok, void* ws,
-                      size_t ws_bytes, void* dx, void* du, void* dbranch, float* dlambda, float* dh0, int B, int T, int D,
-                      int gate_width, float c, int io_dtype, void* stream) {
+                      size_t ws_bytes, void* dx, void* du, void* dbranch, float* dlambda, float* dh0, float* d_gate_bias,
+                      int B, int T, int D, int gate_width, float c, int io_dtype, void* stream) {
   if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
   if (!dout || !x || !u || !lambda || !dx || !du || !dlambda || (branch && !dbranch)) return RGLRU_ERR_NULL_POINTER;
   int rc = check_dims(B, T, D);
@@ -536,8 +538,9 @@ int rglru_grouped_bwd(const void* dout, const float* dh_last, const void* x, con
   rc = check_grouped(D, gate_width, es);
   if (rc != RGLRU_OK) return rc;
   if (!aligned(dout, 16) || !aligned(x, 16) || !aligned(u, 16) || !aligned(branch, 16) || !aligned(dx, 16) ||
-      !aligned(du, 16) || !aligned(dbranch, 16) || !aligned(gate_bias, 16) || !aligned(lambda, 4) || !aligned(h0, 4) ||
-      !aligned(dh_last, 4) || !aligned(dlambda, 4) || !aligned(dh0, 4) || !aligned(ws, 4))
+      !aligned(du, 16) || !aligned(dbranch, 16) || !aligned(gate_bias, 16) || !aligned(d_gate_bias, 16) ||
+      !aligned(lambda, 4) || !aligned(h0, 4) || !aligned(dh_last, 4) || !aligned(dlambda, 4) || !aligned(dh0, 4) ||
+      !aligned(ws, 16))
     return RGLRU_ERR_MISALIGNED;
   if (!ws || ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
   int* status = nullptr;
@@ -553,6 +556,10 @@ int rglru_grouped_bwd(const void* dout, const float* dh_last, const void* x, con
   a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
   a.dlambda = dlambda; a.dh0 = dh0;
   a.ticket = (B <= FUSED_DLAMBDA_MAX_B) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
+  a.dgate_part = d_gate_bias ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.dlam_part + static_cast<size_t>(B) * D) +
+                                                         WS_TAIL_BYTES)
+                             : nullptr;
+  a.dgate = d_gate_bias;
   a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
 
   BwdMaps maps;

@@ -63,6 +63,10 @@ struct ScanBwdArgs {
   void* dg;
   const float* gate_bias;   // grouped gate layout only (see ScanFwdArgs); dur / dui then share that layout too
   int gate_bw;
+  // grouped gate layout only: per-row partial column sums of du [B, 2 D] (workspace) and, when the caller wants
+  // the gate-bias gradient, their fold over the batch [2 D]; both in the gate tensor's column layout
+  float* dgate_part;
+  float* dgate;
   int B, T, D;
   float c;
   int* status;

@@ -655,10 +655,11 @@ __device__ __forceinline__ void bwd_local(uint8_t* tdy, uint8_t* tg, const uint8
 // merged, the branch gradient) over the input tiles.  MASKED = false is the path of a thread whose tokens are
 // all ordinary: the decay that takes the gradient is the decay itself, so R.ar is not read.  The incoming
 // gradient is read back from its tile unless the merged variant replaced it in registers.
-template <typename IO, int TS, int CH, bool MASKED, bool CONV, bool MERGE>
+// SUMS: also accumulate the sums over time of du_r and du_i (the gate-bias gradient of the grouped layout).
+template <typename IO, int TS, int CH, bool MASKED, bool CONV, bool MERGE, bool SUMS>
 __device__ __forceinline__ void bwd_apply(uint8_t* tiles, int off_dx, int off_dr, int off_di, int off_g, int off0,
                                           const float2 (&K)[2], const float2 (&hin)[2], const float2 (&cin)[2],
-                                          BwdRegs<IO, TS>& R, float2 (&dlam)[2]) {
+                                          BwdRegs<IO, TS>& R, float2 (&dlam)[2], float2 (&dsr)[2], float2 (&dsi)[2]) {
   constexpr int ROWB = CH * sizeof(IO);
   float2 h[2] = {hin[0], hin[1]};
   float2 c[2] = {cin[0], cin[1]};
@@ -703,6 +704,10 @@ __device__ __forceinline__ void bwd_apply(uint8_t* tiles, int off_dx, int off_dr
       dlam[cp] = add2(dlam[cp], w);
       // d u_r = dl * d(log a)/d u_r = dl * (-K) r (1 - r) with K = -c logsigmoid(Lambda) >= 0
       drv[cp] = mul2(w, fma2(K[cp], R.rr[st][cp], nK[cp]));
+      if (SUMS) {
+        dsr[cp] = add2(dsr[cp], drv[cp]);
+        dsi[cp] = add2(dsi[cp], div[cp]);
+      }
     }
     Pack<IO>::store2(tdx + off, dxv);
     Pack<IO>::store2(tdr + off, drv);
@@ -855,6 +860,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   if (GROUPED) load_gate_bias<sizeof(IO) == 2>(p.gate_bias, rcol + vec * CV, icol + vec * CV, gb);
 
   float2 dlam[2] = {f2(0.0f), f2(0.0f)};
+  float2 dsr[2] = {f2(0.0f), f2(0.0f)}, dsi[2] = {f2(0.0f), f2(0.0f)};   // grouped layout: sums over time of du_r, du_i
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
 
   for (int q = 0; q < nchunks; ++q) {
@@ -954,8 +960,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
       const float4 r4 = *reinterpret_cast<const float4*>(einR + lane_t * CH + vec * CV);
       const float2 hin[2] = {make_float2(f4.x, f4.y), make_float2(f4.z, f4.w)};
       const float2 cin[2] = {make_float2(r4.x, r4.y), make_float2(r4.z, r4.w)};
-      if (flagged) bwd_apply<IO, TS, CH, true, CONV, MERGE>(tiles, SM::OFF_X + SM::HALO, SM::OFF_UR, SM::OFF_UI, SM::OFF_G, off0, K, hin, cin, R, dlam);
-      else bwd_apply<IO, TS, CH, false, CONV, MERGE>(tiles, SM::OFF_X + SM::HALO, SM::OFF_UR, SM::OFF_UI, SM::OFF_G, off0, K, hin, cin, R, dlam);
+      if (flagged) bwd_apply<IO, TS, CH, true, CONV, MERGE, GROUPED>(tiles, SM::OFF_X + SM::HALO, SM::OFF_UR, SM::OFF_UI, SM::OFF_G, off0, K, hin, cin, R, dlam, dsr, dsi);
+      else bwd_apply<IO, TS, CH, false, CONV, MERGE, GROUPED>(tiles, SM::OFF_X + SM::HALO, SM::OFF_UR, SM::OFF_UI, SM::OFF_G, off0, K, hin, cin, R, dlam, dsr, dsi);
     }
     if (USE_TMA && SELF_ISSUE) {
       fence_async_smem();          // the stage leaves after the next barrier all threads pass
@@ -982,12 +988,20 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     tma_wait_all<0>();
   }
   *reinterpret_cast<float4*>(einF + lane_t * CH + vec * CV) = make_float4(dlam[0].x, dlam[0].y, dlam[1].x, dlam[1].y);
+  if (GROUPED) {   // the chain planes are free now: the two gate sums go through them the same way
+    *reinterpret_cast<float4*>(einR + lane_t * CH + vec * CV) = make_float4(dsr[0].x, dsr[0].y, dsr[1].x, dsr[1].y);
+    *reinterpret_cast<float4*>(aggP + lane_t * CH + vec * CV) = make_float4(dsi[0].x, dsi[0].y, dsi[1].x, dsi[1].y);
+  }
   bar_compute(NCOMP);
-  if (tid < CH && dch < p.D) {
+  static_assert(!GROUPED || NCOMP >= 3 * CH, "one thread per channel and sum");
+  if (tid < (GROUPED ? 3 * CH : CH) && dch < p.D) {
+    const int which = tid / CH;                       // 0: dLambda partial, 1: sum du_r, 2: sum du_i
+    const float* plane = which == 0 ? einF : (which == 1 ? einR : aggP);
     float acc = 0.0f;
 #pragma unroll
-    for (int j = 0; j < LANES; ++j) acc += einF[j * CH + tid];
-    p.dlam_part[static_cast<size_t>(b) * p.D + dch] = acc;
+    for (int j = 0; j < LANES; ++j) acc += plane[j * CH + cch];
+    if (which == 0) p.dlam_part[static_cast<size_t>(b) * p.D + dch] = acc;
+    else if (p.dgate_part) p.dgate_part[static_cast<size_t>(b) * 2 * p.D + (which == 1 ? rcol : icol) + cch] = acc;
   }
   if (!p.ticket) return;   // the caller folds the rows with rglru_dlambda_kernel
 
@@ -1033,7 +1047,33 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
       p.dlambda[d] = (1.0f / (1.0f + expf(lam))) * p.c * acc;
     }
   }
+  if (GROUPED && p.dgate && p.dgate_part) {     // gate-bias gradient: column sums of du over the batch rows
+    const int N2 = 2 * p.D;                     // a multiple of 4: the grouped layout needs 64-channel gate heads
+    for (int d = tid * 4; d < N2; d += NCOMP * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; r0 < p.B; r0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(p.dgate_part + static_cast<size_t>(r0 + j) * N2 + d))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+      }
+      *reinterpret_cast<float4*>(p.dgate + d) = acc;
+    }
+  }
   if (tid == 0) *p.ticket = 0u;
+}
+
+// out[n] = sum_b part[b, n], rows added in index order (gate-bias gradient when the batch is too large for the
+// backward kernel's own fold).
+__global__ void rglru_colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int B, int N) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float acc = 0.0f;
+  for (int b = 0; b < B; ++b) acc += part[static_cast<size_t>(b) * N + n];
+  out[n] = acc;
 }
 
 // dLambda[d] = d/dLambda of sum dl * r * c * logsigmoid(Lambda) = sigmoid(-Lambda_d) * c * sum_b partial[b, d],
@@ -1797,6 +1837,8 @@ static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaS
   e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), bytes, s, maps, a);
   if (e != cudaSuccess || a.ticket) return e;
   rglru_dlambda_kernel<<<(a.D + 255) / 256, 256, 0, s>>>(a.dlam_part, a.lambda, a.dlambda, a.B, a.D, a.c);
+  if (GROUPED && a.dgate && a.dgate_part)
+    rglru_colsum_kernel<<<(2 * a.D + 255) / 256, 256, 0, s>>>(a.dgate_part, a.dgate, a.B, 2 * a.D);
   return cudaGetLastError();
 }
 

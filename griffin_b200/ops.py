@@ -128,8 +128,9 @@ def _rglru_fwd_impl(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Option
 
 def workspace_bytes(B, T, D):
     """Bytes of the scan workspace (``rglru_workspace_bytes``) as plain arithmetic, for shape inference: the
-    states entering every 64-step chunk, one row of dLambda partial sums per batch row, and a 256-byte tail."""
-    return (B * ((T + 63) // 64) * D + B * D) * 4 + 256
+    states entering every 64-step chunk, one row of dLambda partial sums per batch row, a 256-byte tail, and one row
+    of gate-sum partials [2 D] per batch row."""
+    return (B * ((T + 63) // 64) * D + B * D) * 4 + 256 + B * 2 * D * 4
 
 
 _rglru_fwd = torch.library.custom_op("griffin_b200::rglru_fwd", _rglru_fwd_impl, mutates_args=())
@@ -620,17 +621,17 @@ def _grouped_bwd_impl(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, u: Ten
         dbranch = torch.empty_like(x) if branch is not None else x.new_empty((0,))
         dlam = torch.empty(D, device=x.device, dtype=torch.float32)
         dh0 = torch.empty((B, D) if want_dh0 else (0,), device=x.device, dtype=torch.float32)
+        dbias = torch.empty(G, bw2, device=x.device, dtype=torch.float32)    # [2 D] in the gate tensor's column layout
         with _on(x, "rglru_grouped_bwd"):
             rc = lib.rglru_grouped_bwd(_ptr(dout), _ptr(dh_last), _ptr(x), _ptr(u), _ptr(bias), _ptr(branch),
                                        _ptr(lam), _ptr(h0), _ptr(tok), _ptr(ws), ws.numel(), _ptr(dx), _ptr(du),
                                        _ptr(dbranch) if branch is not None else None, _ptr(dlam),
-                                       _ptr(dh0) if want_dh0 else None, B, T, D, bw, c, dt, _stream(x))
+                                       _ptr(dh0) if want_dh0 else None, _ptr(dbias), B, T, D, bw, c, dt, _stream(x))
         _lib.check(rc, "rglru_grouped_bwd")
         dg = du.view(B * T, G, bw2).transpose(0, 1)                    # [G, N, 2 bw] view
         rows = x.view(B * T, G, bw).transpose(0, 1)                    # [G, N, bw] view
         dx.view(B * T, G, bw).transpose(0, 1).baddbmm_(dg, wcat)       # gate path added onto the direct path
         dwcat = torch.bmm(dg.transpose(1, 2), rows)                    # [G, 2 bw, bw]
-        dbias = du.view(B * T, G, bw2).sum(dim=0, dtype=torch.float32)  # [G, 2 bw]
     # (copies, not views: results of an operator may not share storage)
     return (dx, dwcat[:, :bw].to(w_r.dtype).contiguous(), dbias[:, :bw].to(b_r.dtype).contiguous(),
             dwcat[:, bw:].to(w_i.dtype).contiguous(), dbias[:, bw:].to(b_i.dtype).contiguous(), dlam, dh0, dbranch)

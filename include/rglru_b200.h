@@ -152,15 +152,18 @@ int rglru_merge_bwd(const void* dout, const float* dh_last, const void* x, const
  *   u, du     : [B,T,2D] io_dtype in the layout above      gate_bias : [2D] fp32, same column layout, or NULL
  *   gate_width: bw = D / G, a multiple of 64; D * sizeof(element) a multiple of 16 (else RGLRU_ERR_BAD_SHAPE)
  *   x, u, branch, out, dout, dx, du, dbranch and gate_bias must be 16-byte aligned (else RGLRU_ERR_MISALIGNED).
- * Everything else as rglru_fwd / rglru_bwd; the caller's GEMMs turn du into the input and weight gradients and
- * its column sums into the bias gradients. */
+ *   d_gate_bias : [2D] fp32, same column layout, 16-byte aligned, or NULL.  When given, the backward kernel also
+ *               returns the gradient of the gate biases (the sums of du over batch and time, taken from the
+ *               fp32 values before they are rounded to io_dtype, rows folded in index order), which saves the
+ *               caller a reduction pass over du.  The workspace must then be 16-byte aligned.
+ * Everything else as rglru_fwd / rglru_bwd; the caller's GEMMs turn du into the input and weight gradients. */
 int rglru_grouped_fwd(const void* x, const void* u, const float* gate_bias, const void* branch, const float* lambda,
                       const float* h0, const uint8_t* tok, void* out, float* h_last, void* ws, size_t ws_bytes, int B,
                       int T, int D, int gate_width, float c, int io_dtype, void* stream);
 int rglru_grouped_bwd(const void* dout, const float* dh_last, const void* x, const void* u, const float* gate_bias,
                       const void* branch, const float* lambda, const float* h0, const uint8_t* tok, void* ws,
-                      size_t ws_bytes, void* dx, void* du, void* dbranch, float* dlambda, float* dh0, int B, int T, int D,
-                      int gate_width, float c, int io_dtype, void* stream);
+                      size_t ws_bytes, void* dx, void* du, void* dbranch, float* dlambda, float* dh0, float* d_gate_bias,
+                      int B, int T, int D, int gate_width, float c, int io_dtype, void* stream);
 
 /* Raw affine scan h_t = a_t h_{t-1} + b_t on fp32 tensors: the operator
  * fused_rglru_scan(decay, current_input, initial_state) of griffin/triton_scan.py:274-276

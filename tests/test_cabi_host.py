@@ -38,7 +38,7 @@ def test_library_exports_every_declared_symbol(lib):
     for name in names:
         assert hasattr(raw, name), f"{name} is declared in the header but not exported"
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
-    assert lib.rglru_abi_version() == 1
+    assert lib.rglru_abi_version() == 2
 
 
 def test_status_strings(lib):
@@ -53,8 +53,8 @@ def test_workspace_size_and_chunk(lib):
     assert chunk > 0 and chunk % 16 == 0
     B, T, D = 3, 130, 40
     nsave = -(-T // chunk)
-    # chunk-entry states, per-row dLambda partials, and a 256-byte tail holding the completion ticket
-    assert lib.rglru_workspace_bytes(B, T, D, _lib.F32) == 4 * (B * nsave * D + B * D) + 256
+    # chunk-entry states, per-row dLambda partials, a 256-byte tail holding the completion ticket, per-row gate sums
+    assert lib.rglru_workspace_bytes(B, T, D, _lib.F32) == 4 * (B * nsave * D + B * D) + 256 + 4 * B * 2 * D
     assert lib.rglru_workspace_bytes(0, T, D, _lib.F32) == 0
     assert lib.rglru_conv_bwd_workspace_bytes(B, T, D) >= 4 * 5 * D * B
     # the arithmetic that shape inference (the ops' fake implementations) uses is the library's own
@@ -92,8 +92,8 @@ def test_argument_validation_codes(lib):
     assert lib.rglru_grouped_fwd(q, q, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, 5, None) == _lib.ERR_BAD_DTYPE
     assert lib.rglru_grouped_fwd(q, q + 4, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_MISALIGNED
     assert lib.rglru_grouped_fwd(q, None, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
-    assert lib.rglru_grouped_bwd(q, None, q, q, None, q, q, None, None, q, 1 << 20, q, q, None, q, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
-    assert lib.rglru_grouped_bwd(q, None, q, q, None, None, q, None, None, q, 8, q, q, None, q, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
+    assert lib.rglru_grouped_bwd(q, None, q, q, None, q, q, None, None, q, 1 << 20, q, q, None, q, None, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_grouped_bwd(q, None, q, q, None, None, q, None, None, q, 8, q, q, None, q, None, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
     # branch merge: x, conv_w, conv_b, conv_state, u_r, u_i, branch, lambda, h0, tok, out, h_last, ws, ws_bytes, ...
     assert lib.rglru_merge_fwd(p, None, None, None, p, p, None, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_merge_fwd(p, None, None, None, p, p, p, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, 3, None) == _lib.ERR_BAD_DTYPE

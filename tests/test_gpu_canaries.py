@@ -98,11 +98,15 @@ def test_outputs_stay_inside_their_tensors(shape, dtype):
         u2 = rnd(B, T, 2 * D).to(dtype)
         gbias = rnd(2 * D)
         du2 = carve((B, T, 2 * D))
+        dgb = carve((2 * D,), torch.float32)
         check(lib.rglru_grouped_fwd(_p(x), _p(u2), _p(gbias), _p(br), _p(lam), _p(h0), _p(tok), _p(y), _p(hl), _p(ws), nb,
                                     B, T, D, bw, 8.0, io, st), "rglru_grouped_fwd")
         check(lib.rglru_grouped_bwd(_p(dy), _p(dh), _p(x), _p(u2), _p(gbias), _p(br), _p(lam), _p(h0), _p(tok), _p(ws), nb,
-                                    _p(dx), _p(du2), _p(dbr), _p(dlam), _p(dh0), B, T, D, bw, 8.0, io, st),
+                                    _p(dx), _p(du2), _p(dbr), _p(dlam), _p(dh0), _p(dgb), B, T, D, bw, 8.0, io, st),
               "rglru_grouped_bwd")
+        # the gate-bias gradient is the column sum of du (taken before rounding, rows folded in order)
+        want = du2.float().sum(dim=(0, 1))
+        assert float((dgb - want).norm() / want.norm().clamp_min(1e-20)) <= (1e-5 if dtype == torch.float32 else 2e-2)
     # conv alone
     xc, ns = carve((B, T, D)), carve((B, 3, D))
     check(lib.rglru_conv_fwd(_p(x), _p(w), _p(bias), _p(state), _p(tok), _p(xc), _p(ns), B, T, D, io, st), "rglru_conv_fwd")
