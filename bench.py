@@ -630,11 +630,15 @@ def run_lm(args, d: Dist, steps=None, warmup=None) -> dict:
     host_loss = torch.empty(1).pin_memory()
     sampler = ClockSampler(dev.index or 0)
 
+    import contextlib
+
     def train(ids):
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            logits = net(ids[:, :-1], pad_vocab=True)       # vocabulary padded to a multiple of 8, -inf in the padding
-        loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.size(-1)), ids[:, 1:].reshape(-1))
-        loss.backward()
+        # --ddp-no-sync: the same step without the gradient all-reduce (what the collective costs, by difference)
+        with (net.no_sync() if (world > 1 and args.ddp_no_sync) else contextlib.nullcontext()):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits = net(ids[:, :-1], pad_vocab=True)   # vocabulary padded to a multiple of 8, -inf in the padding
+            loss = torch.nn.functional.cross_entropy(logits.float().reshape(-1, logits.size(-1)), ids[:, 1:].reshape(-1))
+            loss.backward()
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
         opt.zero_grad(set_to_none=True)
@@ -657,7 +661,7 @@ def run_lm(args, d: Dist, steps=None, warmup=None) -> dict:
            "scaling": "weak", "vs_baseline": None,
            "dtype": "bf16 autocast (RG-LRU: bf16 I/O, fp32 state and arithmetic)", "data": "synthetic",
            "config": {"workload": f"c3: Griffin-100M ({nparams} params) train step B={B}/GPU T={T} vocab {V}, AdamW, "
-                                  f"{'DDP/NCCL' if world > 1 else 'single GPU'}",
+                                  f"{('DDP/NCCL' + (' WITHOUT all-reduce' if args.ddp_no_sync else '')) if world > 1 else 'single GPU'}",
                       "fold": args.fold, "l2": "activations of one step far exceed L2"},
            "e2e": {"value": world * B * T / e2e_ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B * (T + 1),
                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
@@ -746,6 +750,8 @@ def main() -> None:
     ap.add_argument("--no-extra", action="store_true", help="default workload: skip the c4a and c3 sub-objects")
     ap.add_argument("--no-repeat", action="store_true", help="time one region of K steps only (for profiler runs)")
     ap.add_argument("--no-kernel-timing", action="store_true", help="skip the per-kernel event pass (for profiler runs)")
+    ap.add_argument("--ddp-no-sync", action="store_true",
+                    help="c3 with N > 1: skip the gradient all-reduce (diagnostic: the step's cost without the collective)")
     ap.add_argument("--ref-gpu", action="store_true",
                     help="--impl reference: also time the staged reference's own GPU path (Triton / associative scan)")
     args = ap.parse_args()

@@ -33,6 +33,7 @@ SIGNATURES = {
     "rglru_chunk_steps": (_i, [_i]),
     "rglru_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "rglru_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _f, _i, _vp]),
+    "rglru_fwd_carry": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _f, _i, _vp]),
     "rglru_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
     "rglru_conv_scan_fwd": (_i, [_vp] * 11 + [_vp, _sz, _i, _i, _i, _f, _i, _vp]),
     "rglru_conv_scan_bwd": (_i, [_vp] * 11 + [_vp, _sz] + [_vp] * 5 + [_i, _i, _i, _f, _i, _vp]),
@@ -91,6 +92,23 @@ def check(code: int, what: str) -> None:
     if code == ERR_LAUNCH:
         text += f" ({lib.rglru_last_cuda_error().decode()})"
     raise RuntimeError("CUDA RG-LRU " + text)
+
+
+_TIMEOUT_NAMES = {1: "a tile load never completed", 2: "the producer never saw a chunk's results",
+                  3: "the wait self-test gave up (as it must)"}
+
+
+def check_device() -> None:
+    """Synchronise the current device and raise RuntimeError if a bounded wait inside a kernel has expired since
+    the last check (the kernel then ran to its end on garbage: its outputs, and gradients computed from them,
+    must not be used).  The check costs a device synchronisation, so it belongs at step boundaries -- a
+    training loop can call it every N optimizer steps; nothing on the operator path calls it by itself."""
+    detail = _i(0)
+    rc = load().rglru_device_status(ctypes.byref(detail))
+    if rc == ERR_DEVICE_TIMEOUT:
+        raise RuntimeError(f"CUDA RG-LRU: a bounded wait inside a kernel expired (detail {detail.value}: "
+                           f"{_TIMEOUT_NAMES.get(detail.value, 'unknown')}); results since the last check are invalid")
+    check(rc, "rglru_device_status")
 
 
 def device_status() -> int:

@@ -18,6 +18,7 @@ static int fail_cuda(cudaError_t e) {
   t_last_cuda = e;
   return RGLRU_ERR_LAUNCH;
 }
+int record_cuda_error(cudaError_t e) { return fail_cuda(e); }
 
 constexpr int MAX_DEVICES = 64;
 static std::mutex g_mutex;
@@ -204,9 +205,9 @@ size_t rglru_workspace_bytes(int B, int T, int D, int io_dtype) {
          static_cast<size_t>(B) * 2 * D * sizeof(float);
 }
 
-int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
-              const uint8_t* tok, void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c,
-              int io_dtype, void* stream) {
+static int fwd_common(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+                      const uint8_t* tok, void* y, float* h_last, float* decay_prod, void* ws, size_t ws_bytes, int B, int T,
+                      int D, float c, int io_dtype, void* stream) {
   if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
   if (!x || !u_r || !u_i || !lambda || !y) return RGLRU_ERR_NULL_POINTER;
   int rc = check_dims(B, T, D);
@@ -214,7 +215,7 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
   const bool bf16 = io_dtype == RGLRU_BF16;
   const size_t es = bf16 ? 2 : 4;
   if (!aligned(x, es) || !aligned(u_r, es) || !aligned(u_i, es) || !aligned(y, es) || !aligned(lambda, 4) ||
-      !aligned(h0, 4) || !aligned(h_last, 4) || !aligned(ws, 4))
+      !aligned(h0, 4) || !aligned(h_last, 4) || !aligned(decay_prod, 4) || !aligned(ws, 4))
     return RGLRU_ERR_MISALIGNED;
   if (ws && ws_bytes < rglru_workspace_bytes(B, T, D, io_dtype)) return RGLRU_ERR_WORKSPACE;
   int* status = nullptr;
@@ -223,7 +224,7 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
 
   ScanFwdArgs a = {};
   a.x = x; a.ur = u_r; a.ui = u_i; a.y = y;
-  a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last;
+  a.lambda = lambda; a.h0 = h0; a.tok = tok; a.h_last = h_last; a.decay_prod = decay_prod;
   a.states = static_cast<float*>(ws);
   {
     const size_t nsave = (static_cast<size_t>(T) + SAVE_EVERY - 1) / SAVE_EVERY;
@@ -243,6 +244,19 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
   }
   const cudaError_t e = launch_scan_fwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
+int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+              const uint8_t* tok, void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T, int D, float c,
+              int io_dtype, void* stream) {
+  return fwd_common(x, u_r, u_i, lambda, h0, tok, y, h_last, nullptr, ws, ws_bytes, B, T, D, c, io_dtype, stream);
+}
+
+int rglru_fwd_carry(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+                    const uint8_t* tok, void* y, float* h_last, float* decay_prod, void* ws, size_t ws_bytes, int B,
+                    int T, int D, float c, int io_dtype, void* stream) {
+  if (!h_last || !decay_prod) return RGLRU_ERR_NULL_POINTER;
+  return fwd_common(x, u_r, u_i, lambda, h0, tok, y, h_last, decay_prod, ws, ws_bytes, B, T, D, c, io_dtype, stream);
 }
 
 int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u_r, const void* u_i,

@@ -23,6 +23,7 @@ struct ScanFwdArgs {
   const float* h0;
   const uint8_t* tok;
   float* h_last;
+  float* decay_prod;  // [B, D] product of the (masked) decays over the whole sequence, or nullptr
   float* states;  // [B, ceil(T/SAVE_EVERY), D] or nullptr
   unsigned* ticket;  // completion counter of the workspace (zeroed here for the backward), or nullptr
   // conv-folded variant only: x is the conv INPUT; taps [D,4], bias [D] or nullptr, carried history [B,3,D] or nullptr
@@ -194,5 +195,8 @@ int raw_box_cols();
 cudaError_t launch_wait_selftest(int* status, int* finished, long long limit_cycles, cudaStream_t s);
 
 int* device_status_word();  // device address of the status word of the current device
+
+// Remember a CUDA error for rglru_last_cuda_error() (per host thread) and return RGLRU_ERR_LAUNCH.
+int record_cuda_error(cudaError_t e);
 
 }  // namespace rglru

@@ -6,10 +6,17 @@
 // device memory and hands out none, a callback where cudaMalloc would synchronise the device).  For
 // them this entry point keeps the scratch in a fixed array that is part of the library image.
 //
-// Cost and limits: the array occupies kScratchFloats * 4 bytes on EVERY GPU that loads the library,
-// from load until process exit, whether or not this entry point is ever called.  Larger problems are
-// refused with RGLRU_ERR_TOO_LARGE.  All calls share the one array, so two calls whose kernels can
-// overlap on the GPU (different streams) race on it; calls on one stream are safe.
+// Cost and limits: the array occupies kScratchFloats * 4 bytes on every GPU on which the library's
+// device code gets loaded, until process exit.  With CUDA's lazy module loading (the default) that
+// happens at the first use on a device -- the first call of this entry point resolves the array's
+// address and loads the kernels, which may itself allocate and synchronise -- so a host with a
+// no-allocation region makes ONE warm-up call per device before entering it (and before any stream
+// capture).  Larger problems are refused with RGLRU_ERR_TOO_LARGE.  All calls share the one array, so
+// two calls whose kernels can overlap on the GPU (different streams) race on it; calls on one stream
+// are safe.  The scratch address belongs to the device that is current at the call, so `stream` must
+// be a stream of that device.  This entry point always runs the kernels that split the time axis
+// (one thread per run of 32 steps); it never takes the TMA-staged kernels that rglru_conv_bwd may
+// choose for large batches, so the two can differ in speed, not in results beyond rounding.
 
 #include <mutex>
 
@@ -32,17 +39,17 @@ static float* g_scratch_ptr[kMaxDevices] = {nullptr};
 static int scratch_for_current_device(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return RGLRU_ERR_LAUNCH;
+  if (e != cudaSuccess) return record_cuda_error(e);
   if (dev < 0 || dev >= kMaxDevices) return RGLRU_ERR_UNSUPPORTED;
   std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (!g_scratch_ptr[dev]) {
     int major = 0;
     e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-    if (e != cudaSuccess) return RGLRU_ERR_LAUNCH;
+    if (e != cudaSuccess) return record_cuda_error(e);
     if (major != 10) return RGLRU_ERR_UNSUPPORTED;
     float* ptr = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_conv_bwd_scratch);
-    if (e != cudaSuccess || !ptr) return RGLRU_ERR_LAUNCH;
+    if (e != cudaSuccess || !ptr) return record_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
     g_scratch_ptr[dev] = ptr;
   }
   *out = g_scratch_ptr[dev];
@@ -86,7 +93,7 @@ int rglru_conv_bwd_noalloc(const void* d_conv, const void* x_in, const float* co
   a.vector_ok = (static_cast<size_t>(D) * es) % 16 == 0 && aligned(d_conv, 16) && aligned(x_in, 16) &&
                 aligned(dx_in, 16) && aligned(conv_state, 16) && aligned(d_state, 16) && aligned(conv_w, 16);
   const cudaError_t e = launch_conv_bwd(bf16, a, static_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? RGLRU_OK : RGLRU_ERR_LAUNCH;
+  return e == cudaSuccess ? RGLRU_OK : record_cuda_error(e);
 }
 
 }  // extern "C"

@@ -404,6 +404,10 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   float carry = 0.0f;
   const int dch = d0 + cch;
   if (chain_thread && dch < p.D && p.h0) carry = p.h0[static_cast<size_t>(b) * p.D + dch];
+  // Product of the decays over the sequence: with the final state it is the affine map h0 -> h_last of this
+  // call, which is what a caller that splits one sequence over several calls (or GPUs) needs to chain them.
+  const bool want_prod = p.decay_prod != nullptr;
+  float prod_all = 1.0f;
 
   const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
 
@@ -469,6 +473,10 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
           e = fmaf(ag[j].x, e, ag[j].y);
         }
         carry = e;
+        if (want_prod) {
+#pragma unroll
+          for (int j = 0; j < LANES; ++j) prod_all *= ag[j].x;
+        }
       } else {
         // Each thread composes its segment from the identity, keeping the map (pp, sp) that takes the state
         // entering the segment to the state entering each of its lanes; the segment totals are exchanged through
@@ -490,6 +498,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
           const float2 tot = segtot[sgm * CH + cch];
           if (sgm == seg) enter = e;
           e = fmaf(tot.x, e, tot.y);
+          prod_all *= tot.x;
         }
         carry = e;
 #pragma unroll
@@ -527,6 +536,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
     }
   }
   if (tid < CH && dch < p.D && p.h_last) p.h_last[static_cast<size_t>(b) * p.D + dch] = carry;   // segment 0's copy
+  if (tid < CH && dch < p.D && want_prod) p.decay_prod[static_cast<size_t>(b) * p.D + dch] = prod_all;
 }
 
 // PLAIN: no token flags and a whole number of chunks, so the masked arithmetic is not compiled in.

@@ -359,7 +359,8 @@ class RecurrentBlock(nn.Module):
                 lru.input_gate.weight, lru.input_gate.bias, lru.Lambda, rnn_state, flags, lru.c,
                 y_branch if self.fold_merge else None)
         else:
-            x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags)
+            x_conv, new_conv = ops.causal_conv(x_in, conv_w, self.temporal_conv.bias, conv_state, flags,
+                                               want_state=return_cache)
             y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags,
                                      _branch=y_branch if self.fold_merge else None)
         if restore is not None:

@@ -291,17 +291,19 @@ def linear_scan(decay: Tensor, current_input: Tensor, initial_state: Tensor) -> 
 
 
 # ----------------------------------------------------------------------------- causal conv
-def _conv_fwd_impl(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tensor], tok: Optional[Tensor]
-              ) -> tuple[Tensor, Tensor]:
+def _conv_fwd_impl(x_in: Tensor, w: Tensor, b: Optional[Tensor], state: Optional[Tensor], tok: Optional[Tensor],
+                   want_state: bool = True) -> tuple[Tensor, Tensor]:
+    """(conv output, next conv state [B,3,D]); without ``want_state`` the second result is empty and the small kernel
+    that gathers it is not launched (a training step that keeps no cache has no use for it)."""
     lib = _lib.load()
     _require_cuda(x_in, w, b, state, tok)
     dt = _io_dtype(x_in, "conv")
     B, T, D = x_in.shape
     out = torch.empty_like(x_in)
-    new_state = torch.empty(B, 3, D, device=x_in.device, dtype=x_in.dtype)
+    new_state = torch.empty((B, 3, D) if want_state else (0,), device=x_in.device, dtype=x_in.dtype)
     with _on(x_in, "rglru_conv_fwd"):
-        rc = lib.rglru_conv_fwd(_ptr(x_in), _ptr(w), _ptr(b), _ptr(state), _ptr(tok), _ptr(out), _ptr(new_state),
-                                B, T, D, dt, _stream(x_in))
+        rc = lib.rglru_conv_fwd(_ptr(x_in), _ptr(w), _ptr(b), _ptr(state), _ptr(tok), _ptr(out),
+                                _ptr(new_state) if want_state else None, B, T, D, dt, _stream(x_in))
     _lib.check(rc, "rglru_conv_fwd")
     return out, new_state
 
@@ -310,9 +312,9 @@ _conv_fwd = torch.library.custom_op("griffin_b200::conv_fwd", _conv_fwd_impl, mu
 
 
 @_conv_fwd.register_fake
-def _(x_in, w, b, state, tok):
+def _(x_in, w, b, state, tok, want_state=True):
     B, T, D = x_in.shape
-    return torch.empty_like(x_in), x_in.new_empty((B, 3, D))
+    return torch.empty_like(x_in), x_in.new_empty((B, 3, D) if want_state else (0,))
 
 
 def _conv_bwd_impl(d_conv: Tensor, x_in: Tensor, w: Tensor, state: Optional[Tensor], tok: Optional[Tensor],
@@ -345,7 +347,7 @@ def _(d_conv, x_in, w, state, tok, want_state):
 
 
 def _conv_setup(ctx, inputs, output):
-    x_in, w, b, state, tok = inputs
+    x_in, w, b, state, tok = inputs[:5]
     ctx.save_for_backward(x_in, w, state, tok)
     ctx.has_bias = b is not None
     ctx.want_state = state is not None and ctx.needs_input_grad[3]
@@ -356,7 +358,7 @@ def _conv_backward(ctx, d_out, _d_new_state, _bwd=None):
     if d_out is None:
         d_out = torch.zeros_like(x_in)
     dx, d_w, d_b, d_state = (_bwd or _conv_bwd)(d_out.contiguous(), x_in, w, state, tok, ctx.want_state)
-    return dx, d_w, (d_b if ctx.has_bias else None), (d_state if ctx.want_state else None), None
+    return dx, d_w, (d_b if ctx.has_bias else None), (d_state if ctx.want_state else None), None, None
 
 
 _conv_fwd.register_autograd(_conv_backward, setup_context=_conv_setup)
@@ -364,7 +366,7 @@ _ConvNode = _eager_node("CausalConv", _conv_fwd_impl, _conv_setup, _conv_backwar
 
 
 def causal_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state: Optional[Tensor] = None,
-                tok: Optional[Tensor] = None) -> tuple[Tensor, Tensor]:
+                tok: Optional[Tensor] = None, want_state: bool = True) -> tuple[Tensor, Tensor]:
     """Width-4 depthwise causal convolution; ``weight`` is [D, 4] with column 3 on the current token.
 
     Returns the convolved sequence and the next conv state [B, 3, D].  The gradient with
@@ -378,7 +380,7 @@ def causal_conv(x_in: Tensor, weight: Tensor, bias: Optional[Tensor], conv_state
     b = None if bias is None else bias.to(torch.float32).contiguous()
     st = None if conv_state is None else conv_state.to(x_in.dtype).contiguous()
     return (_conv_fwd if _library_ops_active() else _ConvNode.apply)(
-        x_in.contiguous(), w, b, st, None if tok is None else tok.contiguous())
+        x_in.contiguous(), w, b, st, None if tok is None else tok.contiguous(), want_state)
 
 
 # ----------------------------------------------------------------------------- conv folded into the scan
@@ -766,7 +768,7 @@ def _core_bwd_impl(dy: Tensor, dh_last: Optional[Tensor], x_in: Tensor, conv_w: 
         else:
             dxc, du_r, du_i, dbranch, dlam, dh0 = merge_scan_bwd(dy, dh_last, x_in, conv_w, conv_b, conv_state, u_r, u_i,
                                                                  branch, lam, h0, tok, ws, c, want_dh0)
-        x_conv, _ = _conv_fwd_impl(x_in, conv_w, conv_b, conv_state, tok)     # recomputed, not saved
+        x_conv, _ = _conv_fwd_impl(x_in, conv_w, conv_b, conv_state, tok, False)     # recomputed, not saved
         dx_r, dw_r, db_r = _gate_backward(du_r, x_conv, w_r)
         dx_i, dw_i, db_i = _gate_backward(du_i, x_conv, w_i)
         total = (dxc + dx_r + dx_i).contiguous()

@@ -92,6 +92,16 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
               const uint8_t* tok, void* y, float* h_last, void* ws, size_t ws_bytes, int B, int T,
               int D, float c, int io_dtype, void* stream);
 
+/* rglru_fwd that also returns the product of the decays over the sequence, decay_prod [B,D] fp32 (with masks
+ * applied: 0 through a reset, 1 through padding).  Together with h_last computed from h0 = 0 it is the affine
+ * map  h_last(h0) = decay_prod * h0 + h_last(0)  of this call, which lets one sequence be split over several
+ * calls, or over the GPUs of a box along TIME, with one small exchange of [B,D] pairs between the pieces
+ * (the associative operator of griffin/griffin.py:291-306 applied to whole slices).  The reference has no
+ * such entry point; griffin_b200/time_shard.py is its user.  h_last and decay_prod are required. */
+int rglru_fwd_carry(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
+                    const uint8_t* tok, void* y, float* h_last, float* decay_prod, void* ws, size_t ws_bytes, int B,
+                    int T, int D, float c, int io_dtype, void* stream);
+
 /* Backward of rglru_fwd.  The reference obtains these gradients from autograd over
  * griffin/griffin.py:237-286 with the capped sqrt slope of griffin/griffin.py:59-65
  * and, for the scan itself, griffin/triton_scan.py:63-122.
@@ -210,12 +220,18 @@ int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, co
  * point where the backward runs -- a runtime that owns all device memory and lends none to plugins,
  * a serving loop whose memory plan is frozen, a callback in which an allocation would synchronise
  * the device.)  Same arguments and results as rglru_conv_bwd, minus the workspace: the partial sums
- * live in a fixed 4 MiB array inside the library image, which every GPU that loads the library holds
- * until the process exits.
+ * live in a fixed 4 MiB array inside the library image, which every GPU on which the library's device
+ * code is loaded holds until the process exits.
  *   - Limit: B * ceil(T / 256) * 5 * D <= 1,048,576 floats (rglru_conv_bwd_noalloc_max_bytes() / 4);
  *     anything larger returns RGLRU_ERR_TOO_LARGE and launches nothing.
- *   - The first call on each device looks up the array's device address (with that device current);
- *     make that first call outside any stream capture.
+ *   - The first call on each device looks up the array's device address (with that device current)
+ *     and, under CUDA's lazy module loading, is also what loads the kernels and the array: it may
+ *     allocate and synchronise inside the driver.  Make one warm-up call per device BEFORE entering the
+ *     region where allocation is forbidden, and outside any stream capture.
+ *   - `stream` must belong to the device that is current at the call (the scratch address is that
+ *     device's); a stream of another device fails with RGLRU_ERR_LAUNCH.
+ *   - It always runs the kernels that split the time axis; the TMA-staged kernels that rglru_conv_bwd
+ *     may pick for large batches are not used here (same results up to rounding, possibly slower).
  *   - All calls share the array.  Calls on one stream are ordered and safe; calls that can overlap
  *     on the GPU (different streams, several host threads) race on it and must be serialised by the
  *     caller.  Nothing needs clearing between calls: every entry read is written first by the same call.

@@ -270,6 +270,12 @@ def test_bounded_wait_gives_up_and_reports_without_hanging():
         _lib.check(_lib.ERR_DEVICE_TIMEOUT, "self-test")
     assert lib.rglru_selftest_wait_timeout(0, None, None) == _lib.ERR_BAD_SHAPE
     assert lib.rglru_selftest_wait_timeout(200000, None, None) == _lib.ERR_BAD_SHAPE
+    # the step-boundary helper a training loop would call: raises once with the detail, then the status is clear
+    import griffin_b200
+    assert lib.rglru_selftest_wait_timeout(300, finished.data_ptr(), torch.cuda.current_stream().cuda_stream) == _lib.OK
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        griffin_b200.check_device()
+    griffin_b200.check_device()
     # the context is intact: a regular call works and reports a clean status
     case = orc.make_rglru_case(2, 70, 64, 4, seed=3)
     u_r = orc.block_diagonal_linear(case["x"], case["recurrence_gate.weight"], case["recurrence_gate.bias"])

@@ -66,7 +66,7 @@ def test_opcheck_on_the_registered_operators():
     torch.library.opcheck(ops._rglru_fwd, (x, u_r, u_i, lam, h0, tok, 8.0, True), test_utils=tests)
     w = torch.randn(D, 4, device=dev, requires_grad=True)
     bias = torch.randn(D, device=dev, requires_grad=True)
-    torch.library.opcheck(ops._conv_fwd, (x, w, bias, None, tok), test_utils=tests)
+    torch.library.opcheck(ops._conv_fwd, (x, w, bias, None, tok, True), test_utils=tests)
     decay = torch.rand(B, T, D, device=dev, requires_grad=True)
     torch.library.opcheck(ops._scan_fwd, (decay, x, h0), test_utils=tests)
     branch = torch.randn(B, T, D, device=dev, requires_grad=True)

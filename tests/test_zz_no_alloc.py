@@ -34,6 +34,20 @@ def _case(B, T, D, dtype, seed, with_state, with_flags):
     return t
 
 
+def _oracle_grads(t, B, T, D):
+    """Gradients of sum(conv(x_in) * d_conv) from the CPU oracle in fp64; the token flags used here carry only
+    the number of taps to cut (3 - min(position, 3)), so positions are recovered from them."""
+    from oracle import rglru_oracle as orc
+    x = t["x_in"].double().cpu().requires_grad_(True)
+    w = t["w"].double().cpu().requires_grad_(True)
+    b = torch.zeros(D, dtype=torch.float64, requires_grad=True)
+    state = (torch.zeros(B, 3, D, dtype=torch.float64) if t["state"] is None else t["state"].double().cpu()).requires_grad_(True)
+    seg = torch.full((B, T), 3, dtype=torch.long) if t["tok"] is None else 3 - (t["tok"].cpu().long() & 3)
+    out, _ = orc.causal_conv_dense(x, w, b, state, seg)
+    (out * t["d_conv"].double().cpu()).sum().backward()
+    return {"dx": x.grad, "d_w": w.grad, "d_b": b.grad, "d_state": state.grad}
+
+
 def _run(lib, name, t, B, T, D, io, with_ws):
     dtype = t["x_in"].dtype
     out = {
@@ -74,6 +88,10 @@ def test_noalloc_conv_backward_matches_workspace_version_twice_in_a_row():
         for key in ("dx", "d_w", "d_b", "d_state"):
             assert torch.isfinite(got[key].float()).all(), key
             assert rel_l2(got[key], want[key]) <= tol, key
+        # ... and against the oracle's conv (griffin/griffin.py:474-487 of the reference) differentiated by autograd
+        ref = _oracle_grads(t, B, T, D)
+        for key in ("dx", "d_w", "d_b") + (("d_state",) if with_state else ()):
+            assert rel_l2(got[key], ref[key]) <= tol, (key, "oracle")
 
 
 def test_noalloc_rejects_problems_beyond_its_fixed_scratch():
