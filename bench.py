@@ -173,7 +173,8 @@ class LayerKernels:
         self.h_last = torch.empty(B, D, device=dev)
         self.dlam = torch.empty(D, device=dev)
         self.ws_bytes = self.lib.rglru_workspace_bytes(B, T, D, self.io)
-        self.ws = torch.empty(self.ws_bytes, device=dev, dtype=torch.uint8)
+        # one workspace per set: the backward of a set reads the states its own forward left there
+        self.wss = [torch.empty(self.ws_bytes, device=dev, dtype=torch.uint8) for _ in range(self.nsets)]
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         self.calls = 0
         self.kernels_per_step = 2 if B <= 64 else 3      # fwd + bwd (+ the dLambda fold kernel for B > 64)
@@ -181,8 +182,9 @@ class LayerKernels:
     def fwd(self, s):
         x, u_r, u_i, _ = self.sets[s % self.nsets]
         y = self.outs[s % self.nsets][0]
+        ws = self.wss[s % self.nsets]
         rc = self.lib.rglru_fwd(x.data_ptr(), u_r.data_ptr(), u_i.data_ptr(), self.lam.data_ptr(), None, None,
-                                y.data_ptr(), self.h_last.data_ptr(), self.ws.data_ptr(), self.ws_bytes,
+                                y.data_ptr(), self.h_last.data_ptr(), ws.data_ptr(), self.ws_bytes,
                                 self.B, self.T, self.D, 8.0, self.io, self.stream)
         self._lib.check(rc, "rglru_fwd")
         self.calls += 1
@@ -190,8 +192,9 @@ class LayerKernels:
     def bwd(self, s):
         x, u_r, u_i, dy = self.sets[s % self.nsets]
         _, dx, du_r, du_i = self.outs[s % self.nsets]
+        ws = self.wss[s % self.nsets]
         rc = self.lib.rglru_bwd(dy.data_ptr(), None, x.data_ptr(), u_r.data_ptr(), u_i.data_ptr(), self.lam.data_ptr(),
-                                None, None, self.ws.data_ptr(), self.ws_bytes, dx.data_ptr(), du_r.data_ptr(),
+                                None, None, ws.data_ptr(), self.ws_bytes, dx.data_ptr(), du_r.data_ptr(),
                                 du_i.data_ptr(), self.dlam.data_ptr(), None, self.B, self.T, self.D, 8.0, self.io,
                                 self.stream)
         self._lib.check(rc, "rglru_bwd")
@@ -240,18 +243,23 @@ def run_layer(args, d: Dist) -> dict:
     ms_step, regions = timed_steps(d, k.step, args.steps, repeats)
     launches = k.calls // 2 * k.kernels_per_step // repeats        # counted calls of one region x kernels per call
 
-    # ---- region 2: per-kernel durations (CUDA events around every launch, same stream)
+    # ---- region 2: per-kernel durations: each kernel launched back to back over the rotating sets, CUDA events
+    # on the launching stream around the run (an event between every two launches would keep a kernel's prologue
+    # from overlapping the tail of the one before it, which it does in region 1)
     reps = 1 if args.no_kernel_timing else max(args.steps, 200)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(reps)]
-    for i in range(reps):
-        evs[i][0].record()
-        k.fwd(i)
-        evs[i][1].record()
-        k.bwd(i)
-        evs[i][2].record()
+    for s_ in range(k.nsets):
+        k.fwd(s_)                                   # every set's workspace now holds its forward's states
     torch.cuda.synchronize(dev)
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    per_kernel = {}
+    for name, launch in (("rglru_fwd", k.fwd), ("rglru_bwd", k.bwd)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        per_kernel[name] = e0.elapsed_time(e1) / reps
+    fwd_ms, bwd_ms = per_kernel["rglru_fwd"], per_kernel["rglru_bwd"]
 
     # ---- region 3: end to end through the module API from pinned host memory, every result read back
     e2e = None

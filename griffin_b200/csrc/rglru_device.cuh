@@ -131,6 +131,14 @@ __device__ __forceinline__ void tma_store_3d(const void* map, const void* src, i
                "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+// Ask the copy engine to bring a tile into L2 without waiting for it and without touching shared memory.  A
+// prefetch changes no data, so it may be issued before pdl_wait: if the preceding kernel is still writing the
+// tensor, its writes land in the same L2 and nothing stale is ever read.
+__device__ __forceinline__ void tma_prefetch_3d(const void* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_wait_read() {
@@ -175,8 +183,9 @@ __device__ __forceinline__ float rsqrt_approx(float x) {
 }
 
 // ---------------------------------------------------------------- packed fp32 (two lanes per instruction)
-// sm_100 executes add/mul/fma on a pair of fp32 values in one issue slot; the scan
-// kernels are issue-bound, so all channel arithmetic is written on float2 pairs.
+// sm_100 executes add/mul/fma on a pair of fp32 values in one issue slot (the FMA pipe is busy two cycles
+// for it, so lane throughput is unchanged; what is saved is instruction issue and dependency tracking), so
+// all channel arithmetic is written on float2 pairs.
 __device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }

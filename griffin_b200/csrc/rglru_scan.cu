@@ -1,36 +1,40 @@
 // RG-LRU forward and backward kernels for sm_100a.
 //
-// Work decomposition.  A CTA owns CH = 64 adjacent channels of one batch row and
-// walks the whole sequence in chunks of LANES*TS time-steps.  Inside a chunk the
-// time axis is split over LANES (16 or 32) time-lanes, each thread scanning TS
-// steps of CV = 4 channels in registers (level one), after which one thread per
-// channel chains the lane aggregates and the carry from the previous chunk
-// (level two) and every lane applies its incoming state.  Chunks are staged
-// through shared memory by TMA (cp.async.bulk.tensor, 3-D tiles [1, rows, 64
-// channels]) in a multi-stage mbarrier pipeline; results are written back into
-// the stage in place and leave through TMA stores.  A bounds-checked plain-load
-// staging path with the same arithmetic covers shapes TMA cannot address
-// (D * element size not a multiple of 16 bytes).
+// Work decomposition.  A CTA owns CH (64 or 32) adjacent channels of one batch row and walks the whole
+// sequence in chunks of LANES*TS time-steps.  Inside a chunk the time axis is split over LANES (16 or 32)
+// time-lanes, each thread scanning TS = 4 steps of CV = 4 channels in registers (level one), after which a
+// few threads per channel chain the lane aggregates and the carry from the previous chunk through shared
+// memory (level two: one serial chain of 16 for the 64-channel shape, four segments of eight joined by a
+// small exchange for the 32-lane shape) and every lane applies its incoming state.  Chunks are staged through
+// shared memory by TMA (cp.async.bulk.tensor, 3-D tiles [1, rows, channels]) in a multi-stage mbarrier
+// pipeline; results are written back into the stage in place and leave through TMA stores.  The bulk copies
+// are issued either by a producer warp or, for the bf16 backward, by one compute thread (SELF_ISSUE: eight
+// warps leave every thread the registers it wants).  A bounds-checked plain-load staging path with the same
+// arithmetic covers shapes TMA cannot address (D * element size not a multiple of 16 bytes).
 //
-// The kernels are bound by instruction issue before they are bound by HBM, so
-// the channel arithmetic is written on float2 pairs (one issue slot per two
-// fp32 operations on sm_100) and transcendental work is kept to four MUFU
-// operations per element.
+// What bounds them (ncu on B200, bf16, B = 8, T = 2048, D = 1024): DRAM traffic equals the algorithmic bytes;
+// no pipe is more than 40 % busy and 0.4 instructions issue per scheduler and cycle: with one (backward) or two
+// (forward) CTAs per SM the kernels are bound by dependent-instruction latency inside a warp and by what
+// happens outside the chunk loop, so the channel arithmetic is written on float2 pairs (one issue slot per two
+// fp32 operations), transcendental work is kept to three or four MUFU operations per element, and the
+// prologue (first loads issued before the per-channel rates are worked out, the first chunk prefetched into
+// L2 before the dependency wait) and the epilogue (row sums folded by the last CTA with all loads in flight
+// at once) are kept short.  Sixteen-warp variants with two steps per thread measured 15 % slower.
 //
-// The gate epilogue follows griffin/griffin.py:237-258 of the reference, the
-// scan :280-286, the backward is the closed form of autograd over those lines
-// with the capped sqrt slope of :59-65.  All arithmetic is fp32.
+// The gate epilogue follows griffin/griffin.py:237-258 of the reference, the scan :280-286, the backward is
+// the closed form of autograd over those lines with the capped sqrt slope of :59-65.  All arithmetic is fp32.
 //
-// Template switches of the two kernels (each a separate instantiation, so the
-// plain kernels pay nothing for them):
-//   CONV    the width-4 causal conv in front of the layer (:474-486) is applied
-//           while a chunk is loaded, from an x tile with a three-row halo;
-//   MERGE   the block's GeLU-branch product (:464, :520) is formed in the store
-//           stage and differentiated in the backward's load stage;
-//   GROUPED both gate pre-activations come from one [B, T, 2 D] tensor written
-//           by a single grouped GEMM, and the gate biases are added here.
-// The file also holds the raw affine scan operator (triton_scan.py:274-276), the
-// TMA-staged kernels of the conv alone, and the self-test of the bounded wait.
+// Template switches of the two kernels (each a separate instantiation, so the plain kernels pay nothing for
+// them):
+//   CONV    the width-4 causal conv in front of the layer (:474-486) is applied while a chunk is loaded, from
+//           an x tile with a three-row halo;
+//   MERGE   the block's GeLU-branch product (:464, :520) is formed in the store stage and differentiated in
+//           the backward's load stage;
+//   GROUPED both gate pre-activations come from one [B, T, 2 D] tensor written by a single grouped GEMM, the
+//           gate biases are added here, and the backward also returns their gradient (column sums of du);
+//   PLAIN   no token flags and a whole number of chunks: the masked arithmetic is not compiled in.
+// The file also holds the raw affine scan operator (triton_scan.py:274-276), the TMA-staged kernels of the
+// conv alone, and the self-test of the bounded wait.
 
 #include <atomic>
 #include <cstdlib>
@@ -350,6 +354,11 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       mbar_fence_init();
       prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
       if (MERGE) prefetch_map(&maps.g);
+      // While the kernel in front of this one on the stream drains, pull the first chunk towards L2.
+      tma_prefetch_3d(&maps.x, d0, -(CONV ? 3 : 0), b);
+      tma_prefetch_3d(&maps.ur, rcol, 0, b);
+      tma_prefetch_3d(&maps.ui, icol, 0, b);
+      if (MERGE) tma_prefetch_3d(&maps.g, d0, 0, b);
     }
   }
   __syncthreads();
@@ -821,6 +830,14 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
       prefetch_map(&maps.dy); prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui);
       prefetch_map(&maps.dx); prefetch_map(&maps.dur); prefetch_map(&maps.dui);
       if (MERGE) { prefetch_map(&maps.g); prefetch_map(&maps.dg); }
+      // While the kernel in front of this one on the stream drains, pull the first chunk (the last in time)
+      // towards L2.
+      const int kl = nchunks - 1;
+      tma_prefetch_3d(&maps.dy, d0, kl * TC, b);
+      tma_prefetch_3d(&maps.x, d0, kl * TC - (CONV ? 3 : 0), b);
+      tma_prefetch_3d(&maps.ur, rcol, kl * TC, b);
+      tma_prefetch_3d(&maps.ui, icol, kl * TC, b);
+      if (MERGE) tma_prefetch_3d(&maps.g, d0, kl * TC, b);
     }
   }
   __syncthreads();
@@ -1924,8 +1941,11 @@ static cudaError_t launch_grouped_fwd_t(const FwdMaps& maps, const ScanFwdArgs& 
 template <typename IO, bool MERGE>
 static cudaError_t launch_grouped_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
-  if constexpr (H) return launch_bwd_t<IO, Shape64x16x4, MERGE ? 4 : 5, true, false, MERGE, true, true>(maps, a, s);
-  else return launch_bwd_t<IO, Shape64x16x4, MERGE ? 2 : 3, true, false, MERGE, true>(maps, a, s);
+  // Measured on B200 at B = 16, T = 2048, D = 1024 bf16: with the branch merge (five loads and four stores per
+  // chunk) the producer warp wins although the kernel then spills a little at its 168-register limit (162 us
+  // against 169 us with the copies issued by a compute thread); without the merge the compute-thread variant does.
+  if constexpr (H && !MERGE) return launch_bwd_t<IO, Shape64x16x4, 5, true, false, false, true, true>(maps, a, s);
+  else return launch_bwd_t<IO, Shape64x16x4, H ? 4 : (MERGE ? 2 : 3), true, false, MERGE, true>(maps, a, s);
 }
 cudaError_t launch_grouped_fwd(bool bf16, bool merge, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   if (bf16) return merge ? launch_grouped_fwd_t<__nv_bfloat16, true>(maps, a, s) : launch_grouped_fwd_t<__nv_bfloat16, false>(maps, a, s);
