@@ -409,6 +409,73 @@ def run_c4a_shard(args, d: Dist) -> dict:
     return out
 
 
+def run_time_shard(args, d: Dist) -> dict:
+    """One sequence of B=8, D=1024, bf16, T = 8192 per rank, split along TIME over the ranks: forward + backward
+    through ``griffin_b200.time_shard.rglru_time_sharded`` (two scan passes on every rank but one per direction,
+    one all-gather of [B, D] pairs per direction over NCCL); beside it the same rank's slice as an ordinary
+    unsplit call, i.e. what the step would cost were there no carry between the slices."""
+    from griffin_b200 import _lib, ops
+    from griffin_b200.time_shard import rglru_time_sharded
+
+    B, TS, D = 8, 8192, 1024
+    dev, world = d.dev, d.world
+    if world == 1 and not d.dist.is_initialized():     # the operator wants a process group even for one slice
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        d.dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    g = torch.Generator(device=dev).manual_seed(11 + d.rank)
+    sets = []
+    for _ in range(3):    # 3 x 4 tensors x 134 MB: a step never finds its inputs in L2
+        x = torch.randn(B, TS, D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        u_r = torch.randn(B, TS, D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        u_i = torch.randn(B, TS, D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+        dy = torch.randn(B, TS, D, device=dev, generator=g).to(torch.bfloat16)
+        sets.append((x, u_r, u_i, dy))
+    lam = torch.logit(torch.empty(D, device=dev).uniform_(0.9, 0.999, generator=g).pow(1.0 / 8.0)).requires_grad_(True)
+
+    def clear(x, u_r, u_i):
+        x.grad = u_r.grad = u_i.grad = lam.grad = None
+
+    def sharded(i):
+        x, u_r, u_i, dy = sets[i % 3]
+        clear(x, u_r, u_i)
+        y, _ = rglru_time_sharded(x, u_r, u_i, lam, None, None, 8.0, None)
+        y.backward(dy)
+
+    def unsplit(i):
+        x, u_r, u_i, dy = sets[i % 3]
+        clear(x, u_r, u_i)
+        y, _ = ops.rglru(x, u_r, u_i, lam, None, None, 8.0)
+        y.backward(dy)
+
+    sampler = ClockSampler(dev.index or 0).start()
+    steps = max(3, min(args.steps, 50))
+    for w in range(max(3, args.warmup)):
+        sharded(w)
+        unsplit(w)
+    ms, regions = timed_steps(d, sharded, steps, 3)
+    ms_one, _ = timed_steps(d, unsplit, steps, 3)
+    clocks = sampler.stop()
+    if world == 1:
+        d.dist.destroy_process_group()
+    peak, kind = measured_peak()
+    total = 22 * B * TS * world * D          # algorithmic bytes of the whole sequence, forward + backward
+    return {"metric": "rglru_time_sharded_fwd_bwd_hbm_gbs", "value": total / ms / 1e6, "unit": "GB/s", "n_gpus": world,
+            "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 I/O, f32 state", "data": "synthetic",
+            "config": {"workload": f"time-sharded RG-LRU fwd+bwd bf16 B={B} T={TS * world} ({TS} per rank) D={D}",
+                       "l2": "three rotating input sets of 537 MB each"},
+            "timing": {"regions": len(regions), "value_is": "median over regions",
+                       "ms_per_step_min": min(regions), "ms_per_step_max": max(regions)},
+            "unsplit_slice_ms_per_step": ms_one, "cost_of_the_split": ms / ms_one,
+            "exchange_bytes_per_rank_per_step": 2 * 2 * B * D * 4,
+            "frac_of_hbm_peak_per_gpu": total / world / ms / 1e6 / peak, "peak_source": f"of {kind}",
+            "gpu_launches": (4 if world > 1 else 2) * steps, "clocks": clocks, "device_status": _lib.device_status(),
+            "roofline": {"bound": "hbm", "note": "algorithmic bytes count ONE pass per direction; all ranks but one run two",
+                         "achieved": total / world / ms / 1e6, "peak": peak, "peak_source": f"of {kind}", "unit": "GB/s",
+                         "frac": total / world / ms / 1e6 / peak, "traffic": None}}
+
+
 def cpu_baseline(workload: str, steps: int = 1) -> dict:
     """The reference's sequential path forward+backward on the host cores.
 
@@ -749,7 +816,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["c2", "c3", "c4b"])
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["c2", "c3", "c4b", "tshard"])
     ap.add_argument("--fold", default="merge", choices=["none", "conv", "merge"],
                     help="c2/c3: run conv (and the GeLU-branch product) inside the scan kernels")
     ap.add_argument("--graph", action="store_true", help="c2: replay the block's forward and backward as CUDA graphs")
@@ -778,6 +845,8 @@ def main() -> None:
         out = run_lm(args, d)
     elif args.workload == "c4b":
         out = run_decode(args, d)
+    elif args.workload == "tshard":
+        out = run_time_shard(args, d)
     else:
         out = run_layer(args, d)
         if args.workload == "c1" and not args.no_extra:

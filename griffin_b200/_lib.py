@@ -48,6 +48,8 @@ SIGNATURES = {
     "rglru_conv_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _i, _i, _i, _vp]),
     "rglru_conv_bwd_noalloc_max_bytes": (_sz, []),
     "rglru_conv_bwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "rglru_column_sums_workspace_bytes": (_sz, [ctypes.c_longlong, _i]),
+    "rglru_column_sums": (_i, [_vp, _vp, _vp, _sz, ctypes.c_longlong, _i, _i, _vp]),
     "rglru_decode_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "rglru_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
 }

@@ -710,6 +710,29 @@ int rglru_conv_bwd(const void* d_conv, const void* x_in, const float* conv_w, co
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
 }
 
+size_t rglru_column_sums_workspace_bytes(long long rows, int cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<size_t>(colsum_row_blocks(rows, cols)) * cols * sizeof(float);
+}
+
+int rglru_column_sums(const void* src, float* out, void* ws, size_t ws_bytes, long long rows, int cols, int io_dtype,
+                      void* stream) {
+  if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
+  if (!src || !out) return RGLRU_ERR_NULL_POINTER;
+  if (rows <= 0 || cols <= 0 || rows > (1ll << 40)) return RGLRU_ERR_BAD_SHAPE;
+  const bool bf16 = io_dtype == RGLRU_BF16;
+  const size_t es = bf16 ? 2 : 4;
+  if (!aligned(src, es) || !aligned(out, 4) || !aligned(ws, 4)) return RGLRU_ERR_MISALIGNED;
+  if (!ws || ws_bytes < rglru_column_sums_workspace_bytes(rows, cols)) return RGLRU_ERR_WORKSPACE;
+  int* status = nullptr;
+  const int rc = device_setup(&status);
+  if (rc != RGLRU_OK) return rc;
+  const bool vector_ok = (static_cast<size_t>(cols) * es) % 16 == 0 && aligned(src, 16);
+  const cudaError_t e = launch_column_sums(bf16, src, out, static_cast<float*>(ws), rows, cols, vector_ok,
+                                           static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
+}
+
 int rglru_decode_conv(const void* x_in, const float* conv_w, const float* conv_b, void* conv_state,
                       const uint8_t* tok, void* x_conv, int B, int D, int io_dtype, void* stream) {
   if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;

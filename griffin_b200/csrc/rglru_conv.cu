@@ -456,6 +456,118 @@ __global__ void conv_bwd_reduce_kernel(const float* __restrict__ part, float* __
   else if (db) db[d] = acc;
 }
 
+// ---------------------------------------------------------------- column sums
+// out[c] = sum over rows of src[r, c] for a dense row-major [rows, cols] matrix (the bias gradient of a linear
+// layer from the gradient of its output).  Two launches, fixed summation order, no atomics: a grid of
+// (column tile, row block) CTAs of 32 column vectors x 8 row lanes keeps UNROLL 16-byte loads per thread in
+// flight and leaves one fp32 partial row per row block; the second kernel folds the partial rows, eight
+// interleaved lanes per column combined in lane order.
+constexpr int COLSUM_LANES = 8;
+constexpr int COLSUM_UNROLL = 4;
+
+template <typename IO, int VEC>
+__global__ void __launch_bounds__(32 * COLSUM_LANES) colsum_partial_kernel(const IO* __restrict__ src,
+                                                                          float* __restrict__ part, long long rows,
+                                                                          int cols, long long rows_per_block) {
+  __shared__ float red[COLSUM_LANES][32][VEC + 1];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = (blockIdx.x * 32 + tx) * VEC;
+  const long long r0 = blockIdx.y * rows_per_block;
+  const long long r1 = (r0 + rows_per_block < rows) ? r0 + rows_per_block : rows;
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+  if (col < cols) {
+    const IO* base = src + col;
+    long long r = r0 + ty;
+    for (; r + (COLSUM_UNROLL - 1) * COLSUM_LANES < r1; r += COLSUM_UNROLL * COLSUM_LANES) {
+      typename Vec<IO, VEC>::Raw raw[COLSUM_UNROLL];
+#pragma unroll
+      for (int u = 0; u < COLSUM_UNROLL; ++u) raw[u] = Vec<IO, VEC>::load_raw(base + (r + u * COLSUM_LANES) * cols);
+#pragma unroll
+      for (int u = 0; u < COLSUM_UNROLL; ++u) {
+        float v[VEC];
+        Vec<IO, VEC>::unpack(raw[u], v);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] += v[k];
+      }
+    }
+    for (; r < r1; r += COLSUM_LANES) {
+      float v[VEC];
+      Vec<IO, VEC>::load(base + r * cols, v);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) acc[k] += v[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) red[ty][tx][k] = acc[k];
+  __syncthreads();
+  if (ty == 0 && col < cols) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      float t = red[0][tx][k];
+#pragma unroll
+      for (int l = 1; l < COLSUM_LANES; ++l) t += red[l][tx][k];
+      part[static_cast<size_t>(blockIdx.y) * cols + col + k] = t;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(32 * COLSUM_LANES) colsum_fold_kernel(const float* __restrict__ part,
+                                                                       float* __restrict__ out, int nrow, int cols) {
+  __shared__ float red[COLSUM_LANES][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + tx;
+  float acc = 0.0f;
+  if (col < cols)
+    for (int r = ty; r < nrow; r += COLSUM_LANES) acc += part[static_cast<size_t>(r) * cols + col];
+  red[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && col < cols) {
+    float t = red[0][tx];
+#pragma unroll
+    for (int l = 1; l < COLSUM_LANES; ++l) t += red[l][tx];
+    out[col] = t;
+  }
+}
+
+// Row blocks of a column-sum call: enough CTAs for four per SM, at least 64 rows each.
+int colsum_row_blocks(long long rows, int cols) {
+  const long long tiles = (cols + 255) / 256 > 0 ? (cols + 255) / 256 : 1;
+  long long want = (4 * 148 + tiles - 1) / tiles;
+  const long long most = (rows + 63) / 64;
+  if (want > most) want = most;
+  if (want < 1) want = 1;
+  if (want > 65535) want = 65535;
+  return static_cast<int>(want);
+}
+
+template <typename IO>
+static cudaError_t column_sums_t(const void* src, float* out, float* part, long long rows, int cols, bool vector_ok,
+                                 cudaStream_t s) {
+  constexpr int V = vec_width<IO>();
+  const int nblk = colsum_row_blocks(rows, cols);
+  const long long per = (rows + nblk - 1) / nblk;
+  const IO* p = static_cast<const IO*>(src);
+  if (vector_ok) {
+    const dim3 grid(static_cast<unsigned>((cols / V + 31) / 32), static_cast<unsigned>(nblk));
+    colsum_partial_kernel<IO, V><<<grid, 32 * COLSUM_LANES, 0, s>>>(p, part, rows, cols, per);
+  } else {
+    const dim3 grid(static_cast<unsigned>((cols + 31) / 32), static_cast<unsigned>(nblk));
+    colsum_partial_kernel<IO, 1><<<grid, 32 * COLSUM_LANES, 0, s>>>(p, part, rows, cols, per);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  colsum_fold_kernel<<<(cols + 31) / 32, 32 * COLSUM_LANES, 0, s>>>(part, out, nblk, cols);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_column_sums(bool bf16, const void* src, float* out, float* part, long long rows, int cols,
+                               bool vector_ok, cudaStream_t s) {
+  return bf16 ? column_sums_t<__nv_bfloat16>(src, out, part, rows, cols, vector_ok, s)
+              : column_sums_t<float>(src, out, part, rows, cols, vector_ok, s);
+}
+
 // ---------------------------------------------------------------- decode
 template <typename IO, int VEC>
 __global__ void __launch_bounds__(256) decode_conv_kernel(const IO* __restrict__ xin, const float* __restrict__ w,

@@ -12,7 +12,8 @@ namespace rglru {
 constexpr int SAVE_EVERY = 64;
 // Largest batch for which the backward kernel folds the dLambda rows itself (one CTA walks B x D floats).
 constexpr int FUSED_DLAMBDA_MAX_B = 64;
-constexpr size_t WS_TAIL_BYTES = 256;  // completion ticket at the end of the workspace
+constexpr size_t WS_TAIL_BYTES = 256;  // completion tickets at the end of the workspace
+constexpr int WS_TICKETS = static_cast<int>(WS_TAIL_BYTES / sizeof(unsigned));
 
 struct ScanFwdArgs {
   const void* x;
@@ -170,6 +171,9 @@ int conv_tma_box_rows();
 int conv_tma_box_cols();
 cudaError_t launch_decode_conv(bool bf16, const ConvArgs& a, cudaStream_t s);
 cudaError_t launch_decode_step(bool bf16, const DecodeArgs& a, cudaStream_t s);
+int colsum_row_blocks(long long rows, int cols);   // partial rows a column-sum call leaves in its workspace
+cudaError_t launch_column_sums(bool bf16, const void* src, float* out, float* part, long long rows, int cols,
+                               bool vector_ok, cudaStream_t s);
 
 // use_tma == false selects the bounds-checked plain-load staging path that accepts any D.
 // `variant` picks the CTA shape (see scan_fwd_variant); the tensor maps must be encoded with its box rows.

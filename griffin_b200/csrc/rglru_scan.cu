@@ -18,8 +18,8 @@
 // happens outside the chunk loop, so the channel arithmetic is written on float2 pairs (one issue slot per two
 // fp32 operations), transcendental work is kept to three or four MUFU operations per element, and the
 // prologue (first loads issued before the per-channel rates are worked out, the first chunk prefetched into
-// L2 before the dependency wait) and the epilogue (row sums folded by the last CTA with all loads in flight
-// at once) are kept short.  Sixteen-warp variants with two steps per thread measured 15 % slower.
+// L2 before the dependency wait) and the epilogue (the row sums of a channel tile are folded by whichever of
+// the tile's CTAs finishes last, with all its loads in flight at once) are kept short.  Sixteen-warp variants with two steps per thread measured 15 % slower.
 //
 // The gate epilogue follows griffin/griffin.py:237-258 of the reference, the scan :280-286, the backward is
 // the closed form of autograd over those lines with the capped sqrt slope of :59-65.  All arithmetic is fp32.
@@ -396,7 +396,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   }
   const bool poly = bar_compute_and(NCOMP, fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
-  if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && p.ticket) *p.ticket = 0u;   // consumed by the backward kernel
+  if (blockIdx.x == 0 && blockIdx.y == 0 && tid < WS_TICKETS && p.ticket) p.ticket[tid] = 0u;   // consumed by the backward kernel
 
   ConvTaps ct;
   if (CONV) load_taps(p.conv_w, p.conv_b, d0 + vec * CV, p.D, ct);
@@ -1032,65 +1032,62 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   }
   if (!p.ticket) return;   // the caller folds the rows with rglru_dlambda_kernel
 
-  // The CTA that finishes last folds the per-row partials into dLambda (rows in index order, so the
-  // result does not depend on which CTA that is) and re-arms the ticket for the next backward call.
+  // Channel tiles are dealt to at most 64 completion tickets; the CTA that arrives last at a ticket folds the
+  // per-row partials of that ticket's tiles (rows in index order, so the result does not depend on which CTA
+  // that is) while other tiles are still at work, and re-arms the ticket for the next backward call.
   __shared__ int s_last;
+  const int ntile = static_cast<int>(gridDim.x);
+  const int ngrp = ntile < WS_TICKETS ? ntile : WS_TICKETS;
+  const int grp = static_cast<int>(blockIdx.x) % ngrp;
   __threadfence();
   bar_compute(NCOMP);
   if (tid == 0) {
-    const unsigned total = gridDim.x * gridDim.y;
-    s_last = (atomicAdd(p.ticket, 1u) == total - 1u) ? 1 : 0;
+    const unsigned members = gridDim.y * static_cast<unsigned>((ntile - grp + ngrp - 1) / ngrp);
+    s_last = (atomicAdd(p.ticket + grp, 1u) == members - 1u) ? 1 : 0;
   }
   bar_compute(NCOMP);
   if (!s_last) return;
   __threadfence();
-  // Rows are added in index order whatever the load order; loads go out eight rows at a time so that the
-  // fold costs a few round trips to L2, not one per row.
-  if ((p.D & 3) == 0) {
-    for (int d = tid * 4; d < p.D; d += NCOMP * 4) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r0 = 0; r0 < p.B; r0 += 8) {
-        float4 v[8];
+  const bool fold_gates = GROUPED && p.dgate && p.dgate_part;
+  for (int tile = grp; tile < ntile; tile += ngrp) {
+    const int c0 = tile * CH;
+    if ((p.D & 3) == 0) {
+      // One float4 of columns per thread: CH/4 threads for dLambda, as many again for each gate sum. Loads go
+      // out eight rows at a time so that the fold costs a few round trips to L2, not one per row.
+      const int seg = tid / (CH / 4), c4 = (tid % (CH / 4)) * 4;
+      if (seg < (fold_gates ? 3 : 1) && c0 + c4 < p.D) {
+        const int gc = GROUPED ? grouped_col(c0, p.gate_bw) : c0;
+        const float* src = seg == 0 ? p.dlam_part + c0 + c4 : p.dgate_part + gc + (seg == 2 ? p.gate_bw : 0) + c4;
+        const size_t pitch = seg == 0 ? static_cast<size_t>(p.D) : 2 * static_cast<size_t>(p.D);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r0 = 0; r0 < p.B; r0 += 8) {
+          float4 v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(p.dlam_part + static_cast<size_t>(r0 + j) * p.D + d))
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int j = 0; j < 8; ++j)
+            v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(r0 + j) * pitch))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+          for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+        }
+        if (seg == 0) {
+          const float4 lam = *reinterpret_cast<const float4*>(p.lambda + c0 + c4);
+          float4 out;
+          out.x = (1.0f / (1.0f + expf(lam.x))) * p.c * acc.x;
+          out.y = (1.0f / (1.0f + expf(lam.y))) * p.c * acc.y;
+          out.z = (1.0f / (1.0f + expf(lam.z))) * p.c * acc.z;
+          out.w = (1.0f / (1.0f + expf(lam.w))) * p.c * acc.w;
+          *reinterpret_cast<float4*>(p.dlambda + c0 + c4) = out;
+        } else {
+          *reinterpret_cast<float4*>(p.dgate + gc + (seg == 2 ? p.gate_bw : 0) + c4) = acc;
+        }
       }
-      const float4 lam = *reinterpret_cast<const float4*>(p.lambda + d);
-      float4 out;
-      out.x = (1.0f / (1.0f + expf(lam.x))) * p.c * acc.x;
-      out.y = (1.0f / (1.0f + expf(lam.y))) * p.c * acc.y;
-      out.z = (1.0f / (1.0f + expf(lam.z))) * p.c * acc.z;
-      out.w = (1.0f / (1.0f + expf(lam.w))) * p.c * acc.w;
-      *reinterpret_cast<float4*>(p.dlambda + d) = out;
-    }
-  } else {
-    for (int d = tid; d < p.D; d += NCOMP) {
+    } else if (tid < CH && c0 + tid < p.D) {   // ragged D: never the grouped layout
       float acc = 0.0f;
-      for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + d);
-      const float lam = p.lambda[d];
-      p.dlambda[d] = (1.0f / (1.0f + expf(lam))) * p.c * acc;
+      for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + c0 + tid);
+      p.dlambda[c0 + tid] = (1.0f / (1.0f + expf(p.lambda[c0 + tid]))) * p.c * acc;
     }
   }
-  if (GROUPED && p.dgate && p.dgate_part) {     // gate-bias gradient: column sums of du over the batch rows
-    const int N2 = 2 * p.D;                     // a multiple of 4: the grouped layout needs 64-channel gate heads
-    for (int d = tid * 4; d < N2; d += NCOMP * 4) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r0 = 0; r0 < p.B; r0 += 8) {
-        float4 v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(p.dgate_part + static_cast<size_t>(r0 + j) * N2 + d))
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
-      }
-      *reinterpret_cast<float4*>(p.dgate + d) = acc;
-    }
-  }
-  if (tid == 0) *p.ticket = 0u;
+  if (tid == 0) p.ticket[grp] = 0u;
 }
 
 // out[n] = sum_b part[b, n], rows added in index order (gate-bias gradient when the batch is too large for the

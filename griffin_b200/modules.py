@@ -245,6 +245,16 @@ def _last_real_position(segment_pos: Tensor, active: Optional[Tensor], previous:
     return torch.where(last > 0, picked, fallback)
 
 
+def _project(layer: nn.Module, x: Tensor) -> Tensor:
+    """One of the block's three projections.  A stock ``nn.Linear`` without hooks goes through ``ops.linear`` (same
+    GEMMs; the bias gradient comes from the library's column-sum kernel); anything else — a replaced layer, a layer
+    with hooks — is called as the module it is."""
+    if type(layer) is nn.Linear and not (layer._forward_hooks or layer._forward_pre_hooks or layer._backward_hooks
+                                         or layer._backward_pre_hooks):
+        return ops.linear(x, layer.weight, layer.bias)
+    return layer(x)
+
+
 class RecurrentBlock(nn.Module):
     """Causal conv + RG-LRU temporal-mixing block with cached decoding (griffin/griffin.py:361-529).
 
@@ -300,12 +310,15 @@ class RecurrentBlock(nn.Module):
             active_mask = active_mask.to(device=x.device, dtype=torch.bool)
         previous = None if cache is None else cache.segment_position
         plain = segment_pos is None and cache is None and active_mask is None
-        pos = _positions(x, segment_pos, previous, active_mask)
+        # rows that are one fresh document each need no position tensor unless a cache is asked for
+        pos = None if plain and not return_cache else _positions(x, segment_pos, previous, active_mask)
+        if plain and steps == 0:
+            raise ValueError("Empty token sequences are not supported")
 
-        y_branch = self.linear_y(x)
+        y_branch = _project(self.linear_y, x)
         if not self.fold_merge:
             y_branch = F.gelu(y_branch, approximate="tanh")
-        x_in = self.linear_x(x)
+        x_in = _project(self.linear_x, x)
         restore = None
         if active_mask is not None and steps > 1 and bool((active_mask[:, 1:] & ~active_mask[:, :-1]).any()):
             # a real token follows padding somewhere: stable partition of every row, real tokens first
@@ -365,7 +378,7 @@ class RecurrentBlock(nn.Module):
                                      _branch=y_branch if self.fold_merge else None)
         if restore is not None:
             y = y.gather(1, restore[..., None].expand(-1, -1, y.size(-1)))
-        out = self.linear_out(y if self.fold_merge else y * y_branch)
+        out = _project(self.linear_out, y if self.fold_merge else y * y_branch)
         if active_mask is not None:
             out = torch.where(active_mask[..., None], out, torch.zeros_like(out))
         if return_cache:

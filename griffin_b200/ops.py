@@ -52,17 +52,31 @@ def _on_traced(t: Tensor, name: str):
             torch.cuda.nvtx.range_pop()
 
 
+_SAME_DEVICE = contextlib.nullcontext()
+
+
 def _on(t: Tensor, name: str):
-    """Context that makes ``t``'s device current for one library call; with RGLRU_NVTX=1 the call also sits in an
-    NVTX range named after the entry point, so a profiler's timeline or range filter shows the operators."""
-    return _on_traced(t, name) if _NVTX else torch.cuda.device(t.device)
+    """Context that makes ``t``'s device current for one library call (nothing to do when it already is); with
+    RGLRU_NVTX=1 the call also sits in an NVTX range named after the entry point, so a profiler's timeline or
+    range filter shows the operators."""
+    if _NVTX:
+        return _on_traced(t, name)
+    if t.device.index == torch.cuda.current_device():
+        return _SAME_DEVICE
+    return torch.cuda.device(t.device)
 
 
 def _ptr(t: Optional[Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: Tensor) -> int:
+    """The current stream of ``t``'s device as the integer handle the C ABI takes."""
+    if _raw_stream is not None:
+        return _raw_stream(t.device.index)
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
@@ -844,6 +858,63 @@ def recurrent_core(x_in: Tensor, conv_w: Tensor, conv_b: Optional[Tensor], conv_
         None if tok is None else tok.contiguous(), float(c),
         None if branch is None else branch.to(x_in.dtype).contiguous(), save)
     return y, h_last, new_state
+
+
+# ----------------------------------------------------------------------------- linear layers around the recurrence
+def column_sums(m: Tensor) -> Tensor:
+    """fp32 column sums of a dense [rows, cols] CUDA matrix (``rglru_column_sums``): fixed summation order, one
+    streaming pass.  The bias gradient of a linear layer from the gradient of its output."""
+    if m.dim() != 2:
+        raise ValueError("column_sums takes a [rows, cols] matrix")
+    _require_cuda(m)
+    lib = _lib.load()
+    dt = _io_dtype(m, "column sums")
+    m = m.contiguous()
+    rows, cols = m.shape
+    out = torch.empty(cols, device=m.device, dtype=torch.float32)
+    if rows == 0:
+        return out.zero_()
+    nbytes = lib.rglru_column_sums_workspace_bytes(rows, cols)
+    ws = torch.empty(nbytes, device=m.device, dtype=torch.uint8)
+    with _on(m, "rglru_column_sums"):
+        rc = lib.rglru_column_sums(_ptr(m), _ptr(out), _ptr(ws), nbytes, rows, cols, dt, _stream(m))
+    _lib.check(rc, "rglru_column_sums")
+    return out
+
+
+class _BiasGradTap(torch.autograd.Function):
+    """Identity on the output of a linear layer that was computed with its bias detached; the backward hands the
+    gradient through untouched and supplies the bias gradient from :func:`column_sums`.  The GEMMs and their
+    backward stay autograd's own; only the generic reduction it would launch for the bias (a fifth of streaming
+    bandwidth on [32768, 1024] bf16) is replaced."""
+
+    @staticmethod
+    def forward(ctx, y, bias):
+        ctx.bias_dtype = bias.dtype
+        return y.view_as(y)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dy):
+        db = None
+        if ctx.needs_input_grad[1]:
+            db = column_sums(dy.reshape(-1, dy.shape[-1])).to(ctx.bias_dtype)
+        return dy, db
+
+
+def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor]) -> Tensor:
+    """``F.linear`` for the block's three projections (linear_x / linear_y / linear_out, griffin/griffin.py:379-389).
+    Where a bias gradient is wanted on CUDA tensors of a kernel dtype, outside tracing, the bias gradient comes
+    from :func:`column_sums`; everything else is ``F.linear`` itself."""
+    tap = (bias is not None and bias.requires_grad and torch.is_grad_enabled() and x.is_cuda and x.numel() > 0
+           and not _library_ops_active())
+    if tap:
+        out_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+        tap = out_dtype in _DTYPES
+    if not tap:
+        return torch.nn.functional.linear(x, weight, bias)
+    y = torch.nn.functional.linear(x, weight, bias.detach())
+    return _BiasGradTap.apply(y, bias)
 
 
 # ----------------------------------------------------------------------------- decode (in-place state, no autograd)

@@ -66,10 +66,14 @@ def _scan_with_carry(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optio
     return y, h_last, prod, ws
 
 
-def _all_gather(t: Tensor, group) -> list[Tensor]:
+def _all_gather(t: Tensor, group) -> Tensor:
+    """[world, *t.shape]: every rank's ``t`` (one collective; a group of one needs none)."""
     import torch.distributed as dist
-    out = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
-    dist.all_gather(out, t.contiguous(), group=group)
+    world = dist.get_world_size(group)
+    if world == 1:
+        return t.unsqueeze(0)
+    out = torch.empty((world,) + tuple(t.shape), device=t.device, dtype=t.dtype)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=group)
     return out
 
 
@@ -87,15 +91,15 @@ class _TimeShardedRGLRU(torch.autograd.Function):
         # pass 1: from a zero state (rank 0 starts from the sequence's own initial state: its result is final)
         start = first if rank == 0 else None
         y, h_last, prod, ws = _scan_with_carry(x, u_r, u_i, lam32, start, tok, c, save)
-        prods = _all_gather(prod, group)
-        finals = _all_gather(h_last, group)
+        pairs = _all_gather(torch.stack((prod, h_last)), group)       # [world, 2, B, D]: one exchange
+        prods, finals = pairs[:, 0], pairs[:, 1]
         # rank 0's pair already contains `first`, so the fold starts from zero at rank 1's entry = finals[0]
         enter = fold_entering_states(prods[1:], finals[1:], finals[0])[0] if world > 1 else []
         h_in = start
         if rank > 0:
             h_in = enter[rank - 1].contiguous()
             y, h_last, _, ws = _scan_with_carry(x, u_r, u_i, lam32, h_in, tok, c, save)   # pass 2: from the true state
-        ctx.save_for_backward(x, u_r, u_i, lam32, h_in, tok, ws, prod)
+        ctx.save_for_backward(x, u_r, u_i, lam32, h_in, tok, ws, prods)
         ctx.c, ctx.group, ctx.has_h0 = c, group, h0 is not None
         ctx.lam_dtype = lam.dtype
         return y, h_last
@@ -104,7 +108,7 @@ class _TimeShardedRGLRU(torch.autograd.Function):
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy, dh_last):
         import torch.distributed as dist
-        x, u_r, u_i, lam32, h_in, tok, ws, prod = ctx.saved_tensors
+        x, u_r, u_i, lam32, h_in, tok, ws, prods = ctx.saved_tensors    # prods: every rank's decay product, from the forward
         group = ctx.group
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         dy = torch.zeros_like(x) if dy is None else dy.to(x.dtype).contiguous()
@@ -120,7 +124,6 @@ class _TimeShardedRGLRU(torch.autograd.Function):
         # pass 1: reverse carry out of this slice with the slice's own end gradient only
         dx, du_r, du_i, dlam, dh0 = run(g_end)
         locals_ = _all_gather(dh0, group)
-        prods = _all_gather(prod, group)
         if rank < world - 1:
             # carry entering slice k from the slices after it: fold (P_j, dh0_local_j) for j = world-1 .. k+1; what
             # leaves that chain at slice k+1's start is the gradient of the state at slice k's end

@@ -241,6 +241,17 @@ int rglru_conv_bwd_noalloc(const void* d_conv, const void* x_in, const float* co
                            const uint8_t* tok, void* dx_in, float* d_w, float* d_b, void* d_state, int B, int T,
                            int D, int io_dtype, void* stream);
 
+/* Column sums of a dense row-major matrix: out[c] = sum_r src[r, c], fp32 accumulation in a fixed order (two
+ * launches, no atomics), at streaming bandwidth.  It serves the bias gradients of the three linear layers
+ * around the recurrence (griffin/griffin.py:379-389: linear_x, linear_y, linear_out; the reference leaves them
+ * to autograd's generic reduction), whose inputs are exactly the gradients this library's backward kernels
+ * produce or consume.
+ *   src : [rows, cols] io_dtype   out : [cols] fp32   ws : rglru_column_sums_workspace_bytes(rows, cols) bytes
+ */
+size_t rglru_column_sums_workspace_bytes(long long rows, int cols);
+int rglru_column_sums(const void* src, float* out, void* ws, size_t ws_bytes, long long rows, int cols, int io_dtype,
+                      void* stream);
+
 /* Single-token decode update: the T = 1 case of RecurrentBlock.forward with a cache,
  * griffin/griffin.py:459-528, split at the gate projections (which stay ordinary GEMMs):
  *

@@ -94,6 +94,16 @@ def test_argument_validation_codes(lib):
     assert lib.rglru_grouped_fwd(q, None, None, None, q, None, None, q, None, None, 0, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_grouped_bwd(q, None, q, q, None, q, q, None, None, q, 1 << 20, q, q, None, q, None, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_grouped_bwd(q, None, q, q, None, None, q, None, None, q, 8, q, q, None, q, None, None, 1, 2, 128, 64, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
+    # column sums: size of the partial rows, and the argument checks (no launch: every call is refused)
+    assert lib.rglru_column_sums_workspace_bytes(0, 8) == 0
+    need = lib.rglru_column_sums_workspace_bytes(32768, 1024)
+    assert need % (1024 * 4) == 0 and 0 < need <= 4 * 148 * 1024 * 4
+    assert lib.rglru_column_sums_workspace_bytes(10, 8) == 8 * 4          # fewer than 64 rows: one row block
+    assert lib.rglru_column_sums(q, q, q, 1 << 20, 4, 8, 5, None) == _lib.ERR_BAD_DTYPE
+    assert lib.rglru_column_sums(None, q, q, 1 << 20, 4, 8, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_column_sums(q, q, q, 1 << 20, 0, 8, _lib.F32, None) == _lib.ERR_BAD_SHAPE
+    assert lib.rglru_column_sums(q, q, q, 4, 4, 8, _lib.F32, None) == _lib.ERR_WORKSPACE
+    assert lib.rglru_column_sums(q + 2, q, q, 1 << 20, 4, 8, _lib.F32, None) == _lib.ERR_MISALIGNED
     # branch merge: x, conv_w, conv_b, conv_state, u_r, u_i, branch, lambda, h0, tok, out, h_last, ws, ws_bytes, ...
     assert lib.rglru_merge_fwd(p, None, None, None, p, p, None, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_merge_fwd(p, None, None, None, p, p, p, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, 3, None) == _lib.ERR_BAD_DTYPE
