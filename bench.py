@@ -411,8 +411,8 @@ def run_c4a_shard(args, d: Dist) -> dict:
 
 def run_time_shard(args, d: Dist) -> dict:
     """One sequence of B=8, D=1024, bf16, T = 8192 per rank, split along TIME over the ranks: forward + backward
-    through ``griffin_b200.time_shard.rglru_time_sharded`` (two scan passes on every rank but one per direction,
-    one all-gather of [B, D] pairs per direction over NCCL); beside it the same rank's slice as an ordinary
+    through ``griffin_b200.time_shard.rglru_time_sharded`` (per direction a carry-only pass, one all-gather of
+    [B, D] carries over NCCL, and the full pass); beside it the same rank's slice as an ordinary
     unsplit call, i.e. what the step would cost were there no carry between the slices."""
     from griffin_b200 import _lib, ops
     from griffin_b200.time_shard import rglru_time_sharded
@@ -468,10 +468,10 @@ def run_time_shard(args, d: Dist) -> dict:
             "timing": {"regions": len(regions), "value_is": "median over regions",
                        "ms_per_step_min": min(regions), "ms_per_step_max": max(regions)},
             "unsplit_slice_ms_per_step": ms_one, "cost_of_the_split": ms / ms_one,
-            "exchange_bytes_per_rank_per_step": 2 * 2 * B * D * 4,
+            "exchange_bytes_per_rank_per_step": 3 * B * D * 4,
             "frac_of_hbm_peak_per_gpu": total / world / ms / 1e6 / peak, "peak_source": f"of {kind}",
             "gpu_launches": (4 if world > 1 else 2) * steps, "clocks": clocks, "device_status": _lib.device_status(),
-            "roofline": {"bound": "hbm", "note": "algorithmic bytes count ONE pass per direction; all ranks but one run two",
+            "roofline": {"bound": "hbm", "note": "algorithmic bytes count the full pass of each direction only; the carry-only passes are the cost of the split",
                          "achieved": total / world / ms / 1e6, "peak": peak, "peak_source": f"of {kind}", "unit": "GB/s",
                          "frac": total / world / ms / 1e6 / peak, "traffic": None}}
 
@@ -617,6 +617,11 @@ def _timed(fn, steps, warmup, d: Dist):
     return d.max_over_ranks(e0.elapsed_time(e1) / steps)
 
 
+# Library kernels per forward+backward of one recurrent block on the TMA-staged conv path: conv forward, scan forward,
+# scan backward, conv backward and its partial-row fold, and two column-sum kernels for each of the three bias gradients.
+BLOCK_LAUNCHES = 11
+
+
 def run_block(args, d: Dist) -> dict:
     """The full recurrent temporal block, bf16, B=16/GPU, T=2048, 768 -> 1024 -> 768, conv weights ~ N(0, 1/4), fwd+bwd."""
     from griffin_b200 import RecurrentBlock, _lib
@@ -672,7 +677,7 @@ def run_block(args, d: Dist) -> dict:
             "scan_conv_algorithmic_gbs": world * (22 + 10) * n / ms / 1e6,
             "e2e": {"value": world * n / e2e_ms * 1e3, "unit": "token-channels/s", "h2d_bytes_per_step": 2 * B * T * DM,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
-            "gpu_launches": 6 * args.steps, "clocks": clocks, "device_status": _lib.device_status(),
+            "gpu_launches": BLOCK_LAUNCHES * args.steps, "clocks": clocks, "device_status": _lib.device_status(),
             "roofline": {"bound": "hbm", "note": "GEMMs (torch) dominate this step; see the c1 line for the kernel roofline",
                          "peak": peak, "peak_source": f"of {kind}", "unit": "GB/s", "achieved": None, "frac": None, "traffic": None}}
 
@@ -740,8 +745,8 @@ def run_lm(args, d: Dist, steps=None, warmup=None) -> dict:
                       "fold": args.fold, "l2": "activations of one step far exceed L2"},
            "e2e": {"value": world * B * T / e2e_ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": 8 * B * (T + 1),
                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
-           # per recurrent layer (8 of 12): conv fwd + state, scan fwd, scan bwd, conv bwd + fold
-           "gpu_launches": 8 * 6 * steps,
+           # 8 of the 12 layers are recurrent blocks
+           "gpu_launches": 8 * BLOCK_LAUNCHES * steps,
            "clocks": clocks,
            "device_status": _lib.device_status(),
            "roofline": {"bound": "tensor", "note": "whole-model step: torch GEMMs and attention dominate; the library's kernels "

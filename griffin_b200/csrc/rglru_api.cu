@@ -209,7 +209,7 @@ static int fwd_common(const void* x, const void* u_r, const void* u_i, const flo
                       const uint8_t* tok, void* y, float* h_last, float* decay_prod, void* ws, size_t ws_bytes, int B, int T,
                       int D, float c, int io_dtype, void* stream) {
   if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
-  if (!x || !u_r || !u_i || !lambda || !y) return RGLRU_ERR_NULL_POINTER;
+  if (!x || !u_r || !u_i || !lambda || (!y && !decay_prod)) return RGLRU_ERR_NULL_POINTER;   // no y: carry-only call
   int rc = check_dims(B, T, D);
   if (rc != RGLRU_OK) return rc;
   const bool bf16 = io_dtype == RGLRU_BF16;
@@ -240,7 +240,8 @@ static int fwd_common(const void* x, const void* u_r, const void* u_i, const flo
   if (tma) {
     const int rows = scan_fwd_box_rows(variant), cols = scan_fwd_box_cols(variant);
     tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&
-          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) && make_map(&maps.y, y, bf16, B, T, D, rows, cols);
+          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.y, y ? y : x, bf16, B, T, D, rows, cols);   // without y the map is never used
   }
   const cudaError_t e = launch_scan_fwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);
@@ -264,7 +265,10 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
               void* du_r, void* du_i, float* dlambda, float* dh0, int B, int T, int D, float c, int io_dtype,
               void* stream) {
   if (io_dtype != RGLRU_F32 && io_dtype != RGLRU_BF16) return RGLRU_ERR_BAD_DTYPE;
-  if (!dy || !x || !u_r || !u_i || !lambda || !dx || !du_r || !du_i || !dlambda) return RGLRU_ERR_NULL_POINTER;
+  if (!dy || !x || !u_r || !u_i || !lambda) return RGLRU_ERR_NULL_POINTER;
+  // Carry-only call: dx, du_r, du_i and dlambda all absent and dh0 present; otherwise all four are required.
+  const bool carry_only = !dx && !du_r && !du_i && !dlambda && dh0;
+  if (!carry_only && (!dx || !du_r || !du_i || !dlambda)) return RGLRU_ERR_NULL_POINTER;
   int rc = check_dims(B, T, D);
   if (rc != RGLRU_OK) return rc;
   const bool bf16 = io_dtype == RGLRU_BF16;
@@ -285,7 +289,7 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
   a.states = static_cast<const float*>(ws);
   a.dlam_part = static_cast<float*>(ws) + static_cast<size_t>(B) * nsave * D;
   a.dlambda = dlambda; a.dh0 = dh0;
-  a.ticket = (B <= FUSED_DLAMBDA_MAX_B) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
+  a.ticket = (B <= FUSED_DLAMBDA_MAX_B && !carry_only) ? reinterpret_cast<unsigned*>(a.dlam_part + static_cast<size_t>(B) * D) : nullptr;
   a.B = B; a.T = T; a.D = D; a.c = c; a.status = status;
 
   BwdMaps maps;
@@ -296,8 +300,10 @@ int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u
     const int rows = scan_bwd_box_rows(variant), cols = scan_bwd_box_cols(variant);
     tma = make_map(&maps.dy, dy, bf16, B, T, D, rows, cols) && make_map(&maps.x, x, bf16, B, T, D, rows, cols) &&
           make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) && make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
-          make_map(&maps.dx, dx, bf16, B, T, D, rows, cols) && make_map(&maps.dur, du_r, bf16, B, T, D, rows, cols) &&
-          make_map(&maps.dui, du_i, bf16, B, T, D, rows, cols);
+          // (a carry-only call stores nothing: its three output maps are placeholders over the inputs)
+          make_map(&maps.dx, dx ? dx : x, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dur, du_r ? du_r : u_r, bf16, B, T, D, rows, cols) &&
+          make_map(&maps.dui, du_i ? du_i : u_i, bf16, B, T, D, rows, cols);
   }
   const cudaError_t e = launch_scan_bwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);

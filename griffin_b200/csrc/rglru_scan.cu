@@ -376,7 +376,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       for (int k = 0; k < nchunks; ++k) {
         const int sidx = k % NSTAGE;
         mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
-        tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);
+        if (p.y) tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);   // no y: carry only
         tma_commit();
         if (k + NSTAGE < nchunks) {
           tma_wait_read<0>();
@@ -540,7 +540,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
       bar_compute(NCOMP);
-      tile_store_plain<IO, CH>(tiles + SM::HALO, p.y, b, t0, d0, TC, p.T, p.D);
+      if (p.y) tile_store_plain<IO, CH>(tiles + SM::HALO, p.y, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
   }
@@ -809,10 +809,12 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   auto store = [&](int q) {
     const int k = nchunks - 1 - q;
     uint8_t* st = smem + (q % NSTAGE) * SM::STAGE;
-    tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
-    tma_store_3d(&maps.dur, st + SM::OFF_UR, rcol, k * TC, b);
-    tma_store_3d(&maps.dui, st + SM::OFF_UI, icol, k * TC, b);
-    if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
+    if (p.dx) {     // no dx: the caller wants the carry (dh0) only and nothing leaves the stage
+      tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
+      tma_store_3d(&maps.dur, st + SM::OFF_UR, rcol, k * TC, b);
+      tma_store_3d(&maps.dui, st + SM::OFF_UI, icol, k * TC, b);
+      if (MERGE) tma_store_3d(&maps.dg, st + SM::OFF_G, d0, k * TC, b);
+    }
     tma_commit();
   };
   // Set-up by the thread that will issue the bulk copies (the producer warp's first lane, or with SELF_ISSUE
@@ -998,10 +1000,12 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
       bar_compute(NCOMP);
-      tile_store_plain<IO, CH>(tiles + SM::OFF_X + SM::HALO, p.dx, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<IO, CH>(tiles + SM::OFF_UR, p.dur, b, t0, d0, TC, p.T, p.D);
-      tile_store_plain<IO, CH>(tiles + SM::OFF_UI, p.dui, b, t0, d0, TC, p.T, p.D);
-      if (MERGE) tile_store_plain<IO, CH>(tiles + SM::OFF_G, p.dg, b, t0, d0, TC, p.T, p.D);
+      if (p.dx) {
+        tile_store_plain<IO, CH>(tiles + SM::OFF_X + SM::HALO, p.dx, b, t0, d0, TC, p.T, p.D);
+        tile_store_plain<IO, CH>(tiles + SM::OFF_UR, p.dur, b, t0, d0, TC, p.T, p.D);
+        tile_store_plain<IO, CH>(tiles + SM::OFF_UI, p.dui, b, t0, d0, TC, p.T, p.D);
+        if (MERGE) tile_store_plain<IO, CH>(tiles + SM::OFF_G, p.dg, b, t0, d0, TC, p.T, p.D);
+      }
       bar_compute(NCOMP);
     }
   }
@@ -1859,7 +1863,7 @@ static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaS
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
   e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), bytes, s, maps, a);
-  if (e != cudaSuccess || a.ticket) return e;
+  if (e != cudaSuccess || a.ticket || !a.dlambda) return e;
   rglru_dlambda_kernel<<<(a.D + 255) / 256, 256, 0, s>>>(a.dlam_part, a.lambda, a.dlambda, a.B, a.D, a.c);
   if (GROUPED && a.dgate && a.dgate_part)
     rglru_colsum_kernel<<<(2 * a.D + 255) / 256, 256, 0, s>>>(a.dgate_part, a.dgate, a.B, 2 * a.D);

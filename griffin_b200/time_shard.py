@@ -8,11 +8,13 @@ A slice of the recurrence is an affine map of the state that enters it,
 
 (the associative operator of the reference's ``_associative_scan``, griffin/griffin.py:291-306, applied
 to whole slices), so the slices are chained with ONE small exchange: every rank scans its slice from a
-zero state (``rglru_fwd_carry`` also returns P), the ``[B, D]`` pairs ``(P, h_local)`` are all-gathered,
-every rank folds the pairs of the ranks before it into the state entering its own slice, and scans
-again from that state.  The backward does the same in reverse with the pairs ``(P, dh0_local)``.  A rank
-whose incoming carry is known to be zero (the first in the forward, the last in the backward) scans once.
-The price of the time split is that second pass; the exchange is ``2 * B * D`` floats per rank.
+zero state in a carry-only pass (``rglru_fwd_carry`` without an output tensor: it reads its inputs and
+returns P and h_local, nothing else leaves the chip), the ``[B, D]`` pairs ``(P, h_local)`` are all-gathered,
+every rank folds the pairs of the ranks before it into the state entering its own slice, and scans again,
+in full, from that state.  The backward does the same in reverse: a carry-only pass of ``rglru_bwd`` (no
+gradient tensors, only ``dh0_local``), one all-gather, the full pass with the true incoming carry.  The price
+of the time split is the carry-only pass (3/4 of a forward's traffic, 4/7 of a backward's) on every rank;
+the exchange is ``3 * B * D`` floats per rank and step.  A group of one runs the ordinary single pass.
 
 The reference has no counterpart.  Collectives are plain ``torch.distributed`` all-gathers (NCCL on GPUs);
 there is no peer access.  The carry algebra is separated from the communication so that it can be tested
@@ -48,14 +50,16 @@ def fold_entering_states(decay_prod: Sequence[Tensor], local_final: Sequence[Ten
 
 
 def _scan_with_carry(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
-                     c: float, save: bool) -> tuple[Tensor, Tensor, Tensor, Tensor]:
-    """(y, h_last, decay_prod, workspace) of one slice through ``rglru_fwd_carry``."""
+                     c: float, save: bool, want_y: bool = True) -> tuple[Optional[Tensor], Tensor, Tensor, Tensor]:
+    """(y, h_last, decay_prod, workspace) of one slice through ``rglru_fwd_carry``; ``want_y=False`` is the
+    carry-only pass (y is None and no workspace is written)."""
     lib = _lib.load()
     dt = ops._io_dtype(x, "time-sharded forward")
     B, T, D = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if want_y else None
     h_last = torch.empty(B, D, device=x.device, dtype=torch.float32)
     prod = torch.empty(B, D, device=x.device, dtype=torch.float32)
+    save = save and want_y
     nbytes = lib.rglru_workspace_bytes(B, T, D, dt) if save else 0
     ws = torch.empty(nbytes, device=x.device, dtype=torch.uint8)
     with ops._on(x, "rglru_fwd_carry"):
@@ -64,6 +68,21 @@ def _scan_with_carry(x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Optio
                                  B, T, D, c, dt, ops._stream(x))
     _lib.check(rc, "rglru_fwd_carry")
     return y, h_last, prod, ws
+
+
+def _reverse_carry(dy: Tensor, g_end: Optional[Tensor], x: Tensor, u_r: Tensor, u_i: Tensor, lam: Tensor, h0: Tensor,
+                   tok: Optional[Tensor], ws: Tensor, c: float) -> Tensor:
+    """dh0 of one slice from a carry-only ``rglru_bwd`` call (no gradient tensors are written)."""
+    lib = _lib.load()
+    dt = ops._io_dtype(x, "time-sharded backward")
+    B, T, D = x.shape
+    dh0 = torch.empty(B, D, device=x.device, dtype=torch.float32)
+    with ops._on(x, "rglru_bwd"):
+        rc = lib.rglru_bwd(ops._ptr(dy), ops._ptr(g_end), ops._ptr(x), ops._ptr(u_r), ops._ptr(u_i), ops._ptr(lam),
+                           ops._ptr(h0), ops._ptr(tok), ops._ptr(ws), ws.numel(), None, None, None, None, ops._ptr(dh0),
+                           B, T, D, c, dt, ops._stream(x))
+    _lib.check(rc, "rglru_bwd (carry only)")
+    return dh0
 
 
 def _all_gather(t: Tensor, group) -> Tensor:
@@ -88,17 +107,19 @@ class _TimeShardedRGLRU(torch.autograd.Function):
         lam32 = lam.to(torch.float32).contiguous()
         first = None if h0 is None else h0.to(torch.float32).contiguous()
         save = any(ctx.needs_input_grad)
-        # pass 1: from a zero state (rank 0 starts from the sequence's own initial state: its result is final)
-        start = first if rank == 0 else None
-        y, h_last, prod, ws = _scan_with_carry(x, u_r, u_i, lam32, start, tok, c, save)
-        pairs = _all_gather(torch.stack((prod, h_last)), group)       # [world, 2, B, D]: one exchange
-        prods, finals = pairs[:, 0], pairs[:, 1]
-        # rank 0's pair already contains `first`, so the fold starts from zero at rank 1's entry = finals[0]
-        enter = fold_entering_states(prods[1:], finals[1:], finals[0])[0] if world > 1 else []
-        h_in = start
-        if rank > 0:
-            h_in = enter[rank - 1].contiguous()
-            y, h_last, _, ws = _scan_with_carry(x, u_r, u_i, lam32, h_in, tok, c, save)   # pass 2: from the true state
+        if world == 1:
+            y, h_last, _, ws = _scan_with_carry(x, u_r, u_i, lam32, first, tok, c, save)
+            h_in, prods = first, x.new_empty((1, 0), dtype=torch.float32)
+        else:
+            # pass 1, carry only, from a zero state (rank 0 from the sequence's own initial state)
+            start = first if rank == 0 else None
+            _, h_local, prod, _ = _scan_with_carry(x, u_r, u_i, lam32, start, tok, c, False, want_y=False)
+            pairs = _all_gather(torch.stack((prod, h_local)), group)       # [world, 2, B, D]: one exchange
+            prods, finals = pairs[:, 0], pairs[:, 1]
+            # rank 0's pair already contains `first`, so the fold starts at rank 1's entry = finals[0]
+            enter = fold_entering_states(prods[1:], finals[1:], finals[0])[0]
+            h_in = start if rank == 0 else enter[rank - 1].contiguous()
+            y, h_last, _, ws = _scan_with_carry(x, u_r, u_i, lam32, h_in, tok, c, save)   # pass 2: in full, from the true state
         ctx.save_for_backward(x, u_r, u_i, lam32, h_in, tok, ws, prods)
         ctx.c, ctx.group, ctx.has_h0 = c, group, h0 is not None
         ctx.lam_dtype = lam.dtype
@@ -118,18 +139,17 @@ class _TimeShardedRGLRU(torch.autograd.Function):
         B, T, D = x.shape
         h0_arg = h_in if h_in is not None else torch.zeros(B, D, device=x.device, dtype=torch.float32)
 
-        def run(g):
-            return ops._rglru_bwd_impl(dy, g, x, u_r, u_i, lam32, h0_arg, tok, ws, ctx.c, True)
-
-        # pass 1: reverse carry out of this slice with the slice's own end gradient only
-        dx, du_r, du_i, dlam, dh0 = run(g_end)
-        locals_ = _all_gather(dh0, group)
-        if rank < world - 1:
-            # carry entering slice k from the slices after it: fold (P_j, dh0_local_j) for j = world-1 .. k+1; what
-            # leaves that chain at slice k+1's start is the gradient of the state at slice k's end
-            _, g_in = fold_entering_states(prods[rank + 1:], locals_[rank + 1:], None, reverse=True)
-            g_total = g_in if g_end is None else g_in + g_end
-            dx, du_r, du_i, dlam, dh0 = run(g_total.contiguous())    # pass 2: with the true incoming carry
+        g_total = g_end
+        if world > 1:
+            # pass 1, carry only: what this slice hands to the one before it, given its own end gradient alone
+            locals_ = _all_gather(_reverse_carry(dy, g_end, x, u_r, u_i, lam32, h0_arg, tok, ws, ctx.c), group)
+            if rank < world - 1:
+                # carry entering slice k from the slices after it: fold (P_j, dh0_local_j) for j = world-1 .. k+1; what
+                # leaves that chain at slice k+1's start is the gradient of the state at slice k's end
+                _, g_in = fold_entering_states(prods[rank + 1:], locals_[rank + 1:], None, reverse=True)
+                g_total = (g_in if g_end is None else g_in + g_end).contiguous()
+        # pass 2 (the only pass of a group of one): in full, with the true incoming carry
+        dx, du_r, du_i, dlam, dh0 = ops._rglru_bwd_impl(dy, g_total, x, u_r, u_i, lam32, h0_arg, tok, ws, ctx.c, True)
         # dLambda is a parameter gradient: summed over ranks by the caller's data-parallel machinery or explicitly
         dh0_out = dh0 if (ctx.has_h0 and rank == 0) else (torch.zeros_like(dh0) if ctx.has_h0 else None)
         return dx, du_r, du_i, dlam.to(ctx.lam_dtype), dh0_out, None, None, None
@@ -165,7 +185,7 @@ def run_slices_on_one_device(slices: Sequence[tuple[Tensor, Tensor, Tensor]], la
     prods, finals = [], []
     for k, (x, u_r, u_i) in enumerate(slices):
         _, h_last, prod, _ = _scan_with_carry(x.contiguous(), u_r.contiguous(), u_i.contiguous(), lam32,
-                                              first if k == 0 else None, None, c, False)
+                                              first if k == 0 else None, None, c, False, want_y=False)
         prods.append(prod)
         finals.append(h_last)
     enter = [first] + (fold_entering_states(prods[1:], finals[1:], finals[0])[0] if len(slices) > 1 else [])

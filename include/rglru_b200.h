@@ -97,7 +97,9 @@ int rglru_fwd(const void* x, const void* u_r, const void* u_i, const float* lamb
  * map  h_last(h0) = decay_prod * h0 + h_last(0)  of this call, which lets one sequence be split over several
  * calls, or over the GPUs of a box along TIME, with one small exchange of [B,D] pairs between the pieces
  * (the associative operator of griffin/griffin.py:291-306 applied to whole slices).  The reference has no
- * such entry point; griffin_b200/time_shard.py is its user.  h_last and decay_prod are required. */
+ * such entry point; griffin_b200/time_shard.py is its user.  h_last and decay_prod are required.
+ * y may be NULL: a carry-only pass that reads its inputs and writes h_last and decay_prod only (pass ws = NULL
+ * with it; a slice's first pass needs nothing else). */
 int rglru_fwd_carry(const void* x, const void* u_r, const void* u_i, const float* lambda, const float* h0,
                     const uint8_t* tok, void* y, float* h_last, float* decay_prod, void* ws, size_t ws_bytes, int B,
                     int T, int D, float c, int io_dtype, void* stream);
@@ -110,6 +112,9 @@ int rglru_fwd_carry(const void* x, const void* u_r, const void* u_i, const float
  *   dx       : [B,T,D] io_dtype out -- the DIRECT path only (through b = gamma i x); the
  *              part through the gate projections is the caller's GEMM backward of du_r/du_i
  *   du_r,du_i: [B,T,D] io_dtype out     dlambda : [D] fp32 out     dh0 : [B,D] fp32 out or NULL
+ * Carry-only form (no reference counterpart; the time split's first backward pass): dx, du_r, du_i and dlambda
+ * ALL NULL and dh0 given -- the call reads its inputs and writes dh0 only.  Any other NULL among the four is an
+ * error.
  */
 int rglru_bwd(const void* dy, const float* dh_last, const void* x, const void* u_r, const void* u_i,
               const float* lambda, const float* h0, const uint8_t* tok, void* ws, size_t ws_bytes,

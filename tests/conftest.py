@@ -29,6 +29,21 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(scope="session")
+def nccl_group():
+    """The NCCL process group of a torchrun launch, one per pytest session: set up on first use and torn down when
+    the session ends (a second group created after a destroyed one can pick the first one's stale rendezvous keys
+    out of the store).  Tests that need it are skipped by their own markers when WORLD_SIZE is unset."""
+    import torch.distributed as dist
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    yield dist
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def load_golden(name: str) -> dict[str, torch.Tensor]:
     """Read one golden case as a dict of CPU tensors (bool masks stay bool)."""
     with np.load(os.path.join(GOLDEN_DIR, name + ".npz")) as data:

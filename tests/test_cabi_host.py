@@ -74,6 +74,12 @@ def test_argument_validation_codes(lib):
     # null pointers
     assert lib.rglru_fwd(None, p, p, p, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
     assert lib.rglru_bwd(p, None, p, p, p, p, None, None, p, 1 << 20, p, p, None, p, None, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    # carry-only forms: rglru_fwd itself needs y; the backward takes all four gradient outputs absent plus dh0, or none absent
+    assert lib.rglru_fwd(p, p, p, p, None, None, None, p, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_fwd_carry(p, p, p, p, None, None, None, p, None, None, 0, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_bwd(p, None, p, p, p, p, None, None, p, 1 << 20, None, None, None, None, None, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_bwd(p, None, p, p, p, p, None, None, p, 1 << 20, None, None, None, p, p, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_NULL_POINTER
+    assert lib.rglru_bwd(p, None, p, p, p, p, None, None, None, 0, None, None, None, None, p, 1, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_WORKSPACE
     # shapes
     assert lib.rglru_fwd(p, p, p, p, None, None, p, None, None, 0, 0, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_BAD_SHAPE
     assert lib.rglru_fwd(p, p, p, p, None, None, p, None, None, 0, 70000, 2, 4, 8.0, _lib.F32, None) == _lib.ERR_BAD_SHAPE

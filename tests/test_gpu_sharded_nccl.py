@@ -26,15 +26,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.skipif(WORLD < 2, reason="needs a mul
 
 
 @pytest.fixture(scope="module")
-def group():
-    import torch.distributed as dist
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    yield dist
-    dist.barrier()
-    dist.destroy_process_group()
+def group(nccl_group):
+    return nccl_group
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])

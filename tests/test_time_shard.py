@@ -71,16 +71,41 @@ def test_slices_on_one_device_equal_the_unsplit_call(dtype, tol):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(3, 700, 192), (2, 150, 72)])       # the TMA-staged path and the plain-load path
+def test_carry_only_passes_equal_the_full_calls_and_write_nothing_else(dtype, shape):
+    """rglru_fwd_carry without y and rglru_bwd without gradient tensors return exactly the carries of the full
+    calls, and leave their inputs (over which their unused output descriptors are laid) untouched."""
+    from griffin_b200 import check_device, ops
+    from griffin_b200.time_shard import _reverse_carry, _scan_with_carry
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    B, T, D = shape
+    x, u_r, u_i, dy = (torch.randn(B, T, D, device="cuda", generator=gen).to(dtype) for _ in range(4))
+    lam = orc.init_lambda(D, 8.0, torch.Generator().manual_seed(9)).cuda()
+    h0, g_end = (torch.randn(B, D, device="cuda", generator=gen) for _ in range(2))
+    keep = [t.clone() for t in (x, u_r, u_i, dy)]
+    y, h_full, p_full, ws = _scan_with_carry(x, u_r, u_i, lam, h0, None, 8.0, True)
+    none, h_c, p_c, ws_c = _scan_with_carry(x, u_r, u_i, lam, h0, None, 8.0, True, want_y=False)
+    assert none is None and ws_c.numel() == 0
+    assert torch.equal(h_c, h_full) and torch.equal(p_c, p_full)
+    full = ops._rglru_bwd_impl(dy, g_end, x, u_r, u_i, lam, h0, None, ws, 8.0, True)
+    carry = _reverse_carry(dy, g_end, x, u_r, u_i, lam, h0, None, ws, 8.0)
+    assert torch.equal(carry, full[4])
+    for before, after in zip(keep, (x, u_r, u_i, dy)):
+        assert torch.equal(before, after)
+    again = ops._rglru_bwd_impl(dy, g_end, x, u_r, u_i, lam, h0, None, ws, 8.0, True)     # the workspace is still good
+    for a, b in zip(full, again):
+        assert torch.equal(a, b)
+    check_device()
+
+
+@pytest.mark.gpu
 @pytest.mark.skipif(WORLD < 2, reason="needs a multi-process launch (torchrun)")
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-def test_time_sharded_ranks_equal_the_oracle_on_the_whole_sequence(dtype, tol):
-    import torch.distributed as dist
-
+def test_time_sharded_ranks_equal_the_oracle_on_the_whole_sequence(nccl_group, dtype, tol):
     from griffin_b200.time_shard import rglru_time_sharded
+    dist = nccl_group
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", local)
     B, T, D = 2, 96 * world + 40, 128                 # uneven slices: the last rank gets 40 steps more
