@@ -236,7 +236,7 @@ static int fwd_common(const void* x, const void* u_r, const void* u_i, const flo
 
   FwdMaps maps;
   bool tma = tma_shape_ok(T, D, es) && aligned(x, 16) && aligned(u_r, 16) && aligned(u_i, 16) && aligned(y, 16);
-  const int variant = scan_fwd_variant(B, T, D, bf16);
+  const int variant = y ? scan_fwd_variant(B, T, D, bf16) : 0;   // the carry-only pass exists in the 64-channel shape only
   if (tma) {
     const int rows = scan_fwd_box_rows(variant), cols = scan_fwd_box_cols(variant);
     tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&

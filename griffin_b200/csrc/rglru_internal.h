@@ -12,8 +12,7 @@ namespace rglru {
 constexpr int SAVE_EVERY = 64;
 // Largest batch for which the backward kernel folds the dLambda rows itself (one CTA walks B x D floats).
 constexpr int FUSED_DLAMBDA_MAX_B = 64;
-constexpr size_t WS_TAIL_BYTES = 256;  // completion tickets at the end of the workspace
-constexpr int WS_TICKETS = static_cast<int>(WS_TAIL_BYTES / sizeof(unsigned));
+constexpr size_t WS_TAIL_BYTES = 256;  // completion ticket at the end of the workspace
 
 struct ScanFwdArgs {
   const void* x;

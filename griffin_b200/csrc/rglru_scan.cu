@@ -18,8 +18,8 @@
 // happens outside the chunk loop, so the channel arithmetic is written on float2 pairs (one issue slot per two
 // fp32 operations), transcendental work is kept to three or four MUFU operations per element, and the
 // prologue (first loads issued before the per-channel rates are worked out, the first chunk prefetched into
-// L2 before the dependency wait) and the epilogue (the row sums of a channel tile are folded by whichever of
-// the tile's CTAs finishes last, with all its loads in flight at once) are kept short.  Sixteen-warp variants with two steps per thread measured 15 % slower.
+// L2 before the dependency wait) and the epilogue (row sums folded by the last CTA with all loads in flight
+// at once) are kept short.  Sixteen-warp variants with two steps per thread measured 15 % slower.
 //
 // The gate epilogue follows griffin/griffin.py:237-258 of the reference, the scan :280-286, the backward is
 // the closed form of autograd over those lines with the capped sqrt slope of :59-65.  All arithmetic is fp32.
@@ -308,7 +308,8 @@ struct FwdSmem {
 // no compute warp ever waits on the copy engine's instruction latency.
 // MERGE: the kernel also reads the pre-activation of the block's GeLU branch and writes
 // h_t * gelu(branch_t) (griffin/griffin.py:464, 520 of the reference) instead of h_t.
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false>
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false,
+          bool CARRY = false>
 __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFwdArgs& p) {
   using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
@@ -376,7 +377,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       for (int k = 0; k < nchunks; ++k) {
         const int sidx = k % NSTAGE;
         mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
-        if (p.y) tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);   // no y: carry only
+        if (!CARRY) tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);
         tma_commit();
         if (k + NSTAGE < nchunks) {
           tma_wait_read<0>();
@@ -396,7 +397,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   }
   const bool poly = bar_compute_and(NCOMP, fmaxf(fmaxf(K[0].x, K[0].y), fmaxf(K[1].x, K[1].y)) <= -POLY_RANGE);
 
-  if (blockIdx.x == 0 && blockIdx.y == 0 && tid < WS_TICKETS && p.ticket) p.ticket[tid] = 0u;   // consumed by the backward kernel
+  if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0 && p.ticket) *p.ticket = 0u;   // consumed by the backward kernel
 
   ConvTaps ct;
   if (CONV) load_taps(p.conv_w, p.conv_b, d0 + vec * CV, p.D, ct);
@@ -540,7 +541,7 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
       bar_compute(NCOMP);
-      if (p.y) tile_store_plain<IO, CH>(tiles + SM::HALO, p.y, b, t0, d0, TC, p.T, p.D);
+      if (!CARRY) tile_store_plain<IO, CH>(tiles + SM::HALO, p.y, b, t0, d0, TC, p.T, p.D);
       bar_compute(NCOMP);
     }
   }
@@ -549,10 +550,12 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
 }
 
 // PLAIN: no token flags and a whole number of chunks, so the masked arithmetic is not compiled in.
-template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false>
+// CARRY: the carry-only pass of a time-split sequence: no output tensor, nothing is stored but h_last and decay_prod.
+template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false,
+          bool CARRY = false>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
-  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED, PLAIN>(maps, p);
+  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY>(maps, p);
 }
 // The same kernel capped at 96 registers, which lets two 9-warp CTAs share an SM's register files (five warps
 // on one scheduler partition).  Used for the merged / grouped variants, which otherwise take about 112.
@@ -761,8 +764,9 @@ struct BwdSmem {
 // ahead.  A whole number of warps per scheduler partition leaves every thread 128 registers at 512 threads.
 // PLAIN: the caller passed no token flags and the sequence is a whole number of chunks, so no step is ever
 // masked; the masked arithmetic is not compiled in (half the code, and registers allotted for this path alone).
+// CARRY: the carry-only pass of a time-split sequence: no gradient tensors, nothing is stored but dh0.
 template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED,
-          bool SELF_ISSUE = false, bool PLAIN = false>
+          bool SELF_ISSUE = false, bool PLAIN = false, bool CARRY = false>
 __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0),
                                   (SELF_ISSUE && CH == 32) ? 2 : 1)
     rglru_bwd_kernel(const __grid_constant__ BwdMaps maps, const ScanBwdArgs p) {
@@ -809,7 +813,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   auto store = [&](int q) {
     const int k = nchunks - 1 - q;
     uint8_t* st = smem + (q % NSTAGE) * SM::STAGE;
-    if (p.dx) {     // no dx: the caller wants the carry (dh0) only and nothing leaves the stage
+    if (!CARRY) {
       tma_store_3d(&maps.dx, st + SM::OFF_X + SM::HALO, d0, k * TC, b);
       tma_store_3d(&maps.dur, st + SM::OFF_UR, rcol, k * TC, b);
       tma_store_3d(&maps.dui, st + SM::OFF_UI, icol, k * TC, b);
@@ -1000,7 +1004,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
       if ((tid & 31) == 0) mbar_arrive(&ready[stage]);   // one arrival per warp
     } else {
       bar_compute(NCOMP);
-      if (p.dx) {
+      if (!CARRY) {
         tile_store_plain<IO, CH>(tiles + SM::OFF_X + SM::HALO, p.dx, b, t0, d0, TC, p.T, p.D);
         tile_store_plain<IO, CH>(tiles + SM::OFF_UR, p.dur, b, t0, d0, TC, p.T, p.D);
         tile_store_plain<IO, CH>(tiles + SM::OFF_UI, p.dui, b, t0, d0, TC, p.T, p.D);
@@ -1036,62 +1040,65 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
   }
   if (!p.ticket) return;   // the caller folds the rows with rglru_dlambda_kernel
 
-  // Channel tiles are dealt to at most 64 completion tickets; the CTA that arrives last at a ticket folds the
-  // per-row partials of that ticket's tiles (rows in index order, so the result does not depend on which CTA
-  // that is) while other tiles are still at work, and re-arms the ticket for the next backward call.
+  // The CTA that finishes last folds the per-row partials into dLambda (rows in index order, so the
+  // result does not depend on which CTA that is) and re-arms the ticket for the next backward call.
   __shared__ int s_last;
-  const int ntile = static_cast<int>(gridDim.x);
-  const int ngrp = ntile < WS_TICKETS ? ntile : WS_TICKETS;
-  const int grp = static_cast<int>(blockIdx.x) % ngrp;
   __threadfence();
   bar_compute(NCOMP);
   if (tid == 0) {
-    const unsigned members = gridDim.y * static_cast<unsigned>((ntile - grp + ngrp - 1) / ngrp);
-    s_last = (atomicAdd(p.ticket + grp, 1u) == members - 1u) ? 1 : 0;
+    const unsigned total = gridDim.x * gridDim.y;
+    s_last = (atomicAdd(p.ticket, 1u) == total - 1u) ? 1 : 0;
   }
   bar_compute(NCOMP);
   if (!s_last) return;
   __threadfence();
-  const bool fold_gates = GROUPED && p.dgate && p.dgate_part;
-  for (int tile = grp; tile < ntile; tile += ngrp) {
-    const int c0 = tile * CH;
-    if ((p.D & 3) == 0) {
-      // One float4 of columns per thread: CH/4 threads for dLambda, as many again for each gate sum. Loads go
-      // out eight rows at a time so that the fold costs a few round trips to L2, not one per row.
-      const int seg = tid / (CH / 4), c4 = (tid % (CH / 4)) * 4;
-      if (seg < (fold_gates ? 3 : 1) && c0 + c4 < p.D) {
-        const int gc = GROUPED ? grouped_col(c0, p.gate_bw) : c0;
-        const float* src = seg == 0 ? p.dlam_part + c0 + c4 : p.dgate_part + gc + (seg == 2 ? p.gate_bw : 0) + c4;
-        const size_t pitch = seg == 0 ? static_cast<size_t>(p.D) : 2 * static_cast<size_t>(p.D);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r0 = 0; r0 < p.B; r0 += 8) {
-          float4 v[8];
+  // Rows are added in index order whatever the load order; loads go out eight rows at a time so that the
+  // fold costs a few round trips to L2, not one per row.
+  if ((p.D & 3) == 0) {
+    for (int d = tid * 4; d < p.D; d += NCOMP * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; r0 < p.B; r0 += 8) {
+        float4 v[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(r0 + j) * pitch))
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < 8; ++j)
+          v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(p.dlam_part + static_cast<size_t>(r0 + j) * p.D + d))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
-        }
-        if (seg == 0) {
-          const float4 lam = *reinterpret_cast<const float4*>(p.lambda + c0 + c4);
-          float4 out;
-          out.x = (1.0f / (1.0f + expf(lam.x))) * p.c * acc.x;
-          out.y = (1.0f / (1.0f + expf(lam.y))) * p.c * acc.y;
-          out.z = (1.0f / (1.0f + expf(lam.z))) * p.c * acc.z;
-          out.w = (1.0f / (1.0f + expf(lam.w))) * p.c * acc.w;
-          *reinterpret_cast<float4*>(p.dlambda + c0 + c4) = out;
-        } else {
-          *reinterpret_cast<float4*>(p.dgate + gc + (seg == 2 ? p.gate_bw : 0) + c4) = acc;
-        }
+        for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
       }
-    } else if (tid < CH && c0 + tid < p.D) {   // ragged D: never the grouped layout
+      const float4 lam = *reinterpret_cast<const float4*>(p.lambda + d);
+      float4 out;
+      out.x = (1.0f / (1.0f + expf(lam.x))) * p.c * acc.x;
+      out.y = (1.0f / (1.0f + expf(lam.y))) * p.c * acc.y;
+      out.z = (1.0f / (1.0f + expf(lam.z))) * p.c * acc.z;
+      out.w = (1.0f / (1.0f + expf(lam.w))) * p.c * acc.w;
+      *reinterpret_cast<float4*>(p.dlambda + d) = out;
+    }
+  } else {
+    for (int d = tid; d < p.D; d += NCOMP) {
       float acc = 0.0f;
-      for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + c0 + tid);
-      p.dlambda[c0 + tid] = (1.0f / (1.0f + expf(p.lambda[c0 + tid]))) * p.c * acc;
+      for (int r = 0; r < p.B; ++r) acc += __ldcg(p.dlam_part + static_cast<size_t>(r) * p.D + d);
+      const float lam = p.lambda[d];
+      p.dlambda[d] = (1.0f / (1.0f + expf(lam))) * p.c * acc;
     }
   }
-  if (tid == 0) p.ticket[grp] = 0u;
+  if (GROUPED && p.dgate && p.dgate_part) {     // gate-bias gradient: column sums of du over the batch rows
+    const int N2 = 2 * p.D;                     // a multiple of 4: the grouped layout needs 64-channel gate heads
+    for (int d = tid * 4; d < N2; d += NCOMP * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; r0 < p.B; r0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (r0 + j < p.B) ? __ldcg(reinterpret_cast<const float4*>(p.dgate_part + static_cast<size_t>(r0 + j) * N2 + d))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+      }
+      *reinterpret_cast<float4*>(p.dgate + d) = acc;
+    }
+  }
+  if (tid == 0) *p.ticket = 0u;
 }
 
 // out[n] = sum_b part[b, n], rows added in index order (gate-bias gradient when the batch is too large for the
@@ -1821,16 +1828,16 @@ template <typename... Ts> struct KernelTag {};
 template <int... Vs> struct IntTag {};
 
 template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false,
-          bool PLAIN = false>
+          bool PLAIN = false, bool CARRY = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
   constexpr bool CAPPED = USE_TMA && !CONV && (MERGE || GROUPED);
   void (*kern)(FwdMaps, ScanFwdArgs);
   if constexpr (CAPPED) kern = rglru_fwd_kernel_capped<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
-  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN>;
+  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY>;
   constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
-  cudaError_t e = set_smem<KernelTag<FwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN>>>(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<FwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
   return launch_pdl(kern, grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s, maps, a);
@@ -1839,6 +1846,9 @@ static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaS
 template <typename IO>
 static cudaError_t launch_fwd_io(bool use_tma, int variant, const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
+  if (a.y == nullptr)   // carry-only pass: one shape, masked arithmetic
+    return use_tma ? launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, false, true>(maps, a, s)
+                   : launch_fwd_t<IO, Shape64x16x4, 1, false, false, false, false, false, true>(maps, a, s);
   if (!use_tma) return launch_fwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
   const bool plain = a.tok == nullptr && a.T % 128 == 0;   // no step of any chunk is masked
   if (plain && variant == 0) return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
@@ -1853,13 +1863,13 @@ cudaError_t launch_scan_fwd(bool bf16, bool use_tma, int variant, const FwdMaps&
 }
 
 template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false,
-          bool SELF_ISSUE = false, bool PLAIN = false>
+          bool SELF_ISSUE = false, bool PLAIN = false, bool CARRY = false>
 static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
-  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE, PLAIN>;
+  auto kern = rglru_bwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE, PLAIN, CARRY>;
   constexpr int bytes = BwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
-  cudaError_t e = set_smem<KernelTag<BwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE, PLAIN>>>(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<BwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, SELF_ISSUE, PLAIN, CARRY>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
   e = launch_pdl(kern, grid, V::LANES * (V::CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 32 : 0), bytes, s, maps, a);
@@ -1873,6 +1883,9 @@ static cudaError_t launch_bwd_t(const BwdMaps& maps, const ScanBwdArgs& a, cudaS
 template <typename IO>
 static cudaError_t launch_bwd_io(bool use_tma, int variant, const BwdMaps& maps, const ScanBwdArgs& a, cudaStream_t s) {
   constexpr bool H = sizeof(IO) == 2;
+  if (a.dx == nullptr)   // carry-only pass: producer-warp shape, masked arithmetic
+    return use_tma ? launch_bwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, false, false, true>(maps, a, s)
+                   : launch_bwd_t<IO, Shape64x16x4, 1, false, false, false, false, false, false, true>(maps, a, s);
   if (!use_tma) return launch_bwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
   const bool plain = a.tok == nullptr && a.T % 64 == 0;   // no step of any chunk is masked
   if (variant == 3) {   // bulk copies issued by a compute thread: loads run NSTAGE - 2 chunks ahead, so one more stage

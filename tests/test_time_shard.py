@@ -74,8 +74,8 @@ def test_slices_on_one_device_equal_the_unsplit_call(dtype, tol):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(3, 700, 192), (2, 150, 72)])       # the TMA-staged path and the plain-load path
 def test_carry_only_passes_equal_the_full_calls_and_write_nothing_else(dtype, shape):
-    """rglru_fwd_carry without y and rglru_bwd without gradient tensors return exactly the carries of the full
-    calls, and leave their inputs (over which their unused output descriptors are laid) untouched."""
+    """rglru_fwd_carry without y and rglru_bwd without gradient tensors return the carries of the full calls, and
+    leave their inputs (over which their unused output descriptors are laid) untouched."""
     from griffin_b200 import check_device, ops
     from griffin_b200.time_shard import _reverse_carry, _scan_with_carry
     gen = torch.Generator(device="cuda").manual_seed(9)
@@ -87,10 +87,11 @@ def test_carry_only_passes_equal_the_full_calls_and_write_nothing_else(dtype, sh
     y, h_full, p_full, ws = _scan_with_carry(x, u_r, u_i, lam, h0, None, 8.0, True)
     none, h_c, p_c, ws_c = _scan_with_carry(x, u_r, u_i, lam, h0, None, 8.0, True, want_y=False)
     assert none is None and ws_c.numel() == 0
-    assert torch.equal(h_c, h_full) and torch.equal(p_c, p_full)
+    # (the two calls may run different tile shapes, hence different summation orders inside a chunk)
+    assert orc.rel_l2(h_c, h_full) <= 2e-6 and orc.rel_l2(p_c, p_full) <= 2e-6
     full = ops._rglru_bwd_impl(dy, g_end, x, u_r, u_i, lam, h0, None, ws, 8.0, True)
     carry = _reverse_carry(dy, g_end, x, u_r, u_i, lam, h0, None, ws, 8.0)
-    assert torch.equal(carry, full[4])
+    assert orc.rel_l2(carry, full[4]) <= 2e-6
     for before, after in zip(keep, (x, u_r, u_i, dy)):
         assert torch.equal(before, after)
     again = ops._rglru_bwd_impl(dy, g_end, x, u_r, u_i, lam, h0, None, ws, 8.0, True)     # the workspace is still good
