@@ -91,9 +91,9 @@ def _all_gather(t: Tensor, group) -> Tensor:
     world = dist.get_world_size(group)
     if world == 1:
         return t.unsqueeze(0)
-    out = torch.empty((world,) + tuple(t.shape), device=t.device, dtype=t.dtype)
+    out = torch.empty((world * t.shape[0],) + tuple(t.shape[1:]), device=t.device, dtype=t.dtype)   # concatenated form
     dist.all_gather_into_tensor(out, t.contiguous(), group=group)
-    return out
+    return out.view((world,) + tuple(t.shape))
 
 
 class _TimeShardedRGLRU(torch.autograd.Function):
