@@ -575,7 +575,7 @@ def _stacked_gates(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor
 
 def _grouped_fwd_impl(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor, lam: Tensor, h0: Optional[Tensor],
                  tok: Optional[Tensor], c: float, branch: Optional[Tensor], save: bool
-                 ) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+                 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
     """Gate projections + RG-LRU (+ optional GeLU-branch product) around ONE grouped GEMM.
 
     The two [G, bw, bw] gate weights are stacked per head and a single batched GEMM writes both gate
@@ -583,7 +583,8 @@ def _grouped_fwd_impl(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Ten
     re-layout pass); the kernels read that layout, add the biases themselves and return the gradient in the
     same layout, from which two more batched GEMMs give the input and weight gradients.
     Reference: BlockDiagonalLinear griffin/griffin.py:129-154 called twice at :237-238.
-    Returns (out, h_last, the gate tensor u, the workspace)."""
+    Returns (out, h_last, the gate tensor u, the workspace, the stacked weights, the stacked biases); the last four
+    are what the backward needs beside the inputs."""
     lib = _lib.load()
     with torch.autocast("cuda", enabled=False):
         x = _aligned16(x)
@@ -604,7 +605,7 @@ def _grouped_fwd_impl(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Ten
                                        _ptr(out), _ptr(h_last), _ptr(ws) if save else None, nbytes, B, T, D, bw,
                                        c, dt, _stream(x))
         _lib.check(rc, "rglru_grouped_fwd")
-    return out, h_last, u, ws
+    return out, h_last, u, ws, wcat, bias
 
 
 _grouped_fwd = torch.library.custom_op("griffin_b200::grouped_fwd", _grouped_fwd_impl, mutates_args=())
@@ -613,23 +614,25 @@ _grouped_fwd = torch.library.custom_op("griffin_b200::grouped_fwd", _grouped_fwd
 @_grouped_fwd.register_fake
 def _(x, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch, save):
     B, T, D = x.shape
+    G, bw, _ = w_r.shape
     return (torch.empty_like(x), x.new_empty((B, D), dtype=torch.float32), x.new_empty((B, T, 2 * D)),
-            x.new_empty((workspace_bytes(B, T, D) if save else 0,), dtype=torch.uint8))
+            x.new_empty((workspace_bytes(B, T, D) if save else 0,), dtype=torch.uint8),
+            x.new_empty((G, 2 * bw, bw)), x.new_empty((2 * D,), dtype=torch.float32))
 
 
-def _grouped_bwd_impl(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, u: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor,
-                 b_i: Tensor, branch: Optional[Tensor], lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
+def _grouped_bwd_impl(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, u: Tensor, wcat: Tensor, bias: Tensor,
+                 branch: Optional[Tensor], lam: Tensor, h0: Optional[Tensor], tok: Optional[Tensor],
                  ws: Tensor, c: float, want_dh0: bool
-                 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
-    """(dx, dw_r, db_r, dw_i, db_i, dLambda, dh0, dbranch); absent results are empty tensors."""
+                 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """(dx, d stacked weights [G, 2 bw, bw], d stacked biases [G, 2 bw] fp32, dLambda, dh0, dbranch) from the stacked
+    weights and biases the forward built; absent results are empty tensors.  The caller slices the two stacked
+    gradients into the gates' own."""
     lib = _lib.load()
     with torch.autocast("cuda", enabled=False):
         x = _aligned16(x)
         B, T, D = x.shape
-        G, bw, _ = w_r.shape
-        bw2 = 2 * bw
+        G, bw2, bw = wcat.shape
         dt = _io_dtype(x, "grouped backward")
-        wcat, bias = _stacked_gates(x, w_r, b_r, w_i, b_i)
         dout = _aligned16(dout)
         branch = _aligned16(branch)
         dx = torch.empty_like(x)
@@ -648,41 +651,42 @@ def _grouped_bwd_impl(dout: Tensor, dh_last: Optional[Tensor], x: Tensor, u: Ten
         rows = x.view(B * T, G, bw).transpose(0, 1)                    # [G, N, bw] view
         dx.view(B * T, G, bw).transpose(0, 1).baddbmm_(dg, wcat)       # gate path added onto the direct path
         dwcat = torch.bmm(dg.transpose(1, 2), rows)                    # [G, 2 bw, bw]
-    # (copies, not views: results of an operator may not share storage)
-    return (dx, dwcat[:, :bw].to(w_r.dtype).contiguous(), dbias[:, :bw].to(b_r.dtype).contiguous(),
-            dwcat[:, bw:].to(w_i.dtype).contiguous(), dbias[:, bw:].to(b_i.dtype).contiguous(), dlam, dh0, dbranch)
+    return dx, dwcat, dbias, dlam, dh0, dbranch
 
 
 _grouped_bwd = torch.library.custom_op("griffin_b200::grouped_bwd", _grouped_bwd_impl, mutates_args=())
 
 
 @_grouped_bwd.register_fake
-def _(dout, dh_last, x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws, c, want_dh0):
+def _(dout, dh_last, x, u, wcat, bias, branch, lam, h0, tok, ws, c, want_dh0):
     B, T, D = x.shape
-    return (torch.empty_like(x), torch.empty_like(w_r), torch.empty_like(b_r), torch.empty_like(w_i),
-            torch.empty_like(b_i), x.new_empty((D,), dtype=torch.float32),
-            x.new_empty((B, D) if want_dh0 else (0,), dtype=torch.float32),
+    G, bw2, _ = wcat.shape
+    return (torch.empty_like(x), torch.empty_like(wcat), x.new_empty((G, bw2), dtype=torch.float32),
+            x.new_empty((D,), dtype=torch.float32), x.new_empty((B, D) if want_dh0 else (0,), dtype=torch.float32),
             torch.empty_like(x) if branch is not None else x.new_empty((0,)))
 
 
 def _grouped_setup(ctx, inputs, output):
     x, w_r, b_r, w_i, b_i, lam, h0, tok, c, branch, save = inputs
-    _, _, u, ws = output
-    ctx.save_for_backward(x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws)
+    _, _, u, ws, wcat, bias = output
+    ctx.save_for_backward(x, u, wcat, bias, branch, lam, h0, tok, ws)
     ctx.c, ctx.saved = c, save
+    ctx.param_dtypes = (w_r.dtype, b_r.dtype, w_i.dtype, b_i.dtype)
     ctx.want_dh0 = h0 is not None and ctx.needs_input_grad[6]
 
 
-def _grouped_backward(ctx, dout, dh_last, _du, _dws, _bwd=None):
+def _grouped_backward(ctx, dout, dh_last, _du, _dws, _dwcat, _dbias, _bwd=None):
     if not ctx.saved:
         raise RuntimeError("grouped RG-LRU was run without saving its workspace; backward is unavailable")
-    x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws = ctx.saved_tensors
+    x, u, wcat, bias, branch, lam, h0, tok, ws = ctx.saved_tensors
     dout = torch.zeros_like(x) if dout is None else dout.to(x.dtype).contiguous()
     dh_last = None if dh_last is None else dh_last.to(torch.float32).contiguous()
-    dx, dw_r, db_r, dw_i, db_i, dlam, dh0, dbranch = (_bwd or _grouped_bwd)(
-        dout, dh_last, x, u, w_r, b_r, w_i, b_i, branch, lam, h0, tok, ws, ctx.c, ctx.want_dh0)
-    return (dx, dw_r, db_r, dw_i, db_i, dlam, (dh0 if ctx.want_dh0 else None), None, None,
-            (dbranch if branch is not None else None), None)
+    dx, dwcat, dbias, dlam, dh0, dbranch = (_bwd or _grouped_bwd)(
+        dout, dh_last, x, u, wcat, bias, branch, lam, h0, tok, ws, ctx.c, ctx.want_dh0)
+    bw = wcat.shape[2]
+    dt_wr, dt_br, dt_wi, dt_bi = ctx.param_dtypes
+    return (dx, dwcat[:, :bw].to(dt_wr), dbias[:, :bw].to(dt_br), dwcat[:, bw:].to(dt_wi), dbias[:, bw:].to(dt_bi),
+            dlam, (dh0 if ctx.want_dh0 else None), None, None, (dbranch if branch is not None else None), None)
 
 
 _grouped_fwd.register_autograd(_grouped_backward, setup_context=_grouped_setup)
@@ -708,7 +712,7 @@ def rglru_grouped(x: Tensor, w_r: Tensor, b_r: Tensor, w_i: Tensor, b_i: Tensor,
                          "rows that are a multiple of 16 bytes")
     save = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (x, w_r, b_r, w_i, b_i, lam, h0, branch))
-    out, h_last, _, _ = (_grouped_fwd if _library_ops_active() else _GroupedNode.apply)(
+    out, h_last, _, _, _, _ = (_grouped_fwd if _library_ops_active() else _GroupedNode.apply)(
         x.contiguous(), w_r, b_r, w_i, b_i, lam.to(torch.float32).contiguous(),
         None if h0 is None else h0.to(torch.float32).contiguous(), None if tok is None else tok.contiguous(), float(c),
         None if branch is None else branch.to(x.dtype).contiguous(), save)

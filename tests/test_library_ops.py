@@ -39,9 +39,9 @@ def test_backward_ops_infer_shapes_without_a_gpu():
             w, b, lam = torch.randn(G, 64, 64), torch.randn(G, 64), torch.randn(D)
             ws = torch.empty(ops.workspace_bytes(B, T, D), dtype=torch.uint8)
             h0 = torch.randn(B, D)
-            got = ops._grouped_bwd(x, None, x, u, w, b, w, b, x, lam, h0, None, ws, 8.0, True)
-            assert [tuple(t.shape) for t in got] == [(B, T, D), (G, 64, 64), (G, 64), (G, 64, 64), (G, 64), (D,), (B, D),
-                                                     (B, T, D)]
+            wcat, bcat = torch.randn(G, 128, 64), torch.randn(2 * D)
+            got = ops._grouped_bwd(x, None, x, u, wcat, bcat, x, lam, h0, None, ws, 8.0, True)
+            assert [tuple(t.shape) for t in got] == [(B, T, D), (G, 128, 64), (G, 128), (D,), (B, D), (B, T, D)]
             got = ops._core_bwd(x, None, x, torch.randn(D, 4), torch.randn(D), torch.randn(B, 3, D), w, w, lam, None, None,
                                 x, x, ws, None, 8.0, False, True)
             assert [tuple(t.shape) for t in got] == [(B, T, D), (D, 4), (D,), (B, 3, D), (G, 64, 64), (G, 64), (G, 64, 64),
@@ -123,3 +123,26 @@ def test_block_called_first_under_inference_mode_then_trained():
     torch.cuda.current_stream().wait_stream(side)
     assert rel_l2(out, first) <= 1e-6 and torch.isfinite(xi.grad).all()
     assert not any(t.is_inference() for t in modules._PLAIN_FLAGS.values())
+
+
+def test_linear_is_functional_linear_off_the_gpu_and_under_tracing():
+    """ops.linear only taps the bias gradient for CUDA tensors outside tracing; everywhere else it is F.linear."""
+    from griffin_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(3, 5, 8, requires_grad=True)
+    w = torch.randn(4, 8, requires_grad=True)
+    b = torch.randn(4, requires_grad=True)
+    out = ops.linear(x, w, b)
+    assert "BiasGradTap" not in type(out.grad_fn).__name__
+    ref = torch.nn.functional.linear(x, w, b)
+    assert torch.equal(out, ref)
+    got = torch.autograd.grad(out.sum(), (x, w, b))
+    want = torch.autograd.grad(ref.sum(), (x, w, b))
+    for a, r in zip(got, want):
+        assert torch.equal(a, r)
+    with ops.library_ops():
+        assert "BiasGradTap" not in type(ops.linear(x, w, b).grad_fn).__name__
+    with pytest.raises(RuntimeError):
+        ops.column_sums(torch.zeros(4, 4))           # the kernel has no CPU path
+    with pytest.raises(ValueError):
+        ops.column_sums(torch.zeros(4))
