@@ -410,14 +410,14 @@ def run_c4a_shard(args, d: Dist) -> dict:
 
 
 def run_time_shard(args, d: Dist) -> dict:
-    """One sequence of B=8, D=1024, bf16, T = 8192 per rank, split along TIME over the ranks: forward + backward
+    """One sequence of B=8, D=1024 (``--width``), bf16, T = 8192 per rank, split along TIME over the ranks: forward + backward
     through ``griffin_b200.time_shard.rglru_time_sharded`` (per direction a carry-only pass, one all-gather of
     [B, D] carries over NCCL, and the full pass); beside it the same rank's slice as an ordinary
     unsplit call, i.e. what the step would cost were there no carry between the slices."""
     from griffin_b200 import _lib, ops
     from griffin_b200.time_shard import rglru_time_sharded
 
-    B, TS, D = 8, 8192, 1024
+    B, TS, D = 8, 8192, args.width
     dev, world = d.dev, d.world
     if world == 1 and not d.dist.is_initialized():     # the operator wants a process group even for one slice
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -464,7 +464,7 @@ def run_time_shard(args, d: Dist) -> dict:
             "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 I/O, f32 state", "data": "synthetic",
             "config": {"workload": f"time-sharded RG-LRU fwd+bwd bf16 B={B} T={TS * world} ({TS} per rank) D={D}",
-                       "l2": "three rotating input sets of 537 MB each"},
+                       "l2": f"three rotating input sets of {4 * 2 * B * TS * D / 1e6:.0f} MB each"},
             "timing": {"regions": len(regions), "value_is": "median over regions",
                        "ms_per_step_min": min(regions), "ms_per_step_max": max(regions)},
             "unsplit_slice_ms_per_step": ms_one, "cost_of_the_split": ms / ms_one,
@@ -825,6 +825,7 @@ def main() -> None:
     ap.add_argument("--fold", default="merge", choices=["none", "conv", "merge"],
                     help="c2/c3: run conv (and the GeLU-branch product) inside the scan kernels")
     ap.add_argument("--graph", action="store_true", help="c2: replay the block's forward and backward as CUDA graphs")
+    ap.add_argument("--width", type=int, default=1024, help="tshard: channels D of the time-sharded sequence")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="default workload: skip the c4a and c3 sub-objects")

@@ -81,6 +81,26 @@ static bool encode_map(CUtensorMap* map, const void* base, bool bf16, int B, int
   return r == CUDA_SUCCESS;
 }
 
+// 5-D map over the same tensor for the paired-row tiles of the 32-channel forward: time is viewed as
+// t = 8 q + 4 h + j and the dimensions are ordered (channel, h, j, q, batch), so that a box of
+// [32 channels, 2, 4, rows / 8, 1] arrives in shared memory as [q][j][h][channel]: rows t and t + 4 side by side
+// in one 128-byte line.  T must be a multiple of 8 (the caller asks for it only on whole 128-step chunks).
+static bool encode_map_paired(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || T % 8 != 0 || rows % 8 != 0) return false;
+  const size_t es = bf16 ? 2 : 4;
+  const cuuint64_t pitch = static_cast<cuuint64_t>(D) * es;
+  const cuuint64_t dims[5] = {static_cast<cuuint64_t>(D), 2u, 4u, static_cast<cuuint64_t>(T / 8), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[4] = {4 * pitch, pitch, 8 * pitch, pitch * T};
+  const cuuint32_t box[5] = {static_cast<cuuint32_t>(cols), 2u, 4u, static_cast<cuuint32_t>(rows / 8), 1u};
+  const cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+  const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // A tensor map is a pure function of (base address, element type, shape, box), and a training loop calls with
 // the same handful of buffers step after step (the caching allocator hands the same blocks back), so encoded
 // maps are kept in a small per-thread table: a hit costs a compare and a 128-byte copy instead of a driver call
@@ -99,9 +119,10 @@ struct MapSlot {
 };
 constexpr int MAP_CACHE_SLOTS = 256;   // direct-mapped
 
-static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols) {
+static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T, int D, int rows, int cols,
+                     bool paired = false) {
   static thread_local MapSlot table[MAP_CACHE_SLOTS] = {};
-  const MapKey key{base, B, T, D, rows, cols, bf16 ? 1 : 0};
+  const MapKey key{base, B, T, D, paired ? -rows : rows, cols, bf16 ? 1 : 0};   // negative rows: the paired 5-D form
   uint64_t h = reinterpret_cast<uintptr_t>(base) >> 8;
   h ^= (static_cast<uint64_t>(rows) << 3) ^ (static_cast<uint64_t>(cols) << 11) ^ (static_cast<uint64_t>(D) << 17) ^
        (static_cast<uint64_t>(T) << 29) ^ (static_cast<uint64_t>(B) << 41);
@@ -111,7 +132,8 @@ static bool make_map(CUtensorMap* map, const void* base, bool bf16, int B, int T
     *map = slot.map;
     return true;
   }
-  if (!encode_map(map, base, bf16, B, T, D, rows, cols)) return false;
+  if (!(paired ? encode_map_paired(map, base, bf16, B, T, D, rows, cols) : encode_map(map, base, bf16, B, T, D, rows, cols)))
+    return false;
   slot.key = key;
   slot.map = *map;
   slot.used = true;
@@ -239,9 +261,10 @@ static int fwd_common(const void* x, const void* u_r, const void* u_i, const flo
   const int variant = y ? scan_fwd_variant(B, T, D, bf16) : 0;   // the carry-only pass exists in the 64-channel shape only
   if (tma) {
     const int rows = scan_fwd_box_rows(variant), cols = scan_fwd_box_cols(variant);
-    tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&
-          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) &&
-          make_map(&maps.y, y ? y : x, bf16, B, T, D, rows, cols);   // without y the map is never used
+    const bool paired = scan_fwd_paired(variant, bf16, tok, T);
+    tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols, paired) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols, paired) &&
+          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols, paired) &&
+          make_map(&maps.y, y ? y : x, bf16, B, T, D, rows, cols, paired);   // without y the map is never used
   }
   const cudaError_t e = launch_scan_fwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);

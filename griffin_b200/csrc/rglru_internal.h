@@ -191,6 +191,8 @@ int scan_fwd_variant(int B, int T, int D, bool bf16);
 int scan_bwd_variant(int B, int T, int D, bool bf16);
 int scan_fwd_box_rows(int variant);
 int scan_fwd_box_cols(int variant);
+// True when the call takes the paired-row tile layout, whose tensor maps are 5-D (see rglru_fwd_body).
+bool scan_fwd_paired(int variant, bool bf16, const void* tok, int T);
 int scan_bwd_box_rows(int variant);
 int scan_bwd_box_cols(int variant);
 int raw_box_cols();

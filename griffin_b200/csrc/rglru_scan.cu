@@ -244,7 +244,7 @@ __device__ __forceinline__ void load_hist(const void* conv_state, int b, int d, 
 // Forward
 // ======================================================================
 
-template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV, bool GROUPED>
+template <typename IO, int TS, int CH, bool MASKED, bool POLY, bool CONV, bool GROUPED, int RSTEP = CH * sizeof(IO)>
 __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, const uint8_t* ti, int off0,
                                           const float2 (&K)[2], const uint32_t (&fl)[(TS + 3) / 4],
                                           const ConvTaps& ct, const float2 (*hist)[2], const GateBias& gb,
@@ -256,7 +256,7 @@ __device__ __forceinline__ void fwd_local(const uint8_t* tx, const uint8_t* tr, 
   if (CONV) conv_front<IO, CONV ? TS : 1, CH, MASKED>(tx, off0, ct, fl, hist, xc);
 #pragma unroll
   for (int st = 0; st < TS; ++st) {
-    const int off = off0 + st * ROWB;
+    const int off = off0 + st * RSTEP;   // RSTEP: bytes between a thread's consecutive steps in the tile
     float2 xv[2], rv[2], iv[2];
     if (CONV) { xv[0] = xc[CONV ? st : 0][0]; xv[1] = xc[CONV ? st : 0][1]; }
     else Pack<IO>::unpack2(Pack<IO>::load(tx + off), xv);
@@ -309,13 +309,20 @@ struct FwdSmem {
 // MERGE: the kernel also reads the pre-activation of the block's GeLU branch and writes
 // h_t * gelu(branch_t) (griffin/griffin.py:464, 520 of the reference) instead of h_t.
 template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false,
-          bool CARRY = false>
+          bool CARRY = false, bool PAIRED = false>
 __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFwdArgs& p) {
   using SM = FwdSmem<IO, TS, LANES, CH, NSTAGE, CONV, MERGE>;
   static_assert(!CONV || (SM::HALO % 128 == 0), "the halo must keep the result rows 128-byte aligned for TMA");
   constexpr int NCV = CH / CV;
   constexpr int TC = SM::TC;
   constexpr int ROWB = CH * sizeof(IO);
+  // PAIRED: 64-byte tile rows (32 bf16 channels) put the four time-lanes of a warp on the same sixteen banks.  The
+  // tile is then staged through 5-D tensor maps that view time as (eighth, half, step), t = 8 q + 4 h + j, and lay
+  // it out as [q][j][h][channels]: rows t and t + 4 share one 128-byte line, a thread's four steps are 128 bytes
+  // apart, and two neighbouring time-lanes fill a line between them, so a warp's access touches every bank once.
+  static_assert(!PAIRED || (USE_TMA && PLAIN && !CONV && !MERGE && !GROUPED && TS == 4 && ROWB == 64 && TC % 8 == 0),
+                "paired rows: plain TMA-staged kernel on 64-byte rows only");
+  constexpr int RSTEP = PAIRED ? 2 * ROWB : ROWB;
   constexpr int NCOMP = LANES * NCV;
   extern __shared__ __align__(128) uint8_t smem[];
   float2* agg = reinterpret_cast<float2*>(smem + SM::OFF_AGG);
@@ -339,10 +346,16 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
     const int sidx = k % NSTAGE;
     uint8_t* st = smem + sidx * SM::STAGE;
     mbar_expect_tx(&full[sidx], SM::STAGE);
-    tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
-    tma_load_3d(st + SM::TILEX, &maps.ur, rcol, k * TC, b, &full[sidx]);
-    tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, icol, k * TC, b, &full[sidx]);
-    if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
+    if constexpr (PAIRED) {
+      tma_load_5d(st, &maps.x, d0, 0, 0, k * (TC / 8), b, &full[sidx]);
+      tma_load_5d(st + SM::TILEX, &maps.ur, d0, 0, 0, k * (TC / 8), b, &full[sidx]);
+      tma_load_5d(st + SM::TILEX + SM::TILE, &maps.ui, d0, 0, 0, k * (TC / 8), b, &full[sidx]);
+    } else {
+      tma_load_3d(st, &maps.x, d0, k * TC - (CONV ? 3 : 0), b, &full[sidx]);   // rows before t = 0 read as zero
+      tma_load_3d(st + SM::TILEX, &maps.ur, rcol, k * TC, b, &full[sidx]);
+      tma_load_3d(st + SM::TILEX + SM::TILE, &maps.ui, icol, k * TC, b, &full[sidx]);
+      if (MERGE) tma_load_3d(st + SM::OFF_G, &maps.g, d0, k * TC, b, &full[sidx]);
+    }
   };
   // Set-up by the thread that will issue the bulk copies, published by one early CTA barrier; after it the
   // producer warp and the compute warps go their own ways (the compute warps vote among themselves), so the
@@ -356,10 +369,16 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       prefetch_map(&maps.x); prefetch_map(&maps.ur); prefetch_map(&maps.ui); prefetch_map(&maps.y);
       if (MERGE) prefetch_map(&maps.g);
       // While the kernel in front of this one on the stream drains, pull the first chunk towards L2.
-      tma_prefetch_3d(&maps.x, d0, -(CONV ? 3 : 0), b);
-      tma_prefetch_3d(&maps.ur, rcol, 0, b);
-      tma_prefetch_3d(&maps.ui, icol, 0, b);
-      if (MERGE) tma_prefetch_3d(&maps.g, d0, 0, b);
+      if constexpr (PAIRED) {
+        tma_prefetch_5d(&maps.x, d0, 0, 0, 0, b);
+        tma_prefetch_5d(&maps.ur, d0, 0, 0, 0, b);
+        tma_prefetch_5d(&maps.ui, d0, 0, 0, 0, b);
+      } else {
+        tma_prefetch_3d(&maps.x, d0, -(CONV ? 3 : 0), b);
+        tma_prefetch_3d(&maps.ur, rcol, 0, b);
+        tma_prefetch_3d(&maps.ui, icol, 0, b);
+        if (MERGE) tma_prefetch_3d(&maps.g, d0, 0, b);
+      }
     }
   }
   __syncthreads();
@@ -377,7 +396,8 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       for (int k = 0; k < nchunks; ++k) {
         const int sidx = k % NSTAGE;
         mbar_wait_or_flag(&ready[sidx], (k / NSTAGE) & 1, dead, p.status, DEV_TIMEOUT_STORE);
-        if (!CARRY) tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);
+        if constexpr (PAIRED) tma_store_5d(&maps.y, smem + sidx * SM::STAGE, d0, 0, 0, k * (TC / 8), b);
+        else if (!CARRY) tma_store_3d(&maps.y, smem + sidx * SM::STAGE + SM::HALO, d0, k * TC, b);
         tma_commit();
         if (k + NSTAGE < nchunks) {
           tma_wait_read<0>();
@@ -419,7 +439,8 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
   const bool want_prod = p.decay_prod != nullptr;
   float prod_all = 1.0f;
 
-  const int off0 = (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
+  const int off0 = PAIRED ? ((lane_t >> 1) * TS) * RSTEP + (lane_t & 1) * ROWB + vec * Pack<IO>::BYTES
+                          : (lane_t * TS) * ROWB + vec * Pack<IO>::BYTES;
 
   for (int k = 0; k < nchunks; ++k) {
     const int stage = USE_TMA ? (k % NSTAGE) : 0;
@@ -450,11 +471,11 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
       hist = hist_v;
     }
     if (masked && any_flag(fl)) {
-      if (poly) fwd_local<IO, TS, CH, true, true, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
-      else fwd_local<IO, TS, CH, true, false, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
+      if (poly) fwd_local<IO, TS, CH, true, true, CONV, GROUPED, RSTEP>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
+      else fwd_local<IO, TS, CH, true, false, CONV, GROUPED, RSTEP>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
     } else {
-      if (poly) fwd_local<IO, TS, CH, false, true, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
-      else fwd_local<IO, TS, CH, false, false, CONV, GROUPED>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
+      if (poly) fwd_local<IO, TS, CH, false, true, CONV, GROUPED, RSTEP>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
+      else fwd_local<IO, TS, CH, false, false, CONV, GROUPED, RSTEP>(tx, tr, ti, off0, K, fl, ct, hist, gb, P, S);
     }
     {
       float4* dst = reinterpret_cast<float4*>(agg + lane_t * CH + vec * CV);
@@ -528,11 +549,11 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
         for (int cp = 0; cp < 2; ++cp) yv[cp] = fma2(P[st][cp], e[cp], S[st][cp]);
         if (MERGE) {
           float2 gv[2];
-          Pack<IO>::unpack2(Pack<IO>::load(tiles + SM::OFF_G + off0 + st * ROWB), gv);
+          Pack<IO>::unpack2(Pack<IO>::load(tiles + SM::OFF_G + off0 + st * RSTEP), gv);
 #pragma unroll
           for (int cp = 0; cp < 2; ++cp) yv[cp] = mul2(yv[cp], mul2(gv[cp], gelu_sigmoid2<sizeof(IO) == 2>(gv[cp])));
         }
-        Pack<IO>::store2(ty + off0 + st * ROWB, yv);
+        Pack<IO>::store2(ty + off0 + st * RSTEP, yv);
       }
     }
     if (USE_TMA) {
@@ -551,11 +572,12 @@ __device__ __forceinline__ void rglru_fwd_body(const FwdMaps& maps, const ScanFw
 
 // PLAIN: no token flags and a whole number of chunks, so the masked arithmetic is not compiled in.
 // CARRY: the carry-only pass of a time-split sequence: no output tensor, nothing is stored but h_last and decay_prod.
+// PAIRED: 64-byte tile rows staged two to a 128-byte line through 5-D tensor maps (see rglru_fwd_body).
 template <typename IO, int TS, int LANES, int CH, int NSTAGE, bool USE_TMA, bool CONV, bool MERGE, bool GROUPED, bool PLAIN = false,
-          bool CARRY = false>
+          bool CARRY = false, bool PAIRED = false>
 __global__ void __launch_bounds__(LANES*(CH / CV) + (USE_TMA ? 32 : 0))
     rglru_fwd_kernel(const __grid_constant__ FwdMaps maps, const ScanFwdArgs p) {
-  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY>(maps, p);
+  rglru_fwd_body<IO, TS, LANES, CH, NSTAGE, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY, PAIRED>(maps, p);
 }
 // The same kernel capped at 96 registers, which lets two 9-warp CTAs share an SM's register files (five warps
 // on one scheduler partition).  Used for the merged / grouped variants, which otherwise take about 112.
@@ -1763,6 +1785,12 @@ struct Shape32x32x4 { static constexpr int CH = 32, LANES = 32, TS = 4; };
 static bool fwd_variant_exists(int v) { return v == 0 || v == 2; }
 static bool bwd_variant_exists(int v) { return v == 0 || v == 3; }
 
+// Whether a forward call takes the paired-row tile layout: the 32-channel shape on bf16 tensors without token
+// flags over a whole number of 128-step chunks.  The API encodes 5-D tensor maps exactly when this says so.
+bool scan_fwd_paired(int variant, bool bf16, const void* tok, int T) {
+  static const bool off = getenv("RGLRU_NO_PAIRED") != nullptr;
+  return !off && variant == 2 && bf16 && tok == nullptr && T % 128 == 0;
+}
 int scan_fwd_box_rows(int v) { return v == 2 ? 128 : 64; }
 int scan_fwd_box_cols(int v) { return v == 2 ? 32 : 64; }
 int scan_bwd_box_rows(int) { return 64; }
@@ -1828,16 +1856,16 @@ template <typename... Ts> struct KernelTag {};
 template <int... Vs> struct IntTag {};
 
 template <typename IO, typename V, int STAGES, bool USE_TMA, bool CONV = false, bool MERGE = false, bool GROUPED = false,
-          bool PLAIN = false, bool CARRY = false>
+          bool PLAIN = false, bool CARRY = false, bool PAIRED = false>
 static cudaError_t launch_fwd_t(const FwdMaps& maps, const ScanFwdArgs& a, cudaStream_t s) {
   constexpr int ST = USE_TMA ? STAGES : 1;
   constexpr bool CAPPED = USE_TMA && !CONV && (MERGE || GROUPED);
   void (*kern)(FwdMaps, ScanFwdArgs);
   if constexpr (CAPPED) kern = rglru_fwd_kernel_capped<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED>;
-  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY>;
+  else kern = rglru_fwd_kernel<IO, V::TS, V::LANES, V::CH, ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY, PAIRED>;
   constexpr int bytes = FwdSmem<IO, V::TS, V::LANES, V::CH, ST, CONV, MERGE>::BYTES;
   static_assert(bytes <= 232448, "shared memory of one CTA");
-  cudaError_t e = set_smem<KernelTag<FwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY>>>(kern, bytes);
+  cudaError_t e = set_smem<KernelTag<FwdMaps, IO, V, IntTag<ST, USE_TMA, CONV, MERGE, GROUPED, PLAIN, CARRY, PAIRED>>>(kern, bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((a.D + V::CH - 1) / V::CH, a.B);
   return launch_pdl(kern, grid, V::LANES * (V::CH / CV) + (USE_TMA ? 32 : 0), bytes, s, maps, a);
@@ -1852,7 +1880,13 @@ static cudaError_t launch_fwd_io(bool use_tma, int variant, const FwdMaps& maps,
   if (!use_tma) return launch_fwd_t<IO, Shape64x16x4, 1, false>(maps, a, s);
   const bool plain = a.tok == nullptr && a.T % 128 == 0;   // no step of any chunk is masked
   if (plain && variant == 0) return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
-  if (plain && variant == 2) return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
+  if (plain && variant == 2) {
+    if constexpr (H) {   // 64-byte rows: the paired-row layout (the caller encoded 5-D maps, see scan_fwd_paired)
+      if (scan_fwd_paired(variant, true, a.tok, a.T))
+        return launch_fwd_t<IO, Shape32x32x4, 4, true, false, false, false, true, false, true>(maps, a, s);
+    }
+    return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
+  }
   if (variant == 2) return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true>(maps, a, s);
   return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true>(maps, a, s);
 }
