@@ -261,10 +261,13 @@ static int fwd_common(const void* x, const void* u_r, const void* u_i, const flo
   const int variant = y ? scan_fwd_variant(B, T, D, bf16) : 0;   // the carry-only pass exists in the 64-channel shape only
   if (tma) {
     const int rows = scan_fwd_box_rows(variant), cols = scan_fwd_box_cols(variant);
-    const bool paired = scan_fwd_paired(variant, bf16, tok, T);
-    tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols, paired) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols, paired) &&
-          make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols, paired) &&
-          make_map(&maps.y, y ? y : x, bf16, B, T, D, rows, cols, paired);   // without y the map is never used
+    const void* yy = y ? y : x;   // without y the map is never used
+    a.paired = scan_fwd_paired(variant, bf16, tok, T) && make_map(&maps.x, x, bf16, B, T, D, rows, cols, true) &&
+               make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols, true) &&
+               make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols, true) && make_map(&maps.y, yy, bf16, B, T, D, rows, cols, true);
+    if (!a.paired)
+      tma = make_map(&maps.x, x, bf16, B, T, D, rows, cols) && make_map(&maps.ur, u_r, bf16, B, T, D, rows, cols) &&
+            make_map(&maps.ui, u_i, bf16, B, T, D, rows, cols) && make_map(&maps.y, yy, bf16, B, T, D, rows, cols);
   }
   const cudaError_t e = launch_scan_fwd(bf16, tma, variant, maps, a, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? RGLRU_OK : fail_cuda(e);

@@ -35,6 +35,7 @@ struct ScanFwdArgs {
   // gate_bias [2 D] fp32 in the same column layout or nullptr
   const float* gate_bias;
   int gate_bw;
+  bool paired;  // the four tensor maps are the 5-D paired-row form (32-channel bf16 forward without flags)
   int B, T, D;
   float c;
   int* status;

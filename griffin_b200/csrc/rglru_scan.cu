@@ -9,7 +9,8 @@
 // shared memory by TMA (cp.async.bulk.tensor, 3-D tiles [1, rows, channels]) in a multi-stage mbarrier
 // pipeline; results are written back into the stage in place and leave through TMA stores.  The bulk copies
 // are issued either by a producer warp or, for the bf16 backward, by one compute thread (SELF_ISSUE: eight
-// warps leave every thread the registers it wants).  A bounds-checked plain-load staging path with the same
+// warps leave every thread the registers it wants).  The 64-byte rows of 32-channel bf16 tiles are staged two to a
+// 128-byte line through 5-D tensor maps (PAIRED), which halves the forward's shared-memory bank conflicts.  A bounds-checked plain-load staging path with the same
 // arithmetic covers shapes TMA cannot address (D * element size not a multiple of 16 bytes).
 //
 // What bounds them (ncu on B200, bf16, B = 8, T = 2048, D = 1024): DRAM traffic equals the algorithmic bytes;
@@ -1788,8 +1789,7 @@ static bool bwd_variant_exists(int v) { return v == 0 || v == 3; }
 // Whether a forward call takes the paired-row tile layout: the 32-channel shape on bf16 tensors without token
 // flags over a whole number of 128-step chunks.  The API encodes 5-D tensor maps exactly when this says so.
 bool scan_fwd_paired(int variant, bool bf16, const void* tok, int T) {
-  static const bool off = getenv("RGLRU_NO_PAIRED") != nullptr;
-  return !off && variant == 2 && bf16 && tok == nullptr && T % 128 == 0;
+  return variant == 2 && bf16 && tok == nullptr && T % 128 == 0;
 }
 int scan_fwd_box_rows(int v) { return v == 2 ? 128 : 64; }
 int scan_fwd_box_cols(int v) { return v == 2 ? 32 : 64; }
@@ -1881,9 +1881,8 @@ static cudaError_t launch_fwd_io(bool use_tma, int variant, const FwdMaps& maps,
   const bool plain = a.tok == nullptr && a.T % 128 == 0;   // no step of any chunk is masked
   if (plain && variant == 0) return launch_fwd_t<IO, Shape64x16x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
   if (plain && variant == 2) {
-    if constexpr (H) {   // 64-byte rows: the paired-row layout (the caller encoded 5-D maps, see scan_fwd_paired)
-      if (scan_fwd_paired(variant, true, a.tok, a.T))
-        return launch_fwd_t<IO, Shape32x32x4, 4, true, false, false, false, true, false, true>(maps, a, s);
+    if constexpr (H) {   // 64-byte rows: the paired-row layout when the caller could encode its 5-D maps
+      if (a.paired) return launch_fwd_t<IO, Shape32x32x4, 4, true, false, false, false, true, false, true>(maps, a, s);
     }
     return launch_fwd_t<IO, Shape32x32x4, H ? 4 : 3, true, false, false, false, true>(maps, a, s);
   }

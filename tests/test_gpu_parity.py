@@ -154,8 +154,10 @@ def test_bf16_near_unit_decay_stays_finite():
 
 # (70, 40, 64): more than 64 batch rows, where the dLambda rows are folded by a second kernel instead of the
 # backward kernel's last CTA
+# (3, 256, 200), (2, 384, 72), (1, 512, 40): whole 128-step chunks on few tiles, where unmasked bf16 calls stage
+# their 32-channel forward tiles through the 5-D (paired-row) tensor maps, with a ragged last tile
 SHAPES = [(1, 1, 1), (2, 5, 6), (1, 63, 64), (2, 64, 64), (2, 65, 128), (3, 67, 65), (2, 130, 257),
-          (2, 200, 72), (1, 257, 320), (4, 33, 8), (70, 40, 64)]
+          (2, 200, 72), (1, 257, 320), (4, 33, 8), (70, 40, 64), (3, 256, 200), (2, 384, 72), (1, 512, 40)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
