@@ -245,6 +245,67 @@ def _last_real_position(segment_pos: Tensor, active: Optional[Tensor], previous:
     return torch.where(last > 0, picked, fallback)
 
 
+def _stable_partition(active: Tensor) -> tuple[Tensor, Tensor]:
+    """Indices that move every row's real tokens to the front, order kept (and the padding behind them, order kept):
+    ``order[b, j]`` is the token that lands at place j, ``restore[b, t]`` the place token t lands at.  Two running
+    counts and one scatter instead of two sorts: a real token's place is the number of real tokens before it, a
+    padding token's the row's real count plus the padding before it."""
+    real = active.to(torch.long)
+    before_real = real.cumsum(dim=1) - real                    # real tokens strictly before t
+    pad = 1 - real
+    before_pad = pad.cumsum(dim=1) - pad
+    restore = torch.where(active, before_real, real.sum(dim=1, keepdim=True) + before_pad)
+    steps = torch.arange(active.shape[1], device=active.device, dtype=torch.long).expand_as(restore)
+    order = torch.empty_like(restore).scatter_(1, restore, steps)
+    return order, restore
+
+
+def _flat_rows(index: Tensor) -> Tensor:
+    """Per-row sequence indices [B, T] as indices into the flattened [B * T] tokens."""
+    batch, steps = index.shape
+    return (index + torch.arange(batch, device=index.device, dtype=index.dtype)[:, None] * steps).reshape(-1)
+
+
+class _PermuteRows(torch.autograd.Function):
+    """Move whole tokens of a [B, T, D] tensor by a permutation of every row, given as flat token indices
+    (``_flat_rows``) together with those of the inverse permutation: one index per token (``index_select`` on the
+    flattened tokens, not an index per element), and a backward that is the same move with the inverse permutation,
+    not the atomic scatter-add autograd would use for a gather."""
+
+    @staticmethod
+    def forward(ctx, x, flat_index, flat_inverse):
+        ctx.save_for_backward(flat_inverse)
+        return x.reshape(flat_index.numel(), -1).index_select(0, flat_index).view(x.shape)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (flat_inverse,) = ctx.saved_tensors
+        return grad.reshape(flat_inverse.numel(), -1).index_select(0, flat_inverse).view(grad.shape), None, None
+
+
+_PADDING_KIND: dict = {}     # id(mask tensor) -> (weak reference, version, answer)
+
+
+def _needs_partition(active: Tensor, owner: Tensor) -> bool:
+    """Whether some row has a real token after padding (anything but right padding).  The answer costs a
+    device-to-host read, so it is remembered per mask OBJECT (``owner``: the tensor the caller passed, of which
+    ``active`` is the boolean copy on the right device) and version: a model hands the same mask tensor to every one
+    of its blocks, and only the first of them waits for the device."""
+    import weakref
+    key = id(owner)
+    hit = _PADDING_KIND.get(key)
+    if hit is not None and hit[0]() is owner and hit[1] == owner._version:
+        return hit[2]
+    answer = bool((active[:, 1:] & ~active[:, :-1]).any())
+    if len(_PADDING_KIND) > 64:
+        _PADDING_KIND.clear()
+    try:
+        _PADDING_KIND[key] = (weakref.ref(owner), owner._version, answer)
+    except TypeError:      # (a tensor subclass without weak references: no caching)
+        pass
+    return answer
+
+
 def _project(layer: nn.Module, x: Tensor) -> Tensor:
     """One of the block's three projections.  A stock ``nn.Linear`` without hooks goes through ``ops.linear`` (same
     GEMMs; the bias gradient comes from the library's column-sum kernel); anything else — a replaced layer, a layer
@@ -304,6 +365,7 @@ class RecurrentBlock(nn.Module):
         if x.dim() != 3:
             raise ValueError(f"RecurrentBlock expects [batch, sequence, width], got {tuple(x.shape)}")
         batch, steps = x.shape[:2]
+        caller_mask = active_mask        # the caller's own tensor object: what the padding-kind memo is keyed on
         if active_mask is not None:
             if active_mask.shape != (batch, steps):
                 raise ValueError("active_mask must match the input [batch, sequence] dimensions")
@@ -320,13 +382,13 @@ class RecurrentBlock(nn.Module):
             y_branch = F.gelu(y_branch, approximate="tanh")
         x_in = _project(self.linear_x, x)
         restore = None
-        if active_mask is not None and steps > 1 and bool((active_mask[:, 1:] & ~active_mask[:, :-1]).any()):
+        if active_mask is not None and steps > 1 and _needs_partition(active_mask, caller_mask):
             # a real token follows padding somewhere: stable partition of every row, real tokens first
-            order = torch.argsort((~active_mask).to(torch.uint8), dim=1, stable=True)
-            restore = torch.argsort(order, dim=1)
-            x_in = x_in.gather(1, order[..., None].expand(-1, -1, x_in.size(-1)))
+            order, restore = _stable_partition(active_mask)
+            flat_order, flat_restore = _flat_rows(order), _flat_rows(restore)
+            x_in = _PermuteRows.apply(x_in, flat_order, flat_restore)
             if self.fold_merge:   # the kernels multiply by the branch, so it travels with its tokens
-                y_branch = y_branch.gather(1, order[..., None].expand(-1, -1, y_branch.size(-1)))
+                y_branch = _PermuteRows.apply(y_branch, flat_order, flat_restore)
             kernel_pos, kernel_active = pos.gather(1, order), active_mask.gather(1, order)
         else:
             kernel_pos, kernel_active = pos, active_mask
@@ -377,7 +439,7 @@ class RecurrentBlock(nn.Module):
             y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags,
                                      _branch=y_branch if self.fold_merge else None)
         if restore is not None:
-            y = y.gather(1, restore[..., None].expand(-1, -1, y.size(-1)))
+            y = _PermuteRows.apply(y, flat_restore, flat_order)
         out = _project(self.linear_out, y if self.fold_merge else y * y_branch)
         if active_mask is not None:
             out = torch.where(active_mask[..., None], out, torch.zeros_like(out))

@@ -220,3 +220,41 @@ def test_scan_self_check_says_no_without_a_cuda_device():
     assert cuda_scan_is_usable("cpu") is False
     with pytest.raises(RuntimeError):
         cuda_scan_is_usable("cpu", strict=True)
+
+
+def test_stable_partition_matches_a_stable_sort():
+    """Rows whose padding is not right padding are reordered real-tokens-first; the indices come from running counts
+    and must equal those of a stable sort of the mask (behaviour pinned by the reference: padding neither enters the
+    conv history nor moves the state, griffin/griffin.py:488-510)."""
+    from griffin_b200.modules import _stable_partition
+    gen = torch.Generator().manual_seed(11)
+    for steps in (1, 2, 7, 64, 129):
+        mask = torch.rand(6, steps, generator=gen) < 0.6
+        mask[0] = True
+        mask[1] = False
+        order, restore = _stable_partition(mask)
+        want_order = torch.argsort((~mask).to(torch.uint8), dim=1, stable=True)
+        assert torch.equal(order, want_order)
+        assert torch.equal(restore, torch.argsort(want_order, dim=1))
+        assert torch.equal(torch.gather(order, 1, restore), torch.arange(steps).expand(6, steps))
+
+
+def test_row_permutation_has_a_gather_backward_and_the_padding_kind_is_remembered_per_mask_object():
+    from griffin_b200.modules import _flat_rows, _needs_partition, _PermuteRows, _stable_partition
+    gen = torch.Generator().manual_seed(12)
+    mask = torch.rand(3, 9, generator=gen) < 0.6
+    order, restore = _stable_partition(mask)
+    x = torch.randn(3, 9, 4, dtype=torch.float64, generator=gen).requires_grad_(True)
+    flat_order, flat_restore = _flat_rows(order), _flat_rows(restore)
+    moved = _PermuteRows.apply(x, flat_order, flat_restore)
+    plain = x.gather(1, order[..., None].expand(-1, -1, 4))
+    assert torch.equal(moved, plain)
+    g = torch.randn(3, 9, 4, dtype=torch.float64, generator=gen)
+    assert torch.equal(torch.autograd.grad(moved, x, g)[0], torch.autograd.grad(plain, x, g)[0])
+    assert torch.equal(_PermuteRows.apply(moved, flat_restore, flat_order), x)
+    right = torch.ones(2, 5, dtype=torch.bool)
+    right[:, 3:] = False
+    assert _needs_partition(right, right) is False and _needs_partition(right, right) is False
+    right[0, 4] = True                     # an in-place change is a new version: the answer is worked out again
+    assert _needs_partition(right, right) is True
+    assert _needs_partition(right.clone(), right.clone()) is True      # another object: no stale hit
