@@ -442,7 +442,7 @@ class RecurrentBlock(nn.Module):
             y = _PermuteRows.apply(y, flat_restore, flat_order)
         out = _project(self.linear_out, y if self.fold_merge else y * y_branch)
         if active_mask is not None:
-            out = torch.where(active_mask[..., None], out, torch.zeros_like(out))
+            out = torch.where(active_mask[..., None], out, 0.0)     # (a scalar: no tensor of zeros to write and read)
         if return_cache:
             return out, RecurrentBlockCache(new_rnn, new_conv, _last_real_position(pos, active_mask, previous))
         return out
