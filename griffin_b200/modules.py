@@ -306,6 +306,36 @@ def _needs_partition(active: Tensor, owner: Tensor) -> bool:
     return answer
 
 
+_MASK_PLANS: dict = {}
+
+
+def _shared_between_blocks(owners: tuple, device, build):
+    """``build()``, remembered per (owner tensor OBJECTS, their versions, device).  A model hands the same
+    ``segment_pos`` / ``active_mask`` tensors to every one of its recurrent blocks, and what a block derives from them
+    (positions, flag bytes, the row partition) is the same for all: the first block builds it, the others take it.
+    Nothing is remembered while tracing, under ``torch.inference_mode`` (an inference tensor could not be saved for
+    a later backward) or while a CUDA graph is being captured (a tensor born in a capture holds data only after a
+    replay).  The shared tensors are read-only and live on the stream that built them, like the inputs they come
+    from."""
+    import weakref
+    live = tuple(o for o in owners if o is not None)
+    if (not live or ops._library_ops_active() or torch.is_inference_mode_enabled()
+            or (device.type == "cuda" and torch.cuda.is_current_stream_capturing())):
+        return build()
+    key = tuple(0 if o is None else id(o) for o in owners) + (str(device),)
+    hit = _MASK_PLANS.get(key)
+    if hit is not None and all(ref() is o and version == o._version for (ref, version), o in zip(hit[0], live)):
+        return hit[1]
+    value = build()
+    if len(_MASK_PLANS) > 16:
+        _MASK_PLANS.clear()
+    try:
+        _MASK_PLANS[key] = (tuple((weakref.ref(o), o._version) for o in live), value)
+    except TypeError:      # (a tensor subclass without weak references: nothing is remembered)
+        pass
+    return value
+
+
 def _project(layer: nn.Module, x: Tensor) -> Tensor:
     """One of the block's three projections.  A stock ``nn.Linear`` without hooks goes through ``ops.linear`` (same
     GEMMs; the bias gradient comes from the library's column-sum kernel); anything else — a replaced layer, a layer
@@ -372,37 +402,46 @@ class RecurrentBlock(nn.Module):
             active_mask = active_mask.to(device=x.device, dtype=torch.bool)
         previous = None if cache is None else cache.segment_position
         plain = segment_pos is None and cache is None and active_mask is None
-        # rows that are one fresh document each need no position tensor unless a cache is asked for
-        pos = None if plain and not return_cache else _positions(x, segment_pos, previous, active_mask)
         if plain and steps == 0:
             raise ValueError("Empty token sequences are not supported")
+        caller_pos = segment_pos
+        device = x.device
+
+        def mask_plan():
+            """(positions, flag bytes, flat indices of the row partition or None) for this call's masks."""
+            # rows that are one fresh document each need no position tensor unless a cache is asked for
+            pos = None if plain and not return_cache else _positions(x, segment_pos, previous, active_mask)
+            if plain:
+                # contiguous positions 0..T-1: only the first three tokens lose taps, token 0 is a reset
+                return pos, _plain_flags(batch, steps, device), None
+            moves = None
+            kernel_pos, kernel_active = pos, active_mask
+            if active_mask is not None and steps > 1 and _needs_partition(active_mask, caller_mask):
+                # a real token follows padding somewhere: stable partition of every row, real tokens first
+                order, restore = _stable_partition(active_mask)
+                moves = (_flat_rows(order), _flat_rows(restore))
+                kernel_pos, kernel_active = pos.gather(1, order), active_mask.gather(1, order)
+            padded = None if kernel_active is None else ~kernel_active.all()
+            flags = token_flags(batch, steps, device, reset=kernel_pos == 0, active=kernel_active,
+                                segment_pos=kernel_pos, padded=padded)
+            return pos, flags, moves
+
+        if plain or cache is not None:      # (the plain flags have a memo of their own; a cache differs per block)
+            pos, flags, moves = mask_plan()
+        else:
+            pos, flags, moves = _shared_between_blocks((caller_pos, caller_mask), device, mask_plan)
 
         y_branch = _project(self.linear_y, x)
         if not self.fold_merge:
             y_branch = F.gelu(y_branch, approximate="tanh")
         x_in = _project(self.linear_x, x)
-        restore = None
-        if active_mask is not None and steps > 1 and _needs_partition(active_mask, caller_mask):
-            # a real token follows padding somewhere: stable partition of every row, real tokens first
-            order, restore = _stable_partition(active_mask)
-            flat_order, flat_restore = _flat_rows(order), _flat_rows(restore)
-            x_in = _PermuteRows.apply(x_in, flat_order, flat_restore)
+        if moves is not None:
+            x_in = _PermuteRows.apply(x_in, moves[0], moves[1])
             if self.fold_merge:   # the kernels multiply by the branch, so it travels with its tokens
-                y_branch = _PermuteRows.apply(y_branch, flat_order, flat_restore)
-            kernel_pos, kernel_active = pos.gather(1, order), active_mask.gather(1, order)
-        else:
-            kernel_pos, kernel_active = pos, active_mask
+                y_branch = _PermuteRows.apply(y_branch, moves[0], moves[1])
         conv_state = None if cache is None else cache.conv_state
         if conv_state is not None and conv_state.shape != (batch, self.conv_kernel_size - 1, self.rnn_width):
             raise ValueError("Recurrent convolution cache has an incompatible shape")
-
-        if plain:
-            # contiguous positions 0..T-1: only the first three tokens lose taps, token 0 is a reset
-            flags = _plain_flags(batch, steps, x.device)
-        else:
-            padded = None if kernel_active is None else ~kernel_active.all()
-            flags = token_flags(batch, steps, x.device, reset=kernel_pos == 0, active=kernel_active,
-                                segment_pos=kernel_pos, padded=padded)
 
         conv_w = self.temporal_conv.weight[:, 0, :]
         rnn_state = None if cache is None else cache.rnn_state
@@ -438,8 +477,8 @@ class RecurrentBlock(nn.Module):
                                                want_state=return_cache)
             y, new_rnn = self.rg_lru(x_conv, rnn_state, return_state=True, _flags=flags,
                                      _branch=y_branch if self.fold_merge else None)
-        if restore is not None:
-            y = _PermuteRows.apply(y, flat_restore, flat_order)
+        if moves is not None:
+            y = _PermuteRows.apply(y, moves[1], moves[0])
         out = _project(self.linear_out, y if self.fold_merge else y * y_branch)
         if active_mask is not None:
             out = torch.where(active_mask[..., None], out, 0.0)     # (a scalar: no tensor of zeros to write and read)

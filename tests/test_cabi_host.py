@@ -258,3 +258,25 @@ def test_row_permutation_has_a_gather_backward_and_the_padding_kind_is_remembere
     right[0, 4] = True                     # an in-place change is a new version: the answer is worked out again
     assert _needs_partition(right, right) is True
     assert _needs_partition(right.clone(), right.clone()) is True      # another object: no stale hit
+
+
+def test_mask_plans_are_shared_per_tensor_object_and_version():
+    from griffin_b200.modules import _shared_between_blocks
+    calls = []
+
+    def build():
+        calls.append(1)
+        return len(calls)
+
+    pos, mask = torch.arange(6).reshape(1, 6), torch.ones(1, 6, dtype=torch.bool)
+    cpu = torch.device("cpu")
+    assert _shared_between_blocks((pos, mask), cpu, build) == 1
+    assert _shared_between_blocks((pos, mask), cpu, build) == 1            # same objects, same versions: remembered
+    assert _shared_between_blocks((pos, None), cpu, build) == 2            # another combination
+    mask[0, 5] = False                                                     # in-place change: a new version
+    assert _shared_between_blocks((pos, mask), cpu, build) == 3
+    assert _shared_between_blocks((pos.clone(), mask), cpu, build) == 4    # another object with equal content
+    with torch.inference_mode():
+        assert _shared_between_blocks((pos, mask), cpu, build) == 5        # nothing is remembered here ...
+    assert _shared_between_blocks((pos, mask), cpu, build) == 3            # ... and the earlier entry is untouched
+    assert _shared_between_blocks((None, None), cpu, build) == 6           # no owner: nothing to key on

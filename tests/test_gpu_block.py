@@ -475,3 +475,34 @@ def test_folded_block_matches_reference_gradients_and_cache():
     with torch.no_grad():
         out = blk(case["x"].to(DEV), segment_pos=case["segment_pos"].to(DEV))
     torch.testing.assert_close(out.cpu(), case["full"], atol=2e-6, rtol=2e-5)
+
+
+def test_blocks_that_share_mask_tensors_agree_with_blocks_given_their_own_copies():
+    """A model hands one segment_pos / active_mask tensor to all its blocks; what the first block derives from them
+    is reused by the others.  Results must equal those of calls given fresh copies (nothing to reuse), also after
+    the mask has been changed in place, and with padding that is not right padding."""
+    from griffin_b200 import RecurrentBlock
+    torch.manual_seed(21)
+    B, T = 3, 70
+    blocks = [RecurrentBlock(32, 64, gate_blocks=1).to(DEV) for _ in range(2)]
+    x = torch.randn(B, T, 32, device=DEV)
+    pos = (torch.arange(T, device=DEV) % 23).expand(B, T).contiguous()
+    mask = torch.ones(B, T, dtype=torch.bool, device=DEV)
+    mask[1, 50:] = False                                   # right padding
+    mask[2, :7] = False                                    # left padding: rows are partitioned
+
+    def run(p, m):
+        h = x
+        for blk in blocks:
+            h = blk(h, segment_pos=p() if callable(p) else p, active_mask=m() if callable(m) else m)
+        return h
+
+    shared = run(pos, mask)
+    fresh = run(lambda: pos.clone(), lambda: mask.clone())
+    assert torch.equal(shared, fresh)
+    mask[0, 60:] = False                                   # same object, new version
+    assert torch.equal(run(pos, mask), run(lambda: pos.clone(), lambda: mask.clone()))
+    assert not torch.equal(run(pos, mask), shared)
+    g = torch.autograd.grad(run(pos, mask).square().sum(), blocks[0].linear_x.weight)[0]
+    g2 = torch.autograd.grad(run(lambda: pos.clone(), lambda: mask.clone()).square().sum(), blocks[0].linear_x.weight)[0]
+    assert torch.equal(g, g2)
