@@ -283,7 +283,24 @@ class _PermuteRows(torch.autograd.Function):
         return grad.reshape(flat_inverse.numel(), -1).index_select(0, flat_inverse).view(grad.shape), None, None
 
 
-_PADDING_KIND: dict = {}     # id(mask tensor) -> (weak reference, version, answer)
+def _memo_stamp(t: Tensor):
+    """(weak reference, version) identifying a tensor object in its present state, or None where that cannot be had
+    (inference tensors track no version; some subclasses take no weak references): then nothing is remembered."""
+    import weakref
+    try:
+        return weakref.ref(t), t._version
+    except (RuntimeError, TypeError):
+        return None
+
+
+def _memo_hit(stamp, t: Tensor) -> bool:
+    try:
+        return stamp[0]() is t and stamp[1] == t._version
+    except RuntimeError:
+        return False
+
+
+_PADDING_KIND: dict = {}     # id(mask tensor) -> ((weak reference, version), answer)
 
 
 def _needs_partition(active: Tensor, owner: Tensor) -> bool:
@@ -291,18 +308,16 @@ def _needs_partition(active: Tensor, owner: Tensor) -> bool:
     device-to-host read, so it is remembered per mask OBJECT (``owner``: the tensor the caller passed, of which
     ``active`` is the boolean copy on the right device) and version: a model hands the same mask tensor to every one
     of its blocks, and only the first of them waits for the device."""
-    import weakref
     key = id(owner)
     hit = _PADDING_KIND.get(key)
-    if hit is not None and hit[0]() is owner and hit[1] == owner._version:
-        return hit[2]
+    if hit is not None and _memo_hit(hit[0], owner):
+        return hit[1]
     answer = bool((active[:, 1:] & ~active[:, :-1]).any())
-    if len(_PADDING_KIND) > 64:
-        _PADDING_KIND.clear()
-    try:
-        _PADDING_KIND[key] = (weakref.ref(owner), owner._version, answer)
-    except TypeError:      # (a tensor subclass without weak references: no caching)
-        pass
+    stamp = _memo_stamp(owner)
+    if stamp is not None:
+        if len(_PADDING_KIND) > 64:
+            _PADDING_KIND.clear()
+        _PADDING_KIND[key] = (stamp, answer)
     return answer
 
 
@@ -317,22 +332,20 @@ def _shared_between_blocks(owners: tuple, device, build):
     a later backward) or while a CUDA graph is being captured (a tensor born in a capture holds data only after a
     replay).  The shared tensors are read-only and live on the stream that built them, like the inputs they come
     from."""
-    import weakref
     live = tuple(o for o in owners if o is not None)
     if (not live or ops._library_ops_active() or torch.is_inference_mode_enabled()
             or (device.type == "cuda" and torch.cuda.is_current_stream_capturing())):
         return build()
     key = tuple(0 if o is None else id(o) for o in owners) + (str(device),)
     hit = _MASK_PLANS.get(key)
-    if hit is not None and all(ref() is o and version == o._version for (ref, version), o in zip(hit[0], live)):
+    if hit is not None and all(_memo_hit(stamp, o) for stamp, o in zip(hit[0], live)):
         return hit[1]
     value = build()
-    if len(_MASK_PLANS) > 16:
-        _MASK_PLANS.clear()
-    try:
-        _MASK_PLANS[key] = (tuple((weakref.ref(o), o._version) for o in live), value)
-    except TypeError:      # (a tensor subclass without weak references: nothing is remembered)
-        pass
+    stamps = tuple(_memo_stamp(o) for o in live)
+    if all(stamp is not None for stamp in stamps):
+        if len(_MASK_PLANS) > 16:
+            _MASK_PLANS.clear()
+        _MASK_PLANS[key] = (stamps, value)
     return value
 
 

@@ -280,3 +280,15 @@ def test_mask_plans_are_shared_per_tensor_object_and_version():
         assert _shared_between_blocks((pos, mask), cpu, build) == 5        # nothing is remembered here ...
     assert _shared_between_blocks((pos, mask), cpu, build) == 3            # ... and the earlier entry is untouched
     assert _shared_between_blocks((None, None), cpu, build) == 6           # no owner: nothing to key on
+
+
+def test_memos_leave_inference_tensors_alone():
+    from griffin_b200.modules import _needs_partition, _shared_between_blocks
+    with torch.inference_mode():
+        mask = torch.ones(2, 5, dtype=torch.bool)
+        mask[0, :2] = False
+    calls = []
+    for _ in range(2):       # an inference tensor tracks no version: worked out every time, never an error
+        assert _needs_partition(mask, mask) is True
+        assert _shared_between_blocks((None, mask), torch.device("cpu"), lambda: calls.append(1) or len(calls)) == len(calls)
+    assert len(calls) == 2
