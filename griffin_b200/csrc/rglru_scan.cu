@@ -1041,10 +1041,8 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
 
   // Per-row partial of sum_t dl * r: fold the time-lanes in a fixed order.
   bar_compute(NCOMP);
-  if (self_issuer) {             // the last chunk's results
-    store(nchunks - 1);
-    tma_wait_all<0>();
-  }
+  if (self_issuer) store(nchunks - 1);     // the last chunk's results; the issuing thread drains its stores on its way out
+  auto drain = [&]() { if (USE_TMA && SELF_ISSUE && self_issuer) tma_wait_all<0>(); };
   *reinterpret_cast<float4*>(einF + lane_t * CH + vec * CV) = make_float4(dlam[0].x, dlam[0].y, dlam[1].x, dlam[1].y);
   if (GROUPED) {   // the chain planes are free now: the two gate sums go through them the same way
     *reinterpret_cast<float4*>(einR + lane_t * CH + vec * CV) = make_float4(dsr[0].x, dsr[0].y, dsr[1].x, dsr[1].y);
@@ -1061,20 +1059,23 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     if (which == 0) p.dlam_part[static_cast<size_t>(b) * p.D + dch] = acc;
     else if (p.dgate_part) p.dgate_part[static_cast<size_t>(b) * 2 * p.D + (which == 1 ? rcol : icol) + cch] = acc;
   }
-  if (!p.ticket) return;   // the caller folds the rows with rglru_dlambda_kernel
+  if (!p.ticket) { drain(); return; }   // the caller folds the rows with rglru_dlambda_kernel
 
   // The CTA that finishes last folds the per-row partials into dLambda (rows in index order, so the
   // result does not depend on which CTA that is) and re-arms the ticket for the next backward call.
+  // The ticket is one acquire-release atomic by one thread between two CTA barriers: the barrier in front makes
+  // the partial rows every thread of this CTA stored part of what the release publishes, the barrier behind makes
+  // what the acquire saw (the other CTAs' rows) visible to every thread that goes on to read them, past L1.
   __shared__ int s_last;
-  __threadfence();
   bar_compute(NCOMP);
   if (tid == 0) {
     const unsigned total = gridDim.x * gridDim.y;
-    s_last = (atomicAdd(p.ticket, 1u) == total - 1u) ? 1 : 0;
+    unsigned before;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(before) : "l"(p.ticket), "r"(1u) : "memory");
+    s_last = (before == total - 1u) ? 1 : 0;
   }
   bar_compute(NCOMP);
-  if (!s_last) return;
-  __threadfence();
+  if (!s_last) { drain(); return; }
   // Rows are added in index order whatever the load order; loads go out eight rows at a time so that the
   // fold costs a few round trips to L2, not one per row.
   if ((p.D & 3) == 0) {
@@ -1122,6 +1123,7 @@ __global__ void __launch_bounds__(LANES*(CH / CV) + ((USE_TMA && !SELF_ISSUE) ? 
     }
   }
   if (tid == 0) *p.ticket = 0u;
+  drain();
 }
 
 // out[n] = sum_b part[b, n], rows added in index order (gate-bias gradient when the batch is too large for the
